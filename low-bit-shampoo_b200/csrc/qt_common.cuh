@@ -1,0 +1,42 @@
+// Shared declarations of libqtensor_b200: status codes, stream / error bookkeeping and
+// the launcher prototypes that abi.cu forwards to.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/qtensor_b200.h"
+
+namespace qt {
+
+// Thread-local state behind qt_set_stream / qt_last_error.
+cudaStream_t current_stream();
+void set_current_stream(cudaStream_t s);
+int record(int status);          // stores status as this thread's last error and returns it
+int check_launch();              // cudaGetLastError -> QT_OK / QT_ERR_LAUNCH (recorded)
+
+inline bool valid_blocksize(int bs) {
+    return bs == 64 || bs == 128 || bs == 256 || bs == 512 || bs == 1024 || bs == 2048;
+}
+
+struct QuantArgs {
+    const void *A; int a_dtype; long long strideA;          // elements
+    const float *code;
+    int n, count, bs, bits;
+    float *absmax; long long stride_absmax;
+    float *diag; long long stride_diag;                     // diag == nullptr: plain variant
+    unsigned char *out; long long stride_out;               // bytes
+};
+
+struct DequantArgs {
+    const unsigned char *A; long long strideA;              // bytes
+    const float *code;
+    int n, count, bs, bits;
+    const float *absmax; long long stride_absmax;
+    const float *diag; long long stride_diag;
+    void *out; int out_dtype; long long stride_out;         // elements
+};
+
+int launch_quantize(const QuantArgs &a, cudaStream_t stream);
+int launch_dequantize(const DequantArgs &a, cudaStream_t stream);
+
+}  // namespace qt

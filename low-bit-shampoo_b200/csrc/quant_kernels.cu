@@ -1,0 +1,608 @@
+// Blockwise low-bit quantize / dequantize of square matrices for sm_100a.
+//
+// Semantics follow the reference's CPU quantizer (reference project paths):
+//   qtensor/functional.py:526-615 (_quantize_blockwise_cpu), :618-688
+//   (_dequantize_blockwise_cpu), :703-715 (_nearest_code_indices), :718-746 (nibble
+//   packing) - and replace the CUDA kernels of cudaC_python/csrc/kernels.cu:57-457.
+//
+// Design (HBM-bound byte work, no tensor cores):
+//   * one launch covers a strided batch of same-order matrices (gridDim.y = matrix);
+//   * a quantization block (64..256 elements of one row) is owned by a group of LPU
+//     lanes of one warp, EPL consecutive elements per lane, loaded as 128-bit vectors;
+//     the per-block absmax is a shuffle reduction inside the group;
+//   * the nearest-code rule |q-c_lo| > |c_hi-q| (fp32) is monotone in q, so it is
+//     replaced by 2^bits-1 exact fp32 thresholds found once per CTA by bisection over
+//     float bit patterns; the code index is the number of thresholds <= q.  For 16-entry
+//     codebooks a 1025-cell lookup table in shared memory gives (base index, threshold)
+//     per cell so that one LDS.64 and one compare resolve an element;
+//   * q = x / absmax is an IEEE-rounded fp32 division (the oracle divides);
+//   * codes are packed high-nibble-first and stored as 16/32-bit words.
+//   Orders that are not a multiple of 4, unaligned buffers and block sizes above 256
+//   take a generic two-kernel path (absmax pass, then one thread per output byte).
+#include "qt_common.cuh"
+#include <math_constants.h>
+
+namespace qt {
+
+static constexpr int kLutScale = 512;
+static constexpr int kLutCells = 2 * kLutScale + 1;
+static constexpr int kThreads = 256;
+
+// ------------------------------------------------------------------------------------
+// Codebook tables, built per CTA in shared memory.
+// ------------------------------------------------------------------------------------
+template <int NC>
+struct CodeTables {
+    float raw[NC];
+    float sorted[NC];
+    float thr[NC];            // thr[j], j < NC-1: smallest q that rounds up from sorted[j]; thr[NC-1] = +inf
+    unsigned char perm[NC];   // sorted position -> caller's code index
+    float cmin, cmax;
+    int perm_identity;
+    int need_clamp;
+    int lut_bad;
+    float2 lut[NC == 16 ? kLutCells : 1];   // {threshold inside the cell or +inf, base index bits}
+};
+
+__device__ __forceinline__ long long float_key(float f) {
+    int i = __float_as_int(f);
+    return (long long)(i >= 0 ? i : (i ^ 0x7fffffff));
+}
+__device__ __forceinline__ float key_float(long long k) {
+    int i = (int)k;
+    return __int_as_float(i >= 0 ? i : (i ^ 0x7fffffff));
+}
+__device__ __forceinline__ int lut_cell(float v) {
+    int c = __float2int_rz(fmaf(v, (float)kLutScale, (float)kLutScale));
+    return min(max(c, 0), 2 * kLutScale);
+}
+
+template <int NC>
+__device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < NC; i += blockDim.x) t.raw[i] = code[i];
+    if (tid == 0) { t.lut_bad = 0; }
+    __syncthreads();
+    // stable rank sort (the reference sorts only when the codebook is not ascending;
+    // sorting an ascending codebook is the identity, functional.py:561-565)
+    for (int i = tid; i < NC; i += blockDim.x) {
+        float v = t.raw[i];
+        int rank = 0;
+        for (int j = 0; j < NC; ++j) {
+            float w = t.raw[j];
+            rank += (w < v) || (w == v && j < i);
+        }
+        t.sorted[rank] = v;
+        t.perm[rank] = (unsigned char)i;
+    }
+    __syncthreads();
+    for (int j = tid; j < NC; j += blockDim.x) {
+        if (j == NC - 1) { t.thr[j] = CUDART_INF_F; continue; }
+        const float lo = t.sorted[j], hi = t.sorted[j + 1];
+        // predicate P(q) = |q - lo| > |hi - q| is false at lo and monotone in q
+        long long a = float_key(lo), b = float_key(hi);
+        if (!(fabsf(hi - lo) > 0.0f)) { t.thr[j] = hi; continue; }
+        for (int it = 0; it < 64 && b - a > 1; ++it) {
+            long long m = a + ((b - a) >> 1);
+            float q = key_float(m);
+            bool up = fabsf(q - lo) > fabsf(hi - q);
+            if (up) b = m; else a = m;
+        }
+        t.thr[j] = key_float(b);
+    }
+    if (tid == 0) {
+        bool ident = true;
+        for (int j = 0; j < NC; ++j) ident = ident && (t.perm[j] == j);
+        t.perm_identity = ident;
+        t.cmin = t.sorted[0];
+        t.cmax = t.sorted[NC - 1];
+        t.need_clamp = !(t.sorted[0] <= -1.0f && t.sorted[NC - 1] >= 1.0f);
+    }
+    __syncthreads();
+    if (NC == 16) {
+        for (int k = tid; k < kLutCells; k += blockDim.x) {
+            int base = 0, inside = 0;
+            float th = CUDART_INF_F;
+            for (int j = 0; j < NC - 1; ++j) {
+                int cj = lut_cell(t.thr[j]);
+                base += (cj < k);
+                if (cj == k) { ++inside; th = t.thr[j]; }
+            }
+            if (inside > 1) t.lut_bad = 1;
+            t.lut[k] = make_float2(th, __int_as_float(base));
+        }
+        __syncthreads();
+    }
+}
+
+// Number of thresholds <= q (== index into the sorted codebook).
+template <int NC>
+__device__ __forceinline__ int code_index_search(const CodeTables<NC> &t, float q) {
+    int lo = 0;
+#pragma unroll
+    for (int step = NC / 2; step > 0; step >>= 1)
+        if (t.thr[lo + step - 1] <= q) lo += step;
+    return lo;
+}
+template <int NC>
+__device__ __forceinline__ int code_index(const CodeTables<NC> &t, float q, bool use_lut) {
+    if constexpr (NC == 16) {
+        if (use_lut) {
+            int cell = __float2int_rz(fmaf(q, (float)kLutScale, (float)kLutScale));
+            float2 e = t.lut[cell];
+            return __float_as_int(e.y) + (q >= e.x ? 1 : 0);
+        }
+    }
+    return code_index_search<NC>(t, q);
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Load EPL consecutive elements (EPL*sizeof(T) is 8, 16 or 32 bytes, pointer aligned to it or 16).
+template <typename T, int EPL>
+__device__ __forceinline__ void load_vec(const T *p, float (&x)[EPL]) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int j = 0; j < EPL; j += 4) {
+            float4 v = __ldg(reinterpret_cast<const float4 *>(p + j));
+            x[j] = v.x; x[j + 1] = v.y; x[j + 2] = v.z; x[j + 3] = v.w;
+        }
+    } else {
+        if constexpr (EPL == 8) {
+            uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
+            unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                x[2 * j] = __uint_as_float(w[j] << 16);
+                x[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
+        } else {
+            uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
+            x[0] = __uint_as_float(v.x << 16); x[1] = __uint_as_float(v.x & 0xffff0000u);
+            x[2] = __uint_as_float(v.y << 16); x[3] = __uint_as_float(v.y & 0xffff0000u);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Quantize, vector path.  Requires n % EPL == 0 and vector-aligned buffers.
+// ------------------------------------------------------------------------------------
+template <typename T, int BITS, int EPL, int LPU>
+__global__ void __launch_bounds__(kThreads)
+k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__restrict__ code,
+               int n, int nb, float *__restrict__ absmax_base, long long stride_absmax,
+               float *__restrict__ diag_base, long long stride_diag,
+               unsigned char *__restrict__ out_base, long long stride_out) {
+    constexpr int NC = 1 << BITS;
+    constexpr int BS = EPL * LPU;
+    __shared__ CodeTables<NC> tab;
+
+    const int m = blockIdx.y;
+    const T *A = Abase + (long long)m * strideA;
+    float *absmax = absmax_base + (long long)m * stride_absmax;
+    float *diag = diag_base ? diag_base + (long long)m * stride_diag : nullptr;
+    unsigned char *out = out_base + (long long)m * stride_out;
+
+    const int units = n * nb;
+    const int groups_per_cta = kThreads / LPU;
+    const int G = gridDim.x * groups_per_cta;               // groups striding over this matrix
+    const int lane_u = threadIdx.x % LPU;
+    int u = blockIdx.x * groups_per_cta + threadIdx.x / LPU;
+    // first unit of this thread's warp: uniform loop bound so shuffles see full warps
+    int u_warp = blockIdx.x * groups_per_cta + (threadIdx.x / 32) * (32 / LPU);
+    int r = u / nb, b = u - r * nb;
+    const int dr = G / nb, db = G - dr * nb;
+
+    // issue the first loads before the table build so its latency is hidden
+    float x[EPL];
+    bool have = false;
+    {
+        const int c = b * BS + lane_u * EPL;
+        if (u < units && c < n) { load_vec<T, EPL>(A + (long long)r * n + c, x); have = true; }
+    }
+    build_tables<NC>(tab, code);
+    const bool use_lut = (NC == 16) && !tab.lut_bad;
+    const bool clampq = tab.need_clamp;
+    const bool permute = !tab.perm_identity;
+    const float cmin = tab.cmin, cmax = tab.cmax;
+
+    for (; u_warp < units; u_warp += G) {
+        const int c = b * BS + lane_u * EPL;
+        const bool unit_ok = u < units;
+        const bool lane_ok = unit_ok && c < n;
+        if (!have) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) x[j] = 0.0f;
+            if (lane_ok) load_vec<T, EPL>(A + (long long)r * n + c, x);
+        }
+        have = false;
+        if (diag && lane_ok && r >= c && r < c + EPL) {       // functional.py:574-578
+#pragma unroll
+            for (int j = 0; j < EPL; ++j)
+                if (c + j == r) { diag[r] = x[j]; x[j] = 0.0f; }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) amax = fmaxf(amax, fabsf(x[j]));
+#pragma unroll
+        for (int off = LPU / 2; off > 0; off >>= 1)
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (unit_ok && lane_u == 0) absmax[(long long)r * nb + b] = amax;
+
+        if (lane_ok) {
+            int idx[EPL];
+            if (amax == 0.0f) {                               // functional.py:600-602
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) idx[j] = 0;
+            } else {
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) {
+                    float q = __fdiv_rn(x[j], amax);          // functional.py:604
+                    if (clampq) q = fminf(fmaxf(q, cmin), cmax);
+                    int k = code_index<NC>(tab, q, use_lut);
+                    if (permute) k = tab.perm[k];
+                    idx[j] = k;
+                }
+            }
+            const long long e = (long long)r * n + c;         // flat element index, multiple of EPL
+            if constexpr (BITS == 4) {
+                unsigned w = 0;
+#pragma unroll
+                for (int j = 0; j < EPL; j += 2)
+                    w |= (unsigned)((idx[j] << 4) | idx[j + 1]) << (4 * j);
+                if constexpr (EPL == 8) *reinterpret_cast<unsigned *>(out + (e >> 1)) = w;
+                else *reinterpret_cast<unsigned short *>(out + (e >> 1)) = (unsigned short)w;
+            } else {
+                unsigned w0 = 0, w1 = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w0 |= (unsigned)idx[j] << (8 * j);
+                if constexpr (EPL == 8) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) w1 |= (unsigned)idx[4 + j] << (8 * j);
+                    *reinterpret_cast<uint2 *>(out + e) = make_uint2(w0, w1);
+                } else {
+                    *reinterpret_cast<unsigned *>(out + e) = w0;
+                }
+            }
+        }
+        u += G; r += dr; b += db;
+        if (b >= nb) { b -= nb; r += 1; }
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Quantize, generic path: any order, any alignment, any supported block size.
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+k_absmax_generic(const T *__restrict__ Abase, long long strideA, int n, int nb, int bs,
+                 float *__restrict__ absmax_base, long long stride_absmax,
+                 float *__restrict__ diag_base, long long stride_diag) {
+    const int m = blockIdx.y;
+    const T *A = Abase + (long long)m * strideA;
+    float *absmax = absmax_base + (long long)m * stride_absmax;
+    float *diag = diag_base ? diag_base + (long long)m * stride_diag : nullptr;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * kThreads) >> 5;
+    const int units = n * nb;
+    for (int u = (blockIdx.x * kThreads + threadIdx.x) >> 5; u < units; u += warps) {
+        const int r = u / nb, b = u - r * nb;
+        const int c0 = b * bs, c1 = min(c0 + bs, n);
+        float amax = 0.0f;
+        for (int c = c0 + lane; c < c1; c += 32) {
+            float x = to_f32<T>(A[(long long)r * n + c]);
+            if (diag && c == r) { diag[r] = x; x = 0.0f; }
+            amax = fmaxf(amax, fabsf(x));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) absmax[u] = amax;
+    }
+}
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(kThreads)
+k_encode_generic(const T *__restrict__ Abase, long long strideA, const float *__restrict__ code,
+                 int n, int nb, int bs, const float *__restrict__ absmax_base, long long stride_absmax,
+                 int diagreal, unsigned char *__restrict__ out_base, long long stride_out) {
+    constexpr int NC = 1 << BITS;
+    constexpr int PER = 8 / BITS;                            // elements per output byte
+    __shared__ CodeTables<NC> tab;
+    build_tables<NC>(tab, code);
+    const int m = blockIdx.y;
+    const T *A = Abase + (long long)m * strideA;
+    const float *absmax = absmax_base + (long long)m * stride_absmax;
+    unsigned char *out = out_base + (long long)m * stride_out;
+    const long long total = (long long)n * n;
+    const long long nbytes = (total + PER - 1) / PER;
+    const bool use_lut = (NC == 16) && !tab.lut_bad;
+    for (long long byte = (long long)blockIdx.x * kThreads + threadIdx.x; byte < nbytes;
+         byte += (long long)gridDim.x * kThreads) {
+        unsigned v = 0;
+#pragma unroll
+        for (int h = 0; h < PER; ++h) {
+            const long long e = byte * PER + h;
+            int k = 0;                                        // padding nibble is 0 (functional.py:724-732)
+            if (e < total) {
+                const int r = (int)(e / n), c = (int)(e - (long long)r * n);
+                float x = to_f32<T>(A[e]);
+                if (diagreal && r == c) x = 0.0f;
+                const float amax = absmax[(long long)r * nb + c / bs];
+                if (amax != 0.0f) {
+                    float q = __fdiv_rn(x, amax);
+                    if (tab.need_clamp) q = fminf(fmaxf(q, tab.cmin), tab.cmax);
+                    k = tab.perm[code_index<NC>(tab, q, use_lut)];
+                }
+            }
+            v = (BITS == 4) ? ((v << 4) | (unsigned)k) : (unsigned)k;
+        }
+        out[byte] = (unsigned char)v;
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Dequantize.
+// ------------------------------------------------------------------------------------
+template <typename T, int EPL> __device__ __forceinline__ void store_vec(T *p, const float (&v)[EPL]);
+template <> __device__ __forceinline__ void store_vec<float, 4>(float *p, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store_vec<float, 8>(float *p, const float (&v)[8]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ unsigned pack_bf16x2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);           // .x = a (low half), .y = b
+    return *reinterpret_cast<unsigned *>(&h);
+}
+template <> __device__ __forceinline__ void store_vec<__nv_bfloat16, 4>(__nv_bfloat16 *p, const float (&v)[4]) {
+    *reinterpret_cast<uint2 *>(p) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+}
+template <> __device__ __forceinline__ void store_vec<__nv_bfloat16, 8>(__nv_bfloat16 *p, const float (&v)[8]) {
+    *reinterpret_cast<uint4 *>(p) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                               pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+
+// Vector path: n % EPL == 0, aligned buffers; any supported block size (power of two).
+template <typename T, int BITS, int EPL>
+__global__ void __launch_bounds__(kThreads)
+k_dequantize_vec(const unsigned char *__restrict__ in_base, long long stride_in, const float *__restrict__ code,
+                 int n, int nb, int bs_shift, const float *__restrict__ absmax_base, long long stride_absmax,
+                 const float *__restrict__ diag_base, long long stride_diag,
+                 T *__restrict__ out_base, long long stride_out) {
+    constexpr int NC = 1 << BITS;
+    __shared__ float2 pair_lut[BITS == 4 ? 256 : 1];          // byte -> (high-nibble value, low-nibble value)
+    __shared__ float code_s[BITS == 8 ? 256 : 16];
+    for (int i = threadIdx.x; i < NC; i += blockDim.x) code_s[i] = code[i];
+    __syncthreads();
+    if (BITS == 4)
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) pair_lut[i] = make_float2(code_s[i >> 4], code_s[i & 15]);
+    __syncthreads();
+
+    const int m = blockIdx.y;
+    const unsigned char *in = in_base + (long long)m * stride_in;
+    const float *absmax = absmax_base + (long long)m * stride_absmax;
+    const float *diag = diag_base ? diag_base + (long long)m * stride_diag : nullptr;
+    T *out = out_base + (long long)m * stride_out;
+
+    const int chunks_per_row = n / EPL;
+    const int chunks = n * chunks_per_row;
+    const int S = gridDim.x * kThreads;
+    int t = blockIdx.x * kThreads + threadIdx.x;
+    int r = t / chunks_per_row, cc = t - r * chunks_per_row;
+    const int dr = S / chunks_per_row, dc = S - dr * chunks_per_row;
+    for (; t < chunks; t += S) {
+        const int c = cc * EPL;
+        const long long e = (long long)r * n + c;
+        const float amax = __ldg(absmax + (long long)r * nb + (c >> bs_shift));
+        const float z = (amax == 0.0f) ? 0.0f : -0.0f;        // exact +0.0 for all-zero blocks (functional.py:663-665)
+        float v[EPL];
+        if constexpr (BITS == 4) {
+            unsigned w;
+            if constexpr (EPL == 8) w = __ldg(reinterpret_cast<const unsigned *>(in + (e >> 1)));
+            else w = __ldg(reinterpret_cast<const unsigned short *>(in + (e >> 1)));
+#pragma unroll
+            for (int j = 0; j < EPL / 2; ++j) {
+                float2 p = pair_lut[(w >> (8 * j)) & 255u];
+                v[2 * j] = fmaf(p.x, amax, z);
+                v[2 * j + 1] = fmaf(p.y, amax, z);
+            }
+        } else {
+            unsigned w0, w1 = 0;
+            if constexpr (EPL == 8) {
+                uint2 ww = __ldg(reinterpret_cast<const uint2 *>(in + e));
+                w0 = ww.x; w1 = ww.y;
+            } else {
+                w0 = __ldg(reinterpret_cast<const unsigned *>(in + e));
+            }
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) {
+                unsigned byte = ((j < 4 ? w0 : w1) >> (8 * (j & 3))) & 255u;
+                v[j] = fmaf(code_s[byte], amax, z);
+            }
+        }
+        if (diag && r >= c && r < c + EPL) {                  // functional.py:673-678
+            const float d = diag[r];
+#pragma unroll
+            for (int j = 0; j < EPL; ++j)
+                if (c + j == r) v[j] = d;
+        }
+        store_vec<T, EPL>(out + e, v);
+        r += dr; cc += dc;
+        if (cc >= chunks_per_row) { cc -= chunks_per_row; r += 1; }
+    }
+}
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(kThreads)
+k_dequantize_generic(const unsigned char *__restrict__ in_base, long long stride_in, const float *__restrict__ code,
+                     int n, int nb, int bs, const float *__restrict__ absmax_base, long long stride_absmax,
+                     const float *__restrict__ diag_base, long long stride_diag,
+                     T *__restrict__ out_base, long long stride_out) {
+    constexpr int NC = 1 << BITS;
+    __shared__ float code_s[NC];
+    for (int i = threadIdx.x; i < NC; i += blockDim.x) code_s[i] = code[i];
+    __syncthreads();
+    const int m = blockIdx.y;
+    const unsigned char *in = in_base + (long long)m * stride_in;
+    const float *absmax = absmax_base + (long long)m * stride_absmax;
+    const float *diag = diag_base ? diag_base + (long long)m * stride_diag : nullptr;
+    T *out = out_base + (long long)m * stride_out;
+    const long long total = (long long)n * n;
+    for (long long e = (long long)blockIdx.x * kThreads + threadIdx.x; e < total; e += (long long)gridDim.x * kThreads) {
+        const int r = (int)(e / n), c = (int)(e - (long long)r * n);
+        int k;
+        if (BITS == 8) k = in[e];
+        else { unsigned char byte = in[e >> 1]; k = (e & 1) ? (byte & 15) : (byte >> 4); }
+        const float amax = absmax[(long long)r * nb + c / bs];
+        float v = fmaf(code_s[k], amax, (amax == 0.0f) ? 0.0f : -0.0f);
+        if (diag && r == c) v = diag[r];
+        out[e] = from_f32<T>(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Host launchers.
+// ------------------------------------------------------------------------------------
+static int g_sm_count = 0;
+static int sm_count() {
+    if (g_sm_count == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        g_sm_count = n;
+    }
+    return g_sm_count;
+}
+
+static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// grid.x for `work_items` thread-iterations of one matrix, `count` matrices in grid.y:
+// enough CTAs to fill the machine a few times over, at least `min_iters` iterations per
+// thread where the matrix is large enough to amortise the per-CTA table build.
+static unsigned grid_x_for(long long thread_iters, int count, int min_iters) {
+    long long ctas = (thread_iters + (long long)kThreads * min_iters - 1) / ((long long)kThreads * min_iters);
+    const long long target = (long long)sm_count() * 8;      // resident CTAs of 256 threads per SM
+    long long per_matrix_cap = (target * 4 + count - 1) / count;
+    if (per_matrix_cap < 1) per_matrix_cap = 1;
+    if (ctas > per_matrix_cap) ctas = per_matrix_cap;
+    if (ctas < 1) ctas = 1;
+    return (unsigned)ctas;
+}
+
+template <typename T, int BITS>
+static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
+    const int n = a.n, nb = (n + a.bs - 1) / a.bs;
+    const T *A = static_cast<const T *>(a.A);
+    const size_t esz = sizeof(T);
+    const bool strides_ok8 = (a.strideA * (long long)esz) % 16 == 0 && a.stride_out % 4 == 0;
+    const bool strides_ok4 = (a.strideA * (long long)esz) % (4 * esz) == 0 && a.stride_out % (BITS == 4 ? 2 : 4) == 0;
+    const bool ptr_ok8 = aligned(A, 16) && aligned(a.out, BITS == 4 ? 4 : 8);
+    const bool ptr_ok4 = aligned(A, 4 * esz) && aligned(a.out, BITS == 4 ? 2 : 4);
+    const bool many = a.count > 1;
+    int epl = 0;
+    if (a.bs <= 256) {
+        if (n % 8 == 0 && ptr_ok8 && (!many || strides_ok8)) epl = 8;
+        else if (n % 4 == 0 && ptr_ok4 && (!many || strides_ok4) && a.bs <= 128) epl = 4;
+    }
+    if (epl) {
+        const int lpu = a.bs / epl;
+        const long long units = (long long)n * nb;
+        dim3 grid(grid_x_for(units * lpu, a.count, 4), a.count);
+#define QT_LAUNCH_Q(E, L)                                                                          \
+        k_quantize_vec<T, BITS, E, L><<<grid, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.absmax, \
+            a.stride_absmax, a.diag, a.stride_diag, a.out, a.stride_out)
+        if (epl == 8 && lpu == 8) QT_LAUNCH_Q(8, 8);
+        else if (epl == 8 && lpu == 16) QT_LAUNCH_Q(8, 16);
+        else if (epl == 8 && lpu == 32) QT_LAUNCH_Q(8, 32);
+        else if (epl == 4 && lpu == 16) QT_LAUNCH_Q(4, 16);
+        else QT_LAUNCH_Q(4, 32);
+#undef QT_LAUNCH_Q
+        return;
+    }
+    const long long units = (long long)n * nb;
+    dim3 g1(grid_x_for(units * 32, a.count, 1), a.count);
+    k_absmax_generic<T><<<g1, kThreads, 0, s>>>(A, a.strideA, n, nb, a.bs, a.absmax, a.stride_absmax, a.diag, a.stride_diag);
+    const long long nbytes = ((long long)n * n * BITS + 7) / 8;
+    dim3 g2(grid_x_for(nbytes, a.count, 4), a.count);
+    k_encode_generic<T, BITS><<<g2, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.bs, a.absmax, a.stride_absmax,
+                                                     a.diag != nullptr, a.out, a.stride_out);
+}
+
+int launch_quantize(const QuantArgs &a, cudaStream_t s) {
+    if (a.bits != 4 && a.bits != 8) return record(QT_ERR_BITS);
+    if (!valid_blocksize(a.bs)) return record(QT_ERR_BLOCKSIZE);
+    if (a.a_dtype != QT_F32 && a.a_dtype != QT_BF16) return record(QT_ERR_DTYPE);
+    if (a.n < 0 || a.count < 0 || a.n > 46340 || a.count > 65535) return record(QT_ERR_ARG);
+    if (a.n == 0 || a.count == 0) return record(QT_OK);
+    if (!a.A || !a.code || !a.absmax || !a.out) return record(QT_ERR_ARG);
+    if (!aligned(a.absmax, 4) || !aligned(a.code, 4) || (a.diag && !aligned(a.diag, 4))) return record(QT_ERR_ARG);
+    if (!aligned(a.A, a.a_dtype == QT_F32 ? 4 : 2)) return record(QT_ERR_ARG);
+    if (a.a_dtype == QT_F32) {
+        if (a.bits == 4) launch_quantize_typed<float, 4>(a, s); else launch_quantize_typed<float, 8>(a, s);
+    } else {
+        if (a.bits == 4) launch_quantize_typed<__nv_bfloat16, 4>(a, s); else launch_quantize_typed<__nv_bfloat16, 8>(a, s);
+    }
+    return check_launch();
+}
+
+template <typename T, int BITS>
+static void launch_dequantize_typed(const DequantArgs &a, cudaStream_t s) {
+    const int n = a.n, nb = (n + a.bs - 1) / a.bs;
+    T *out = static_cast<T *>(a.out);
+    const size_t esz = sizeof(T);
+    int bs_shift = 0;
+    while ((1 << bs_shift) < a.bs) ++bs_shift;
+    const bool many = a.count > 1;
+    auto ok = [&](int epl) {
+        const size_t in_bytes = (size_t)epl * BITS / 8, out_bytes = (size_t)(epl * esz > 16 ? 16 : epl * esz);
+        if (n % epl) return false;
+        if (!aligned(a.A, in_bytes) || !aligned(out, out_bytes)) return false;
+        if (many && (a.strideA % (long long)in_bytes || (a.stride_out * (long long)esz) % (long long)out_bytes)) return false;
+        return true;
+    };
+    // fp32 output: 4 elements per thread keeps every 128-bit store fully coalesced;
+    // bf16 output: 8 elements per thread make one 128-bit store.
+    int epl = 0;
+    if (esz == 2) epl = ok(8) ? 8 : (ok(4) ? 4 : 0);
+    else epl = ok(4) ? 4 : 0;
+    if (epl) {
+        const long long chunks = (long long)n * (n / epl);
+        dim3 grid(grid_x_for(chunks, a.count, 4), a.count);
+        if (epl == 8)
+            k_dequantize_vec<T, BITS, 8><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax,
+                a.stride_absmax, a.diag, a.stride_diag, out, a.stride_out);
+        else
+            k_dequantize_vec<T, BITS, 4><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax,
+                a.stride_absmax, a.diag, a.stride_diag, out, a.stride_out);
+        return;
+    }
+    dim3 grid(grid_x_for((long long)n * n, a.count, 4), a.count);
+    k_dequantize_generic<T, BITS><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, a.bs, a.absmax, a.stride_absmax,
+                                                           a.diag, a.stride_diag, out, a.stride_out);
+}
+
+int launch_dequantize(const DequantArgs &a, cudaStream_t s) {
+    if (a.bits != 4 && a.bits != 8) return record(QT_ERR_BITS);
+    if (!valid_blocksize(a.bs)) return record(QT_ERR_BLOCKSIZE);
+    if (a.out_dtype != QT_F32 && a.out_dtype != QT_BF16) return record(QT_ERR_DTYPE);
+    if (a.n < 0 || a.count < 0 || a.n > 46340 || a.count > 65535) return record(QT_ERR_ARG);
+    if (a.n == 0 || a.count == 0) return record(QT_OK);
+    if (!a.A || !a.code || !a.absmax || !a.out) return record(QT_ERR_ARG);
+    if (!aligned(a.absmax, 4) || !aligned(a.code, 4) || (a.diag && !aligned(a.diag, 4))) return record(QT_ERR_ARG);
+    if (!aligned(a.out, a.out_dtype == QT_F32 ? 4 : 2)) return record(QT_ERR_ARG);
+    if (a.out_dtype == QT_F32) {
+        if (a.bits == 4) launch_dequantize_typed<float, 4>(a, s); else launch_dequantize_typed<float, 8>(a, s);
+    } else {
+        if (a.bits == 4) launch_dequantize_typed<__nv_bfloat16, 4>(a, s); else launch_dequantize_typed<__nv_bfloat16, 8>(a, s);
+    }
+    return check_launch();
+}
+
+}  // namespace qt

@@ -1,0 +1,63 @@
+"""Loader of the native library (same role as the reference's qtensor/cextension.py:21-29).
+
+The reference picks `libqtensor_cuda{torch CUDA version}.so`; this build ships one
+sm_100a library, `libqtensor_b200.so`, next to this file.  There is no fallback: when
+the library is absent get_lib() raises, and every CUDA entry point of
+qtensor.functional then fails with a RuntimeError.
+"""
+import ctypes as ct
+from pathlib import Path
+
+LIBRARY_NAME = "libqtensor_b200.so"
+
+# every symbol the library must export: the sixteen that the reference's
+# qtensor/functional.py:17-60 dereferences at import time, then the additive ones
+LEGACY_SYMBOLS = tuple(
+    f"c{op}_blockwise_{kind}{bits}bit_{dt}"
+    for op in ("quantize", "dequantize")
+    for kind in ("", "diagreal_")
+    for bits in (8, 4)
+    for dt in ("fp32", "bf16")
+)
+EXTRA_SYMBOLS = (
+    "qt_version", "qt_last_error", "qt_error_string", "qt_set_stream",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise",
+)
+
+_lib = None
+
+
+def library_path() -> Path:
+    return (Path(__file__).parent / LIBRARY_NAME).resolve()
+
+
+def _declare(lib):
+    vp, i32, i64 = ct.c_void_p, ct.c_int, ct.c_longlong
+    lib.qt_version.restype = i32
+    lib.qt_last_error.restype = i32
+    lib.qt_error_string.restype = ct.c_char_p
+    lib.qt_error_string.argtypes = [i32]
+    lib.qt_set_stream.restype = None
+    lib.qt_set_stream.argtypes = [vp]
+    lib.qt_quantize_blockwise.restype = i32
+    lib.qt_quantize_blockwise.argtypes = [vp, i32, i64, vp, i32, i32, vp, i64, vp, i64, vp, i64, i32, i32, vp]
+    lib.qt_dequantize_blockwise.restype = i32
+    lib.qt_dequantize_blockwise.argtypes = [vp, i64, vp, i32, i32, vp, i64, vp, i64, vp, i32, i64, i32, i32, vp]
+    for name in LEGACY_SYMBOLS:
+        getattr(lib, name).restype = None
+    return lib
+
+
+def get_lib():
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not path.is_file():
+            raise FileNotFoundError(
+                f"Quantization library not found at {path}; build it with csrc/build.py (nvcc, sm_100a).")
+        lib = ct.cdll.LoadLibrary(str(path))
+        missing = [s for s in LEGACY_SYMBOLS + EXTRA_SYMBOLS if not hasattr(lib, s)]
+        if missing:
+            raise RuntimeError(f"{path} lacks symbols: {missing}")
+        _lib = _declare(lib)
+    return _lib
