@@ -1,0 +1,383 @@
+"""Shared implementation of the two Shampoo flavours.
+
+`shampoo2` keeps each statistic in eigen-factor form (QTensorSVDFast) and `shampoo1`
+keeps the dense statistic (QTensorDiagReal); everything else - blocking, schedule,
+grafting, the AdamW / SGD tails - is common.  Class and argument names follow the
+reference's optimizers/shampoo2.py (BlockPartitioner :35-99, Preconditioner :102-275,
+ShampooSGD :278-367, ShampooAdamW :370-468) and optimizers/shampoo1.py.
+"""
+import itertools
+import math
+from collections import defaultdict
+
+import torch
+import torch.optim as optim
+
+import qtensor.functional as F
+from qtensor.utils import QTensorDiagReal, QTensorSVDFast
+from optimizers import _engine as E
+
+CODE = 'linear-2'
+
+
+class BlockPartitioner:
+    """Splits every dimension longer than `block_size` into chunks of `block_size` plus a
+    remainder; a tensor becomes the row-major grid of those blocks."""
+
+    def __init__(self, var, block_size):
+        self._shape = var.shape
+        self._cuts = []                    # per dimension: list of chunk lengths
+        self._splits = []                  # (dim, interior cut positions) for split dimensions
+        self._split_sizes = []
+        for dim, d in enumerate(var.shape):
+            if block_size > 0 and d > block_size:
+                full, rest = divmod(d, block_size)
+                sizes = [block_size] * full + ([rest] if rest else [])
+                self._cuts.append(sizes)
+                self._splits.append((dim, list(itertools.accumulate(sizes))[:-1]))
+                self._split_sizes.append((dim, sizes))
+            else:
+                self._cuts.append([d])
+        self._num_splits = len(self._cuts)
+        self._preconditioner_shapes = []
+        for combo in itertools.product(*self._cuts):
+            self._preconditioner_shapes.extend([[d, d] for d in combo])
+
+    def shapes_for_preconditioners(self):
+        return self._preconditioner_shapes
+
+    def num_splits(self):
+        return self._num_splits
+
+    def block_slices(self):
+        """Index tuples of the blocks, in partition() order."""
+        per_dim = []
+        for sizes in self._cuts:
+            ends = list(itertools.accumulate(sizes))
+            per_dim.append([slice(e - s, e) for s, e in zip(sizes, ends)])
+        return list(itertools.product(*per_dim))
+
+    def partition(self, tensor):
+        assert tensor.shape == self._shape
+        return [tensor[idx] for idx in self.block_slices()]
+
+    def merge_partitions(self, partitions):
+        out = torch.empty(self._shape, dtype=partitions[0].dtype, device=partitions[0].device)
+        slices = self.block_slices()
+        assert len(slices) == len(partitions)
+        for idx, part in zip(slices, partitions):
+            out[idx].copy_(part)
+        return out
+
+
+def _transformed_shape(shape):
+    dims = [x for x in shape if x != 1]
+    if len(dims) > 1:
+        dims = (dims[0], -1)
+    return dims
+
+
+def preconditioner_orders(shape, prec_maxorder):
+    """Orders of the preconditioner matrices a parameter of `shape` gets (block-major, axis-minor)."""
+    ts = _transformed_shape(shape)
+    if len(ts) <= 1:
+        return []
+    numel = math.prod(shape)
+    rows = ts[0]
+    probe = torch.empty((rows, numel // rows), device="meta")
+    return [s[0] for s in BlockPartitioner(probe, prec_maxorder).shapes_for_preconditioners()]
+
+
+class Preconditioner:
+    """Statistics and inverse-root preconditioners of one parameter."""
+
+    flavour = "s2"
+
+    def __init__(self, var, name2qmap,
+                 stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200,
+                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64,
+                 rect_t1=1, rect_t2=4, inv_root_mode=0, classes=None):
+        self.stat_decay = stat_decay
+        self.matrix_eps = matrix_eps
+        self.inv_root_mode = inv_root_mode
+        self._original_shape = var.shape
+        self._transformed_shape = _transformed_shape(var.shape)
+        reshaped = torch.reshape(var, self._transformed_shape)
+        self._partitioner = BlockPartitioner(reshaped, prec_maxorder)
+        self._active = False
+        self.statistics = []
+        self.preconditioners = []
+        self._slots = []                                   # (OrderClass, slot) per statistic
+        rank = len(self._transformed_shape)
+        if rank <= 1:
+            return
+        if prec_bits in (4, 8) and not var.is_cuda:
+            raise RuntimeError("low-bit preconditioner state needs CUDA tensors; this package has no CPU quantizer "
+                               "(use prec_bits=32 for CPU runs)")
+        device = var.device
+        code = name2qmap[CODE].to(device) if prec_bits in (4, 8) else None
+        if code is not None:
+            name2qmap[CODE] = code
+        for shape in self._partitioner.shapes_for_preconditioners():
+            n = shape[0]
+            if classes is not None:
+                cls = classes[n]
+            else:
+                cls = E.OrderClass(n, 1, device, self.flavour, prec_bits, quan_blocksize, code, min_lowbit_size,
+                                   rect_t1, rect_t2)
+            slot = cls.alloc()
+            self._slots.append((cls, slot))
+            common = dict(bits=prec_bits, name2qmap=name2qmap, code=CODE, blocksize=quan_blocksize,
+                          min_lowbit_size=min_lowbit_size)
+            eye = torch.eye(n, device=device)
+            if self.flavour == "s2":
+                stat = QTensorSVDFast(matrix_eps * eye, rect_t1=rect_t1, rect_t2=rect_t2, log_prefix=None,
+                                      storage=cls.stat_storage(slot), **common)
+            else:
+                stat = QTensorDiagReal(matrix_eps * eye, storage=cls.stat_storage(slot), **common)
+            self.statistics.append(stat)
+            self.preconditioners.append(QTensorDiagReal(eye, storage=cls.prec.storage(slot), **common))
+
+    def set_device(self, device):
+        for s, p in zip(self.statistics, self.preconditioners):
+            s.set_device(device)
+            p.set_device(device)
+
+    # -- work lists consumed by the batched engine -------------------------------------
+    def _grad_blocks(self, grad):
+        return self._partitioner.partition(torch.reshape(grad, self._transformed_shape))
+
+    def statistics_items(self, grad):
+        rank = len(self._transformed_shape)
+        items = []
+        for j, g in enumerate(self._grad_blocks(grad)):
+            for axis in range(rank):
+                cls, slot = self._slots[j * rank + axis]
+                items.append((cls, slot, g, axis))
+        return items
+
+    def apply_items(self, grad):
+        items = []
+        for j, g in enumerate(self._grad_blocks(grad)):
+            (c0, s0), (c1, s1) = self._slots[2 * j], self._slots[2 * j + 1]
+            items.append((c0, s0, c1, s1, g))
+        return items
+
+    def merge(self, blocks):
+        return torch.reshape(self._partitioner.merge_partitions(blocks), self._original_shape)
+
+    # -- per-parameter entry points (reference API) --------------------------------------
+    def _weights(self):
+        w1 = self.stat_decay
+        return w1, (1.0 if w1 == 1.0 else 1.0 - w1)
+
+    def add_statistics(self, grad):
+        if not self.statistics:
+            return
+        E.add_statistics(self.statistics_items(grad), *self._weights(), eps=self.matrix_eps)
+
+    def compute_preconditioners(self):
+        if self.statistics:
+            E.compute_preconditioners(list(self._slots), self.matrix_eps, self.inv_root_mode)
+        self._active = True
+
+    def preconditioned_grad(self, grad):
+        if not self.preconditioners:
+            return grad
+        return self.merge(E.preconditioned_blocks(self.apply_items(grad)))
+
+    def is_active(self) -> bool:
+        return self._active
+
+
+def _make_codebooks(prec_bits):
+    name2qmap = {}
+    if prec_bits in (4, 8):
+        if CODE == 'dynamic':
+            name2qmap[CODE] = F.create_dynamic_map(signed=True, total_bits=prec_bits, power=1)
+        elif CODE == 'linear-2':
+            name2qmap[CODE] = F.create_linear_map(signed=True, total_bits=prec_bits, power=2)
+    return name2qmap
+
+
+class _ShampooBase(optim.Optimizer):
+    """Schedule, state creation and the batched preconditioning pass shared by the SGD and
+    AdamW variants.  Subclasses implement `_init_moments` and `_apply_update`."""
+
+    preconditioner_cls = Preconditioner
+
+    def _setup(self, prec_bits):
+        self.name2qmap = _make_codebooks(prec_bits)
+
+    def load_state_dict(self, state_dict):
+        super().load_state_dict(state_dict)
+        for group in self.param_groups:
+            for p in group['params']:
+                state = self.state[p]
+                if len(state) != 0:
+                    state['preconditioner'].set_device(p.device)
+
+    def _create_states(self, group, params):
+        """One arena per preconditioner order for all new parameters of the group."""
+        new = [p for p in params if len(self.state[p]) == 0]
+        if not new:
+            return
+        flavour = self.preconditioner_cls.flavour
+        counts = defaultdict(int)
+        for p in new:
+            for n in preconditioner_orders(p.shape, group['prec_maxorder']):
+                counts[(p.device, n)] += 1
+        bits = group['prec_bits']
+        classes = {}
+        for (device, n), c in counts.items():
+            code = None
+            if bits in (4, 8):
+                code = self.name2qmap[CODE].to(device)
+                self.name2qmap[CODE] = code
+            classes.setdefault(device, {})[n] = E.OrderClass(
+                n, c, device, flavour, bits, group['quan_blocksize'], code, group['min_lowbit_size'],
+                group.get('rect_t1', 1), group.get('rect_t2', 4))
+        for p in new:
+            state = self.state[p]
+            state['step'] = 0
+            state['preconditioner'] = self.preconditioner_cls(
+                p, self.name2qmap,
+                stat_decay=group['stat_decay'], matrix_eps=group['matrix_eps'], prec_maxorder=group['prec_maxorder'],
+                prec_bits=bits, min_lowbit_size=group['min_lowbit_size'], quan_blocksize=group['quan_blocksize'],
+                rect_t1=group.get('rect_t1', 1), rect_t2=group.get('rect_t2', 4),
+                inv_root_mode=group.get('inv_root_mode', 0), classes=classes.get(p.device))
+            self._init_moments(p, state)
+
+    def _precondition(self, group, params):
+        """Runs the statistics / inverse-root / apply phases for `params` (all with grads) and
+        returns the list of update directions (grafted to the gradient norm where active)."""
+        t1, t2 = group['stat_compute_steps'], group['prec_compute_steps']
+        start = group['start_prec_step']
+        stat_items, root_items, apply_list = [], [], []
+        w1 = group['stat_decay']
+        w2 = 1.0 if w1 == 1.0 else 1.0 - w1
+        for p in params:
+            state = self.state[p]
+            state['step'] += 1
+            pre = state['preconditioner']
+            if state['step'] % t1 == 0 and pre.statistics:
+                stat_items += pre.statistics_items(p.grad.data)
+        if stat_items:
+            E.add_statistics(stat_items, w1, w2, eps=group['matrix_eps'])
+        for p in params:
+            state = self.state[p]
+            pre = state['preconditioner']
+            if state['step'] % t2 == 0:
+                root_items += pre._slots
+                pre._active = True
+        if root_items:
+            E.compute_preconditioners(root_items, group['matrix_eps'], group.get('inv_root_mode', 0))
+        directions = []
+        for p in params:
+            state = self.state[p]
+            pre = state['preconditioner']
+            directions.append(p.grad.data)
+            if state['step'] >= start and pre.is_active():
+                apply_list.append((len(directions) - 1, p, pre))
+        if apply_list:
+            items, owner = [], []
+            for k, p, pre in apply_list:
+                if pre.preconditioners:
+                    its = pre.apply_items(p.grad.data)
+                    owner.append((k, pre, len(items), len(items) + len(its)))
+                    items += its
+            blocks = E.preconditioned_blocks(items) if items else []
+            for k, pre, a, b in owner:
+                directions[k] = pre.merge(blocks[a:b])
+            # grafting: rescale the direction to the gradient's norm (shampoo2.py:453).  For
+            # parameters without preconditioners the direction IS the gradient, scaled in place.
+            ks = [k for k, _, _ in apply_list]
+            dirs = [directions[k] for k in ks]
+            gn = torch._foreach_norm([params[k].grad.data for k in ks])
+            dn = torch._foreach_norm(dirs)
+            torch._foreach_add_(dn, 1e-12)
+            torch._foreach_div_(gn, dn)
+            torch._foreach_mul_(dirs, gn)
+        return directions
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        for group in self.param_groups:
+            params = [p for p in group['params'] if p.grad is not None]
+            for p in params:
+                if p.grad.data.is_sparse:
+                    raise RuntimeError('Shampoo does not support sparse yet')
+            if not params:
+                continue
+            self._create_states(group, params)
+            self._apply_update(group, params)
+
+
+class ShampooSGDBase(_ShampooBase):
+    def __init__(self, params, lr=0.1, momentum=0.9, weight_decay=0.0, nesterov=False,
+                 start_prec_step=1, stat_compute_steps=100, prec_compute_steps=500,
+                 stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200,
+                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, **extra):
+        defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay, nesterov=nesterov,
+                        start_prec_step=start_prec_step, stat_compute_steps=stat_compute_steps,
+                        prec_compute_steps=prec_compute_steps, stat_decay=stat_decay, matrix_eps=matrix_eps,
+                        prec_maxorder=prec_maxorder, prec_bits=prec_bits, min_lowbit_size=min_lowbit_size,
+                        quan_blocksize=quan_blocksize, **extra)
+        super().__init__(params, defaults)
+        self._setup(prec_bits)
+
+    def _init_moments(self, p, state):
+        state['momentum'] = torch.zeros_like(p, memory_format=torch.preserve_format)
+
+    def _apply_update(self, group, params):
+        directions = self._precondition(group, params)
+        wd, mom = group['weight_decay'], group['momentum']
+        for p, d in zip(params, directions):
+            buf = self.state[p]['momentum']
+            if wd != 0.0:
+                d.add_(p.data, alpha=wd)
+            buf.mul_(mom).add_(d)
+            upd = d.add(buf, alpha=mom) if group['nesterov'] else buf
+            p.data.add_(upd, alpha=-group['lr'])
+
+
+class ShampooAdamWBase(_ShampooBase):
+    def __init__(self, params, lr=0.001, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                 start_prec_step=1, stat_compute_steps=100, prec_compute_steps=500,
+                 stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200,
+                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, **extra):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                        start_prec_step=start_prec_step, stat_compute_steps=stat_compute_steps,
+                        prec_compute_steps=prec_compute_steps, stat_decay=stat_decay, matrix_eps=matrix_eps,
+                        prec_maxorder=prec_maxorder, prec_bits=prec_bits, min_lowbit_size=min_lowbit_size,
+                        quan_blocksize=quan_blocksize, **extra)
+        super().__init__(params, defaults)
+        self._setup(prec_bits)
+
+    def _init_moments(self, p, state):
+        state['exp_avg'] = torch.zeros_like(p, memory_format=torch.preserve_format)
+        state['exp_avg_sq'] = torch.zeros_like(p, memory_format=torch.preserve_format)
+
+    def _apply_update(self, group, params):
+        # decoupled weight decay first, as in the reference (shampoo2.py:441)
+        torch._foreach_mul_(params, 1 - group['lr'] * group['weight_decay'])
+        directions = self._precondition(group, params)
+        beta1, beta2 = group['betas']
+        by_step = defaultdict(list)
+        for k, p in enumerate(params):
+            by_step[self.state[p]['step']].append(k)
+        for step, ks in by_step.items():
+            ps = [params[k] for k in ks]
+            ds = [directions[k] for k in ks]
+            m1 = [self.state[p]['exp_avg'] for p in ps]
+            m2 = [self.state[p]['exp_avg_sq'] for p in ps]
+            bc1 = 1 - beta1 ** step
+            bc2 = 1 - beta2 ** step
+            torch._foreach_mul_(m1, beta1)
+            torch._foreach_add_(m1, ds, alpha=1 - beta1)
+            torch._foreach_mul_(m2, beta2)
+            torch._foreach_addcmul_(m2, ds, ds, value=1 - beta2)
+            denom = torch._foreach_sqrt(m2)
+            torch._foreach_div_(denom, math.sqrt(bc2))
+            torch._foreach_add_(denom, group['eps'])
+            torch._foreach_addcdiv_(ps, m1, denom, value=-(group['lr'] / bc1))

@@ -191,3 +191,16 @@ def dequantize_blockwise_diagreal(
 ) -> Tensor:
     """Inverse of quantize_blockwise_diagreal (diagonal restored from `diag`)."""
     return _dequantize(A, code, order, absmax, diag, outdtype, out, blocksize, bits, True)
+
+
+@torch.no_grad()
+def compute_power(Vt, S, p, iter_count=4, ridge_epsilon=1e-6, indices=None, max_eigen=None):
+    """Inverse p-th root from an eigen-factor form: rows `indices` of Vt are rectified by
+    `iter_count` Bjorck steps, then  rows^T diag((S + ridge * lambda_max)^(-1/p)) rows
+    (reference functional.py:749-762; lambda_max defaults to max(S))."""
+    rows = Vt[indices] if indices is not None else Vt
+    for _ in range(iter_count):
+        rows = torch.addmm(rows, rows @ rows.T, rows, beta=1.5, alpha=-0.5)
+    top = max_eigen if max_eigen is not None else S.max()
+    weights = 1 / (S + ridge_epsilon * top).pow(1 / p)
+    return rows.T @ (weights.unsqueeze(1) * rows)

@@ -37,3 +37,16 @@ def bits_equal(a, b):
     if a.shape != b.shape or a.dtype != b.dtype:
         return False
     return a.tobytes() == b.tobytes()
+
+
+def load_optimizer_cases():
+    blob = np.load(os.path.join(GOLDEN, "optimizer_cases.npz"))
+    meta = json.loads(bytes(blob["meta"]).decode())
+    return blob, meta
+
+
+def rel_fro(a, b):
+    """Relative Frobenius error ||a-b|| / ||b|| over a list of arrays taken as one vector."""
+    num = sum(float(np.sum((np.asarray(x, dtype=np.float64) - np.asarray(y, dtype=np.float64)) ** 2)) for x, y in zip(a, b))
+    den = sum(float(np.sum(np.asarray(y, dtype=np.float64) ** 2)) for y in b)
+    return (num / max(den, 1e-300)) ** 0.5
