@@ -1,0 +1,328 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: one shampoo2-AdamW 4-bit optimizer step on ViT-Base/32
+parameter shapes (every interval firing: statistics refresh, inverse 4th root, apply,
+AdamW tail), plus the blockwise quantize / dequantize rate of the same state.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU oracle port of the same
+step (oracle/shampoo_oracle.py + oracle/qoracle.c) on this machine's host cores, on a
+bounded sample of the workload.  Multi-GPU runs are launched with torch.distributed.run.
+"""
+import argparse
+import ctypes as ct
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "low-bit-shampoo_b200"))
+
+METRIC = "shampoo2 4-bit optimizer step ms (ViT-B/32); quant/dequant HBM GB/s"
+HYPER = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.05, start_prec_step=1,
+             stat_compute_steps=1, prec_compute_steps=1, stat_decay=0.95, matrix_eps=1e-6,
+             prec_maxorder=1200, prec_bits=4, min_lowbit_size=4096, quan_blocksize=64,
+             rect_t1=1, rect_t2=4, inv_root_mode=0)
+WORKLOAD = ("vit_base_patch32_224 parameter set (88.2M params, 226 preconditioner matrices of order "
+            "50..1200), shampoo2-adamw 4-bit block 64, T1=T2=1 so statistics refresh, inverse root and "
+            "apply all run every step")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the same step on the host cores.
+# ---------------------------------------------------------------------------------------
+
+SAMPLE_LAYERS = 4
+
+
+def vit_layer_shapes(layers=SAMPLE_LAYERS):
+    d, mlp = 768, 3072
+    one = [(3 * d, d), (3 * d,), (d, d), (d,), (mlp, d), (mlp,), (d, mlp), (d,), (d,), (d,), (d,), (d,)]
+    return one * layers
+
+
+def sum_cubes(shapes, maxorder=1200):
+    from optimizers._base import preconditioner_orders
+    return sum(n ** 3 for s in shapes for n in preconditioner_orders(tuple(s), maxorder))
+
+
+def cpu_reference_step_ms(steps, warmup):
+    """Oracle port on SAMPLE_LAYERS encoder layers (of 12) scaled to the full model by the
+    sum of n^3 over preconditioner orders."""
+    import torch
+    from oracle.shampoo_oracle import OracleShampoo
+    import workloads
+    shapes = vit_layer_shapes()
+    full = [tuple(p.shape) for p in workloads.vit_base_patch32_224().parameters()]
+    scale = sum_cubes(full) / sum_cubes(shapes)
+    g = torch.Generator().manual_seed(0)
+    params = [torch.randn(s, generator=g) * 0.02 for s in shapes]
+    opt = OracleShampoo(params, kind="adamw", flavour="s2", **{
+        "lr": HYPER["lr"], "betas": HYPER["betas"], "eps": HYPER["eps"], "weight_decay": HYPER["weight_decay"],
+        "stat_compute_steps": 1, "prec_compute_steps": 1, "stat_decay": HYPER["stat_decay"],
+        "matrix_eps": HYPER["matrix_eps"], "prec_maxorder": 1200, "prec_bits": 4, "quan_blocksize": 64,
+        "rect_t1": 1, "rect_t2": 4, "inv_root_mode": 0})
+    times = []
+    for it in range(warmup + steps):
+        grads = [torch.randn(s, generator=g) * 1e-2 for s in shapes]
+        t0 = time.perf_counter()
+        opt.step(grads)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    sample = (f"{SAMPLE_LAYERS} of 12 ViT-B/32 encoder layers ({len(shapes)} tensors, {18 * SAMPLE_LAYERS} preconditioner matrices), {steps} step(s) after "
+              f"{warmup} warm-up, {ms:.0f} ms per sample step, scaled x{scale:.2f} by sum n^3 to the full model")
+    return ms * scale, torch.get_num_threads(), sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+    ms, cores, sample = cpu_reference_step_ms(steps, warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": ms, "unit": "ms/step", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 arithmetic on 4-bit state", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in HYPER.items()}},
+            "cpu_baseline": {"value": ms, "unit": "ms/step", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": ms, "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm.
+# ---------------------------------------------------------------------------------------
+
+def quantizer_roofline(torch, lib, device, iters=20):
+    """Quantize / dequantize rate on the workload's largest order class (125 matrices of
+    order 768, 4-bit diagreal, block 64; 320 MB of fp32 per pass, larger than L2)."""
+    import qtensor.functional as F
+    n, count, bs = 768, 125, 64
+    nb = (n + bs - 1) // bs
+    A = torch.randn(count, n, n, device=device)
+    packed = torch.empty(count, n * n // 2, dtype=torch.uint8, device=device)
+    absmax = torch.empty(count, n * nb, device=device)
+    diag = torch.empty(count, n, device=device)
+    out = torch.empty_like(A)
+    code = F.create_linear_map(True, 4, 2).to(device)
+    p = lambda t: ct.c_void_p(t.data_ptr())
+    st = ct.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def q():
+        rc = lib.qt_quantize_blockwise(p(A), 0, n * n, p(code), n, count, p(absmax), n * nb, p(diag), n,
+                                       p(packed), n * n // 2, bs, 4, st)
+        assert rc == 0
+
+    def d():
+        rc = lib.qt_dequantize_blockwise(p(packed), n * n // 2, p(code), n, count, p(absmax), n * nb, p(diag), n,
+                                         p(out), 0, n * n, bs, 4, st)
+        assert rc == 0
+
+    bytes_per_launch = count * (4 * n * n + n * n // 2 + 4 * n * nb + 4 * n)
+    res = {}
+    for name, fn in (("quantize", q), ("dequantize", d)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        res[name] = {"us_per_launch": ms * 1e3, "gbs": bytes_per_launch / ms / 1e6}
+    return res, bytes_per_launch, f"{count} matrices of order {n}, 4-bit diagreal, block {bs}"
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    import workloads
+    from optimizers.shampoo2 import ShampooAdamW
+    from qtensor.cextension import get_lib
+    lib = get_lib()
+
+    torch.manual_seed(0)
+    model = workloads.vit_base_patch32_224().to(device)
+    params = [p for p in model.parameters()]
+    kwargs = dict(HYPER)
+    if world > 1:
+        kwargs["process_group"] = dist.group.WORLD
+    opt = ShampooAdamW(params, **kwargs)
+    loss = workloads.synthetic_gradients(model, 256, 224, 1000, device, autocast_bf16=True, seed=rank)
+    if world > 1:
+        for p in params:                     # data-parallel replicas: average gradients once
+            dist.all_reduce(p.grad, op=dist.ReduceOp.AVG)
+    grads = [p.grad.detach().clone() for p in params]
+    grad_bytes = sum(g.numel() * g.element_size() for g in grads)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernel-level: device-resident inputs ------------------------------------------
+    for _ in range(args.warmup):
+        opt.step()
+    barrier()
+    launches0 = lib.qt_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            opt.step()
+        e1.record()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = lib.qt_launch_count() - launches0
+    t = torch.tensor([ms_total], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+
+    # ---- end to end: gradients arrive from pinned host memory, a scalar goes back -----
+    host = [torch.empty(g.shape, dtype=g.dtype).pin_memory() for g in grads]
+    for h, g in zip(host, grads):
+        h.copy_(g)
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        for p, h in zip(params, host):
+            p.grad.copy_(h, non_blocking=True)
+        opt.step()
+        checksum = float(params[-1].detach().float().sum().cpu())
+    e3.record()
+    barrier()
+    t = torch.tensor([e2.elapsed_time(e3)], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    qres, qbytes, qdesc = quantizer_roofline(torch, lib, device)
+    roof = {"bound": "hbm", "kernel": "k_quantize_vec (4-bit diagreal, block 64)", "achieved": qres["quantize"]["gbs"],
+            "peak": hbm_peak, "unit": "GB/s", "frac": qres["quantize"]["gbs"] / hbm_peak, "peak_kind": f"of {peak_kind}",
+            "traffic": None, "bytes_per_launch": qbytes, "case": qdesc,
+            "dequantize": {"achieved": qres["dequantize"]["gbs"], "frac": qres["dequantize"]["gbs"] / hbm_peak}}
+    line = {"metric": METRIC, "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 arithmetic on 4-bit state", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "gradients": "one bf16-autocast cross-entropy backward, batch 256 per GPU of "
+                       "N(0,1) 224x224 images, uniform labels (computed once, reused every step)",
+                       "l2": "per-step working set (4-bit state 130 MB + fp32 temporaries > 2 GB) exceeds the 126 MB L2",
+                       "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in HYPER.items()}},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": grad_bytes, "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches),
+            "quant_gbs": qres["quantize"]["gbs"], "dequant_gbs": qres["dequantize"]["gbs"],
+            "roofline": roof, "loss": loss}
+    if world == 1:
+        ms, cores, sample = cpu_reference_step_ms(1, 1)
+        line["cpu_baseline"] = {"value": ms, "unit": "ms/step", "cores": cores, "kind": "port", "sample": sample}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", default=None, choices=["quant"],
+                    help="run only one small kernel case (for an ncu capture) and print its rates")
+    args = ap.parse_args()
+    if args.profile_case == "quant":
+        import torch
+        from qtensor.cextension import get_lib
+        res, nbytes, desc = quantizer_roofline(torch, get_lib(), torch.device("cuda", 0), iters=3)
+        print(json.dumps({"case": desc, "bytes_per_launch": nbytes, **res}))
+        return
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

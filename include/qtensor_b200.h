@@ -72,6 +72,10 @@ void cdequantize_blockwise_diagreal_4bit_fp32(unsigned char *A, float *code, int
 /* Library ABI version (major*100 + minor). */
 int qt_version(void);
 
+/* Number of CUDA kernels this library has launched in this process (all threads).
+ * Additive; the reference has no counterpart. */
+unsigned long long qt_launch_count(void);
+
 /* Status of the most recent call made by this thread (legacy or qt_*), and its text.
  * Replaces the reference's fprintf + exit(1) (cudaC_python/csrc/ops.cuh:20-26). */
 int qt_last_error(void);
@@ -102,6 +106,21 @@ int qt_dequantize_blockwise(const unsigned char *A, long long strideA,
                             const float *diag, long long stride_diag,
                             void *out, int out_dtype, long long stride_out,
                             int blocksize, int bits, void *stream);
+
+/*
+ * One 32-column panel step of a batched Householder QR (compact-WY form), the building
+ * block that replaces the per-matrix torch.linalg.qr of the eigenbasis refresh
+ * (reference: qtensor/utils.py:157).  For each of `count` row-major order x order
+ * matrices (A + m*strideA floats) the columns j0 .. j0+width-1 (width <= 32), rows j0 ..
+ * order-1, are factored.  Outputs, per matrix:
+ *   V + m*strideV : order x order row-major; the block rows j0.., columns j0..j0+width-1
+ *                   receives the Householder vectors (zeros above the diagonal, ones on it);
+ *   T + m*strideT : 32 x 32 row-major upper-triangular factor with H_1..H_w = I - V T V^T.
+ * A itself is only read.  Orders above about 1700 are refused with QT_ERR_UNSUPPORTED
+ * (the panel must fit in shared memory).
+ */
+int qt_householder_panel(const float *A, long long strideA, int order, int count, int j0, int width,
+                         float *V, long long strideV, float *T, long long strideT, void *stream);
 
 #ifdef __cplusplus
 }

@@ -2,6 +2,7 @@
 // The sixteen legacy symbols mirror the reference's pythonInterface.cpp:27-52; they keep
 // the void return type and record failures instead of exiting the process.
 #include "qt_common.cuh"
+#include <atomic>
 
 namespace qt {
 
@@ -10,7 +11,9 @@ static thread_local int tl_last_error = QT_OK;
 
 cudaStream_t current_stream() { return tl_stream; }
 void set_current_stream(cudaStream_t s) { tl_stream = s; }
+static std::atomic<unsigned long long> g_launches{0};
 int record(int status) { tl_last_error = status; return status; }
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 int check_launch() {
     cudaError_t e = cudaGetLastError();
     return record(e == cudaSuccess ? QT_OK : QT_ERR_LAUNCH);
@@ -56,6 +59,7 @@ void cdequantize_blockwise_diagreal_4bit_bf16(unsigned char *A, float *code, int
 void cdequantize_blockwise_diagreal_4bit_fp32(unsigned char *A, float *code, int order, float *absmax, float *diag, float *out, int blocksize) { legacy_dequantize(A, code, order, absmax, diag, out, QT_F32, blocksize, 4, true); }
 
 int qt_version(void) { return 100; }
+unsigned long long qt_launch_count(void) { return qt::g_launches.load(std::memory_order_relaxed); }
 int qt_last_error(void) { return tl_last_error; }
 const char *qt_error_string(int status) {
     switch (status) {
@@ -86,6 +90,12 @@ int qt_dequantize_blockwise(const unsigned char *A, long long strideA, const flo
     DequantArgs a{A, strideA, code, order, count, blocksize, bits, absmax, stride_absmax,
                   diag, stride_diag, out, out_dtype, stride_out};
     return launch_dequantize(a, static_cast<cudaStream_t>(stream));
+}
+
+int qt_householder_panel(const float *A, long long strideA, int order, int count, int j0, int width,
+                         float *V, long long strideV, float *T, long long strideT, void *stream) {
+    return launch_householder_panel(A, strideA, order, count, j0, width, V, strideV, T, strideT,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

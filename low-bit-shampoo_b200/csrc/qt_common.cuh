@@ -12,6 +12,7 @@ namespace qt {
 cudaStream_t current_stream();
 void set_current_stream(cudaStream_t s);
 int record(int status);          // stores status as this thread's last error and returns it
+void count_launch(int n);        // adds n to the process-wide kernel launch counter
 int check_launch();              // cudaGetLastError -> QT_OK / QT_ERR_LAUNCH (recorded)
 
 inline bool valid_blocksize(int bs) {
@@ -38,5 +39,7 @@ struct DequantArgs {
 
 int launch_quantize(const QuantArgs &a, cudaStream_t stream);
 int launch_dequantize(const DequantArgs &a, cudaStream_t stream);
+int launch_householder_panel(const float *A, long long strideA, int n, int count, int j0, int w,
+                             float *V, long long strideV, float *T, long long strideT, cudaStream_t stream);
 
 }  // namespace qt

@@ -524,6 +524,7 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
         else if (epl == 4 && lpu == 16) QT_LAUNCH_Q(4, 16);
         else QT_LAUNCH_Q(4, 32);
 #undef QT_LAUNCH_Q
+        count_launch(1);
         return;
     }
     const long long units = (long long)n * nb;
@@ -533,6 +534,7 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
     dim3 g2(grid_x_for(nbytes, a.count, 4), a.count);
     k_encode_generic<T, BITS><<<g2, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.bs, a.absmax, a.stride_absmax,
                                                      a.diag != nullptr, a.out, a.stride_out);
+    count_launch(2);
 }
 
 int launch_quantize(const QuantArgs &a, cudaStream_t s) {
@@ -581,8 +583,10 @@ static void launch_dequantize_typed(const DequantArgs &a, cudaStream_t s) {
         else
             k_dequantize_vec<T, BITS, 4><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax,
                 a.stride_absmax, a.diag, a.stride_diag, out, a.stride_out);
+        count_launch(1);
         return;
     }
+    count_launch(1);
     dim3 grid(grid_x_for((long long)n * n, a.count, 4), a.count);
     k_dequantize_generic<T, BITS><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, a.bs, a.absmax, a.stride_absmax,
                                                            a.diag, a.stride_diag, out, a.stride_out);

@@ -20,6 +20,7 @@ import torch
 
 import qtensor.functional as F
 from optimizers import matrix_functions as MF
+from optimizers._qr import householder_q
 
 _TEMP_ELEMS = 1 << 28          # cap on floats per batched temporary (1 GiB)
 
@@ -163,7 +164,7 @@ def op_ema_gram(L, G, axis, w1, w2):
 def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
     quotients diag(V^T L V) (utils.py:158)."""
-    V = torch.linalg.qr(torch.bmm(L, Vt.transpose(1, 2))).Q
+    V = householder_q(torch.bmm(L, Vt.transpose(1, 2)))
     eigs = (torch.bmm(L, V) * V).sum(dim=1)
     return V, eigs
 

@@ -20,8 +20,8 @@ LEGACY_SYMBOLS = tuple(
     for dt in ("fp32", "bf16")
 )
 EXTRA_SYMBOLS = (
-    "qt_version", "qt_last_error", "qt_error_string", "qt_set_stream",
-    "qt_quantize_blockwise", "qt_dequantize_blockwise",
+    "qt_version", "qt_launch_count", "qt_last_error", "qt_error_string", "qt_set_stream",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel",
 )
 
 _lib = None
@@ -35,6 +35,7 @@ def _declare(lib):
     vp, i32, i64 = ct.c_void_p, ct.c_int, ct.c_longlong
     lib.qt_version.restype = i32
     lib.qt_last_error.restype = i32
+    lib.qt_launch_count.restype = ct.c_ulonglong
     lib.qt_error_string.restype = ct.c_char_p
     lib.qt_error_string.argtypes = [i32]
     lib.qt_set_stream.restype = None
@@ -43,6 +44,8 @@ def _declare(lib):
     lib.qt_quantize_blockwise.argtypes = [vp, i32, i64, vp, i32, i32, vp, i64, vp, i64, vp, i64, i32, i32, vp]
     lib.qt_dequantize_blockwise.restype = i32
     lib.qt_dequantize_blockwise.argtypes = [vp, i64, vp, i32, i32, vp, i64, vp, i64, vp, i32, i64, i32, i32, vp]
+    lib.qt_householder_panel.restype = i32
+    lib.qt_householder_panel.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, i64, vp]
     for name in LEGACY_SYMBOLS:
         getattr(lib, name).restype = None
     return lib

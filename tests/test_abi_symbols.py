@@ -9,7 +9,7 @@ from conftest import ROOT
 def declared_functions():
     text = open(os.path.join(ROOT, "include", "qtensor_b200.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"\b(?:void|int|const char \*)\s*\*?\s*((?:c|qt_)\w+)\s*\(", text)
+    names = re.findall(r"\b(?:void|int|unsigned long long|const char \*)\s*\*?\s*((?:c|qt_)\w+)\s*\(", text)
     return sorted(set(names))
 
 
