@@ -122,6 +122,41 @@ int qt_dequantize_blockwise(const unsigned char *A, long long strideA,
 int qt_householder_panel(const float *A, long long strideA, int order, int count, int j0, int width,
                          float *V, long long strideV, float *T, long long strideT, void *stream);
 
+/*
+ * fp32 matrix -> two bf16 planes, hi = bf16(x), lo = bf16(x - hi): the operand format of
+ * qt_gemm_bf16x3.  X is rows x cols with ldx floats between rows, `batch` matrices strideX
+ * floats apart; the planes have ldp elements between rows (a multiple of 8) and strideP
+ * elements between matrices.  Additive; the reference multiplies fp32 tensors with
+ * torch.matmul (e.g. optimizers/shampoo2.py:188-190).
+ */
+int qt_split_bf16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                  void *hi, void *lo, long long ldp, long long strideP, void *stream);
+
+/*
+ * Batched D = alpha * A * B^T-or-B + beta * C on the tcgen05 tensor cores with fp32
+ * accumulation, operands as bf16 hi/lo planes (three MMAs per k-slice: hi*hi + hi*lo +
+ * lo*hi, about 1e-5 relative accuracy).  Replaces the torch.matmul / @ products of the
+ * reference's hot path (optimizers/shampoo2.py:188-199, :265-268; qtensor/utils.py:157-158,
+ * :196, :203; qtensor/functional.py:757, :762; optimizers/matrix_functions.py:132-135).
+ *   A is logically M x K: a_mn == 0 -> stored [M][K] (K contiguous), a_mn == 1 -> stored [K][M];
+ *   B is logically N x K: b_mn == 0 -> stored [N][K],               b_mn == 1 -> stored [K][N];
+ *   lda / ldb / strideA / strideB in bf16 elements, multiples of 8, bases 16-byte aligned;
+ *   C (optional, fp32, ldc) and D (fp32, ldd) are row-major M x N; Dhi/Dlo (optional) receive
+ *   D as bf16 planes (ldp).  At least one of D and Dhi/Dlo must be given.
+ * Device-side waits are bounded; a wait that expires sets an error word readable with
+ * qt_device_error() after synchronising.
+ */
+int qt_gemm_bf16x3(const void *Ahi, const void *Alo, long long lda, long long strideA, int a_mn,
+                   const void *Bhi, const void *Blo, long long ldb, long long strideB, int b_mn,
+                   int M, int N, int K, int batch, float alpha, float beta,
+                   const float *C, long long ldc, long long strideC,
+                   float *D, long long ldd, long long strideD,
+                   void *Dhi, void *Dlo, long long ldp, long long strideP, void *stream);
+
+/* Sticky device-side error word (QT_OK or QT_ERR_TIMEOUT); synchronises the device.
+ * clear != 0 resets it.  Additive; the reference has no device-side waits. */
+int qt_device_error(int clear);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,425 @@
+// Batched fp32-accurate matrix products on the 5th-generation tensor cores (tcgen05).
+//
+// Replaces the fp32 cuBLAS products of the reference's hot path (reference project paths
+// optimizers/shampoo2.py:188-199, :265-268; qtensor/utils.py:157-158, :196, :203;
+// qtensor/functional.py:757, :762; optimizers/matrix_functions.py:132-135).
+//
+// Precision scheme ("bf16x3"): every fp32 operand x is carried as two bf16 planes,
+// hi = bf16(x) and lo = bf16(x - hi); a product is accumulated in fp32 in tensor memory as
+// hi*hi + hi*lo + lo*hi (the lo*lo term, below 2^-16 relative, is dropped).  Three
+// tcgen05.mma.kind::f16 instructions per k-slice share one TMEM accumulator.
+//
+// Kernel structure (one 128 x 128 output tile per CTA, one CTA per SM at a time):
+//   warp 4      TMA producer: cp.async.bulk.tensor 3-D loads (batch is the third
+//               coordinate) of the four operand planes into a 3-stage shared-memory ring,
+//               128-byte swizzle, completion on mbarriers;
+//   warp 5      allocates 128 TMEM columns and issues the MMAs (one elected lane);
+//               tcgen05.commit releases ring slots and signals the epilogue;
+//   warps 0-3   epilogue: tcgen05.ld (32 lanes x 32 columns per instruction), then
+//               D = alpha * acc + beta * C in fp32, written as fp32 and/or as bf16 hi/lo
+//               planes for the next product of a chain.
+// Operands may be K-major (row = M or N index, K contiguous) or MN-major (row = K index).
+// Out-of-range rows / columns / k are zero-filled by TMA; the epilogue masks its stores.
+// Every wait is bounded: on expiry the kernel records an error word and drains.
+#include "qt_common.cuh"
+#include <cuda.h>
+
+namespace qt {
+
+static constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3;
+static constexpr int PLANE_TILE_BYTES = BM * BK * 2;                 // 16 KiB per plane tile
+static constexpr int STAGE_BYTES = 4 * PLANE_TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
+static constexpr int GEMM_THREADS = 192;
+static constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+static constexpr unsigned WAIT_LIMIT = 1u << 18;
+
+__device__ int g_gemm_error = 0;
+
+struct GemmParams {
+    int M, N, K, batch;
+    float alpha, beta;
+    const float *C; long long ldc, strideC;
+    float *D; long long ldd, strideD;
+    __nv_bfloat16 *Dhi, *Dlo; long long ldp, strideP;
+    int tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded parity wait; also gives up when another role raised the CTA's abort flag.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag) {
+    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+        unsigned ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(&g_gemm_error, QT_ERR_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap *map, unsigned bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
+              const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo,
+              const GemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *aligned = smem_raw + (base - smem_u32(smem_raw));
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(aligned + STAGES * STAGE_BYTES);
+    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
+    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 2 * STAGES + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const unsigned bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    const unsigned acc_bar = bar0 + 8u * (2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // a wait that expired in an earlier CTA (or launch) poisons the rest of the grid: drain fast
+    if (*reinterpret_cast<volatile int *>(&g_gemm_error) != 0) return;
+    int tile = blockIdx.x;
+    const int tn = tile % p.tiles_n; tile /= p.tiles_n;
+    const int tm = tile % p.tiles_m;
+    const int b = tile / p.tiles_m;
+    const int m0 = tm * BM, n0 = tn * BN;
+    const int num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_acc = *tmem_slot;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1, abort_flag)) break;
+                const unsigned stage = base + s * STAGE_BYTES;
+                mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                const int k0 = kb * BK;
+                if (!A_MN) {
+                    tma_load_3d(stage, &mapAhi, full_bar(s), k0, m0, b);
+                    tma_load_3d(stage + PLANE_TILE_BYTES, &mapAlo, full_bar(s), k0, m0, b);
+                } else {
+                    for (int h = 0; h < 2; ++h) {
+                        tma_load_3d(stage + h * (PLANE_TILE_BYTES / 2), &mapAhi, full_bar(s), m0 + 64 * h, k0, b);
+                        tma_load_3d(stage + PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapAlo, full_bar(s), m0 + 64 * h, k0, b);
+                    }
+                }
+                if (!B_MN) {
+                    tma_load_3d(stage + 2 * PLANE_TILE_BYTES, &mapBhi, full_bar(s), k0, n0, b);
+                    tma_load_3d(stage + 3 * PLANE_TILE_BYTES, &mapBlo, full_bar(s), k0, n0, b);
+                } else {
+                    for (int h = 0; h < 2; ++h) {
+                        tma_load_3d(stage + 2 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBhi, full_bar(s), n0 + 64 * h, k0, b);
+                        tma_load_3d(stage + 3 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBlo, full_bar(s), n0 + 64 * h, k0, b);
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N, M
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                   ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(full_bar(s), (kb / STAGES) & 1, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned stage = base + s * STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    // K-major: 8-row groups 1024 B apart, a 16-element k-slice is 32 B further along the row.
+                    // MN-major: 64-wide MN chunks 8192 B apart (LBO), 8-k-row groups 1024 B apart, a k-slice is 2048 B further.
+                    const unsigned a_off = A_MN ? k * 2048u : k * 32u;
+                    const unsigned b_off = B_MN ? k * 2048u : k * 32u;
+                    const unsigned a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
+                    const unsigned long long a_hi = smem_desc(stage + a_off, a_lbo, 1024u);
+                    const unsigned long long a_lo = smem_desc(stage + PLANE_TILE_BYTES + a_off, a_lbo, 1024u);
+                    const unsigned long long b_hi = smem_desc(stage + 2 * PLANE_TILE_BYTES + b_off, b_lbo, 1024u);
+                    const unsigned long long b_lo = smem_desc(stage + 3 * PLANE_TILE_BYTES + b_off, b_lbo, 1024u);
+                    umma_bf16(tmem_acc, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);
+                    umma_bf16(tmem_acc, a_hi, b_lo, idesc, 1u);
+                    umma_bf16(tmem_acc, a_hi, b_hi, idesc, 1u);
+                }
+                umma_commit(empty_bar(s));
+            }
+            umma_commit(acc_bar);
+        }
+    } else {
+        // epilogue: warp q owns TMEM lanes 32q .. 32q+31, i.e. output rows m0 + 32q + lane
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_bar, 0, abort_flag));
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = m0 + warp * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(c * 32), v);
+                const int col0 = n0 + c * 32;
+                if (row < p.M && col0 < p.N) {
+                    const int valid = min(32, p.N - col0);
+                    if (p.C && p.beta != 0.0f) {
+                        const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = (j < valid) ? fmaf(p.alpha, v[j], p.beta * crow[j]) : 0.0f;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = p.alpha * v[j];
+                    }
+                    if (p.D) {
+                        float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + col0;
+                        if (valid == 32 && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(drow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (j < valid) drow[j] = v[j];
+                        }
+                    }
+                    if (p.Dhi) {
+                        __nv_bfloat16 *hrow = p.Dhi + (long long)b * p.strideP + (long long)row * p.ldp + col0;
+                        __nv_bfloat16 *lrow = p.Dlo + (long long)b * p.strideP + (long long)row * p.ldp + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < valid) {
+                                const __nv_bfloat16 h = __float2bfloat16_rn(v[j]);
+                                hrow[j] = h;
+                                lrow[j] = __float2bfloat16_rn(v[j] - __bfloat162float(h));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+    }
+}
+
+// fp32 -> (hi, lo) bf16 planes, optionally transposing nothing: plain elementwise pass.
+__global__ void __launch_bounds__(256)
+k_split_bf16(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
+             __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, long long ldp, long long strideP) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    __nv_bfloat16 *h = hi + (long long)b * strideP, *l = lo + (long long)b * strideP;
+    const long long total = (long long)rows * cols;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / cols), c = (int)(e - (long long)r * cols);
+        const float v = x[(long long)r * ldx + c];
+        const __nv_bfloat16 vh = __float2bfloat16_rn(v);
+        h[(long long)r * ldp + c] = vh;
+        l[(long long)r * ldp + c] = __float2bfloat16_rn(v - __bfloat162float(vh));
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Host side.
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// Plane of a logical (outer x inner) bf16 matrix per batch entry, `ld` elements between rows.
+static bool make_map(CUtensorMap *map, const void *base, long long inner, long long outer, long long batch,
+                     long long ld, long long stride_batch, unsigned box_inner, unsigned box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)stride_batch * 2};
+    cuuint32_t box[3] = {box_inner, box_outer, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_split_bf16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                      void *hi, void *lo, long long ldp, long long strideP, cudaStream_t s) {
+    if (rows < 0 || cols < 0 || batch < 0 || batch > 65535) return record(QT_ERR_ARG);
+    if (rows == 0 || cols == 0 || batch == 0) return record(QT_OK);
+    if (!X || !hi || !lo || ldx < cols || ldp < cols) return record(QT_ERR_ARG);
+    long long total = (long long)rows * cols;
+    long long ctas = (total + 256 * 8 - 1) / (256 * 8);
+    if (ctas > 148 * 16) ctas = 148 * 16;
+    dim3 grid((unsigned)ctas, batch);
+    k_split_bf16<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, static_cast<__nv_bfloat16 *>(hi),
+                                       static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    count_launch(1);
+    return check_launch();
+}
+
+struct GemmArgs {
+    const void *Ahi, *Alo; long long lda, strideA; int a_mn;
+    const void *Bhi, *Blo; long long ldb, strideB; int b_mn;
+    int M, N, K, batch; float alpha, beta;
+    const float *C; long long ldc, strideC;
+    float *D; long long ldd, strideD;
+    void *Dhi, *Dlo; long long ldp, strideP;
+};
+
+static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) {
+    if (a.M < 0 || a.N < 0 || a.K < 0 || a.batch < 0) return record(QT_ERR_ARG);
+    if (a.M == 0 || a.N == 0 || a.batch == 0) return record(QT_OK);
+    if (a.K == 0) return record(QT_ERR_UNSUPPORTED);
+    if (!a.Ahi || !a.Alo || !a.Bhi || !a.Blo || (!a.D && !a.Dhi)) return record(QT_ERR_ARG);
+    if ((a.Dhi == nullptr) != (a.Dlo == nullptr)) return record(QT_ERR_ARG);
+    // TMA: 16-byte aligned bases, row pitches and batch strides
+    if (!al16(a.Ahi) || !al16(a.Alo) || !al16(a.Bhi) || !al16(a.Blo)) return record(QT_ERR_ARG);
+    if (a.lda % 8 || a.ldb % 8 || a.strideA % 8 || a.strideB % 8) return record(QT_ERR_ARG);
+    CUtensorMap mAhi, mAlo, mBhi, mBlo;
+    bool ok = true;
+    if (!a.a_mn) {       // stored [M][K]
+        ok = ok && make_map(&mAhi, a.Ahi, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);
+        ok = ok && make_map(&mAlo, a.Alo, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);
+    } else {             // stored [K][M]
+        ok = ok && make_map(&mAhi, a.Ahi, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);
+        ok = ok && make_map(&mAlo, a.Alo, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);
+    }
+    if (!a.b_mn) {       // stored [N][K]
+        ok = ok && make_map(&mBhi, a.Bhi, a.K, a.N, a.batch, a.ldb, a.strideB, BK, BN);
+        ok = ok && make_map(&mBlo, a.Blo, a.K, a.N, a.batch, a.ldb, a.strideB, BK, BN);
+    } else {             // stored [K][N]
+        ok = ok && make_map(&mBhi, a.Bhi, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);
+        ok = ok && make_map(&mBlo, a.Blo, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);
+    }
+    if (!ok) return record(QT_ERR_LAUNCH);
+    GemmParams p;
+    p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch; p.alpha = a.alpha; p.beta = a.beta;
+    p.C = a.C; p.ldc = a.ldc; p.strideC = a.strideC; p.D = a.D; p.ldd = a.ldd; p.strideD = a.strideD;
+    p.Dhi = static_cast<__nv_bfloat16 *>(a.Dhi); p.Dlo = static_cast<__nv_bfloat16 *>(a.Dlo);
+    p.ldp = a.ldp; p.strideP = a.strideP;
+    p.tiles_m = (a.M + BM - 1) / BM; p.tiles_n = (a.N + BN - 1) / BN;
+    const long long ctas = (long long)p.tiles_m * p.tiles_n * a.batch;
+    if (ctas > 0x7fffffffLL) return record(QT_ERR_UNSUPPORTED);
+    static bool attr_done = false;
+    if (!attr_done) {
+        bool good = cudaFuncSetAttribute(k_gemm_bf16x3<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
+        good = good && cudaFuncSetAttribute(k_gemm_bf16x3<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
+        good = good && cudaFuncSetAttribute(k_gemm_bf16x3<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
+        good = good && cudaFuncSetAttribute(k_gemm_bf16x3<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
+        if (!good) return record(QT_ERR_LAUNCH);
+        attr_done = true;
+    }
+    const unsigned grid = (unsigned)ctas;
+    if (!a.a_mn && !a.b_mn) k_gemm_bf16x3<false, false><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
+    else if (!a.a_mn && a.b_mn) k_gemm_bf16x3<false, true><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
+    else if (a.a_mn && !a.b_mn) k_gemm_bf16x3<true, false><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
+    else k_gemm_bf16x3<true, true><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
+    count_launch(1);
+    return check_launch();
+}
+
+int read_gemm_error(bool clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return QT_ERR_LAUNCH;
+    if (clear && v != 0) {
+        int z = 0;
+        cudaMemcpyToSymbol(g_gemm_error, &z, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace qt
+
+using namespace qt;
+
+extern "C" {
+
+int qt_split_bf16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                  void *hi, void *lo, long long ldp, long long strideP, void *stream) {
+    return launch_split_bf16(X, ldx, strideX, rows, cols, batch, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
+}
+
+int qt_gemm_bf16x3(const void *Ahi, const void *Alo, long long lda, long long strideA, int a_mn,
+                   const void *Bhi, const void *Blo, long long ldb, long long strideB, int b_mn,
+                   int M, int N, int K, int batch, float alpha, float beta,
+                   const float *C, long long ldc, long long strideC,
+                   float *D, long long ldd, long long strideD,
+                   void *Dhi, void *Dlo, long long ldp, long long strideP, void *stream) {
+    GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, M, N, K, batch, alpha, beta,
+               C, ldc, strideC, D, ldd, strideD, Dhi, Dlo, ldp, strideP};
+    return launch_gemm_bf16x3(a, static_cast<cudaStream_t>(stream));
+}
+
+int qt_device_error(int clear) { return read_gemm_error(clear != 0); }
+
+}  // extern "C"

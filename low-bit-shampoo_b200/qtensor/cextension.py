@@ -21,7 +21,7 @@ LEGACY_SYMBOLS = tuple(
 )
 EXTRA_SYMBOLS = (
     "qt_version", "qt_launch_count", "qt_last_error", "qt_error_string", "qt_set_stream",
-    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel", "qt_split_bf16", "qt_gemm_bf16x3", "qt_device_error",
 )
 
 _lib = None
@@ -46,6 +46,14 @@ def _declare(lib):
     lib.qt_dequantize_blockwise.argtypes = [vp, i64, vp, i32, i32, vp, i64, vp, i64, vp, i32, i64, i32, i32, vp]
     lib.qt_householder_panel.restype = i32
     lib.qt_householder_panel.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, i64, vp]
+    f32 = ct.c_float
+    lib.qt_split_bf16.restype = i32
+    lib.qt_split_bf16.argtypes = [vp, i64, i64, i32, i32, i32, vp, vp, i64, i64, vp]
+    lib.qt_gemm_bf16x3.restype = i32
+    lib.qt_gemm_bf16x3.argtypes = [vp, vp, i64, i64, i32, vp, vp, i64, i64, i32, i32, i32, i32, i32, f32, f32,
+                                   vp, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp]
+    lib.qt_device_error.restype = i32
+    lib.qt_device_error.argtypes = [i32]
     for name in LEGACY_SYMBOLS:
         getattr(lib, name).restype = None
     return lib
