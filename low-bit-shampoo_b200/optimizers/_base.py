@@ -174,7 +174,8 @@ class Preconditioner:
     def add_statistics(self, grad):
         if not self.statistics:
             return
-        E.add_statistics(self.statistics_items(grad), *self._weights(), eps=self.matrix_eps)
+        E.add_statistics(self.statistics_items(grad), *self._weights(), eps=self.matrix_eps,
+                         exact=(self.inv_root_mode != 0))
 
     def compute_preconditioners(self):
         if self.statistics:
@@ -263,7 +264,7 @@ class _ShampooBase(optim.Optimizer):
             if state['step'] % t1 == 0 and pre.statistics:
                 stat_items += pre.statistics_items(p.grad.data)
         if stat_items:
-            E.add_statistics(stat_items, w1, w2, eps=group['matrix_eps'])
+            E.add_statistics(stat_items, w1, w2, eps=group['matrix_eps'], exact=(group.get('inv_root_mode', 0) != 0))
         for p in params:
             state = self.state[p]
             pre = state['preconditioner']

@@ -21,6 +21,7 @@ import torch
 import qtensor.functional as F
 from optimizers import matrix_functions as MF
 from optimizers._qr import householder_q
+from optimizers import _gemm
 
 _TEMP_ELEMS = 1 << 28          # cap on floats per batched temporary (1 GiB)
 
@@ -142,36 +143,104 @@ class OrderClass:
 
 # ---------------------------------------------------------------------------------------
 # The dense products of the hot path, one named operation each.
+#
+# On CUDA they run on the library's tcgen05 kernel (optimizers/_gemm.py): operands are
+# carried as bf16 hi/lo planes, a product chain hands planes from one epilogue to the next
+# prologue, and transposes are operand-major flags, not copies.  On CPU tensors (32-bit
+# state, used by the host-logic tests) the same operations are plain torch products.
 # ---------------------------------------------------------------------------------------
+USE_TENSOR_CORES = True
+# Set while an order class with plain 16/32-bit state, or a Schur-Newton inverse root, is
+# processed: those paths have no quantisation noise to hide the ~1e-5 relative error of the
+# split-bf16 products (and the Newton iteration amplifies it), so they stay on fp32 products.
+_EXACT = False
 
-def op_bjorck(V):
+
+class _exact:
+    def __init__(self, on):
+        self.on = on
+
+    def __enter__(self):
+        global _EXACT
+        self.prev, _EXACT = _EXACT, (_EXACT or self.on)
+
+    def __exit__(self, *exc):
+        global _EXACT
+        _EXACT = self.prev
+
+
+class Mat:
+    """A batch of matrices available as an fp32 tensor, as bf16 hi/lo planes, or both."""
+
+    def __init__(self, f32=None, planes=None):
+        self.f32, self._planes = f32, planes
+
+    @property
+    def planes(self):
+        if self._planes is None:
+            x = self.f32 if self.f32.stride(2) == 1 else self.f32.contiguous()
+            self._planes = _gemm.split(x)
+        return self._planes
+
+
+def _tc(t):
+    return USE_TENSOR_CORES and not _EXACT and t.is_cuda and F.lib is not None
+
+
+def mm(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, want_float=True, want_planes=False,
+       exact=False):
+    """alpha * op(A) @ op(B) + beta * C over a batch; A, B are Mat, C an fp32 tensor.
+    `exact` forces an fp32 product (operands must then be available as fp32)."""
+    ref = A.f32 if A.f32 is not None else A._planes.hi
+    if _tc(ref) and not exact:
+        D, P = _gemm.matmul(A.planes, B.planes, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C,
+                            want_float=want_float, want_planes=want_planes)
+        return Mat(D, P)
+    a = A.f32.transpose(1, 2) if trans_a else A.f32
+    b = B.f32.transpose(1, 2) if trans_b else B.f32
+    if C is not None and beta != 0.0:
+        return Mat(torch.baddbmm(C, a, b, beta=beta, alpha=alpha))
+    out = torch.bmm(a, b)
+    return Mat(out if alpha == 1.0 else out * alpha)
+
+
+def op_bjorck(V, want_planes=False):
     """1.5 V - 0.5 (V V^T) V on the rows of each V in the batch (utils.py:196, functional.py:757)."""
-    return torch.baddbmm(V, torch.bmm(V, V.transpose(1, 2)), V, beta=1.5, alpha=-0.5)
+    W = mm(V, V, trans_b=True, want_float=not _tc(V.f32), want_planes=_tc(V.f32))
+    return mm(W, V, alpha=-0.5, beta=1.5, C=V.f32, want_planes=want_planes and _tc(V.f32))
 
 
-def op_scaled_gram(rows, weights):
+def op_scaled_gram(rows, weights, want_planes=False):
     """rows^T diag(weights) rows (utils.py:203, functional.py:762)."""
-    return torch.bmm(rows.transpose(1, 2), weights.unsqueeze(2) * rows)
+    scaled = Mat(weights.unsqueeze(2) * rows.f32)
+    return mm(rows, scaled, trans_a=True, want_planes=want_planes and _tc(rows.f32))
 
 
 def op_ema_gram(L, G, axis, w1, w2):
-    """w1 L + w2 G G^T (axis 0) or w1 L + w2 G^T G (axis 1) (shampoo2.py:185-199)."""
+    """w1 L + w2 G G^T (axis 0) or w1 L + w2 G^T G (axis 1) (shampoo2.py:185-199); L fp32 tensor.
+
+    Kept in fp32: the statistic's small eigenvalues (the half of the spectrum that is kept,
+    regularised by only matrix_eps * lambda_max) must be accurate to ~1e-7 * lambda_max, which
+    the split-bf16 products (1e-5) do not deliver."""
+    Gm = Mat(G)
     if axis == 0:
-        return torch.baddbmm(L, G, G.transpose(1, 2), beta=w1, alpha=w2)
-    return torch.baddbmm(L, G.transpose(1, 2), G, beta=w1, alpha=w2)
+        return mm(Gm, Gm, trans_b=True, alpha=w2, beta=w1, C=L, exact=True).f32
+    return mm(Gm, Gm, trans_a=True, alpha=w2, beta=w1, C=L, exact=True).f32
 
 
 def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
-    quotients diag(V^T L V) (utils.py:158)."""
-    V = householder_q(torch.bmm(L, Vt.transpose(1, 2)))
-    eigs = (torch.bmm(L, V) * V).sum(dim=1)
+    quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
+    V = householder_q(mm(L, Vt, trans_b=True).f32)
+    LV = mm(L, Mat(V), exact=True).f32          # Rayleigh quotients need fp32 (see op_ema_gram)
+    eigs = (LV * V).sum(dim=1)
     return V, eigs
 
 
 def op_apply(P0, G, P1):
-    """P0 G P1 (shampoo2.py:265-268)."""
-    return torch.bmm(torch.bmm(P0, G), P1)
+    """P0 G P1 (shampoo2.py:265-268); fp32 tensors in and out."""
+    T = mm(Mat(P0), Mat(G), want_float=not _tc(G), want_planes=_tc(G))
+    return mm(T, Mat(P1)).f32
 
 
 def _runs(indices):
@@ -213,14 +282,19 @@ def _ema_update(L, grads_axes, w1, w2):
     return L
 
 
-def add_statistics(items, w1, w2, eps=1e-6):
-    """items: list of (OrderClass, slot, grad_block, axis).  Refreshes the statistics."""
+def add_statistics(items, w1, w2, eps=1e-6, exact=False):
+    """items: list of (OrderClass, slot, grad_block, axis).  Refreshes the statistics.
+    `exact` keeps every product in fp32 (used when the inverse root is the Schur-Newton
+    iteration, which amplifies operand rounding)."""
     by_class = defaultdict(list)
     for cls, slot, g, axis in items:
         by_class[cls].append((slot, g, axis))
     for cls, entries in by_class.items():
         runs = _runs([e[0] for e in entries])
         for a, b, pos in _split_runs(runs, cls.sub_batch()):
+          # the dense flavour re-quantises L itself and then runs the Newton iteration on it:
+          # a 1e-5 operand error flips a few 4-bit codes and the iteration amplifies them
+          with _exact(exact or not cls.stat.lowbit or cls.flavour == "s1"):
             ga = [(entries[p][1], entries[p][2]) for p in pos]
             if cls.flavour == "s1":
                 if REFERENCE_DIAGREAL_NONE and cls.stat.lowbit:
@@ -229,14 +303,14 @@ def add_statistics(items, w1, w2, eps=1e-6):
                     L = cls.stat.dequantize(a, b)
                 cls.stat.quantize(a, b, _ema_update(L, ga, w1, w2))
                 continue
-            Vt = cls.stat.dequantize(a, b)
+            Vt = Mat(cls.stat.dequantize(a, b))
             if cls.stat.lowbit:
                 for _ in range(cls.rect_t1):
-                    Vt = op_bjorck(Vt)
-            rows = _gather_rows(Vt, cls.keep_idx[a:b])
-            L = op_scaled_gram(rows, cls.S[a:b])
+                    Vt = op_bjorck(Vt, want_planes=True)
+            rows = Mat(_gather_rows(Vt.f32, cls.keep_idx[a:b]))
+            L = op_scaled_gram(rows, cls.S[a:b]).f32
             L = _ema_update(L, ga, w1, w2)
-            V, eigs = op_subspace_step(L, Vt)
+            V, eigs = op_subspace_step(Mat(L), Vt)
             vals, idx = torch.sort(eigs, dim=1)
             cls.keep_idx[a:b] = idx[:, : cls.keep]
             cls.S[a:b] = vals[:, : cls.keep]
@@ -251,6 +325,7 @@ def compute_preconditioners(items, eps, inv_root_mode, exponent=4):
         by_class[cls].append(slot)
     for cls, slots in by_class.items():
         for a, b, _ in _split_runs(_runs(slots), cls.sub_batch()):
+          with _exact((not cls.stat.lowbit) or cls.flavour == "s1" or inv_root_mode != 0):
             if cls.flavour == "s1":
                 if REFERENCE_DIAGREAL_NONE and cls.stat.lowbit:
                     L = _eps_identity(cls, b - a, eps)
@@ -259,20 +334,20 @@ def compute_preconditioners(items, eps, inv_root_mode, exponent=4):
                 P = MF.ComputePower(L, exponent, ridge_epsilon=eps)
             elif inv_root_mode == 0:
                 Vt = cls.stat.dequantize(a, b)
-                rows = _gather_rows(Vt, cls.keep_idx[a:b])
+                rows = Mat(_gather_rows(Vt, cls.keep_idx[a:b]))
                 if cls.stat.lowbit:
                     for _ in range(cls.rect_t2):
-                        rows = op_bjorck(rows)
+                        rows = op_bjorck(rows, want_planes=True)
                 rho = eps * cls.max_eig[a:b]
                 weights = 1 / (cls.S[a:b] + rho.unsqueeze(1)).pow(1 / exponent)
-                P = op_scaled_gram(rows, weights)
+                P = op_scaled_gram(rows, weights).f32
             else:
-                Vt = cls.stat.dequantize(a, b)
+                Vt = Mat(cls.stat.dequantize(a, b))
                 if cls.stat.lowbit:
                     for _ in range(cls.rect_t1):
                         Vt = op_bjorck(Vt)
-                rows = _gather_rows(Vt, cls.keep_idx[a:b])
-                P = MF.ComputePower(op_scaled_gram(rows, cls.S[a:b]), exponent, ridge_epsilon=eps)
+                rows = Mat(_gather_rows(Vt.f32, cls.keep_idx[a:b]))
+                P = MF.ComputePower(op_scaled_gram(rows, cls.S[a:b]).f32, exponent, ridge_epsilon=eps)
             cls.prec.quantize(a, b, P)
 
 
@@ -303,7 +378,9 @@ def preconditioned_blocks(items):
             G = torch.stack([items[k][4] for k in part])
             P0 = torch.stack([cache[(items[k][0], items[k][1])] for k in part]).to(dt)
             P1 = torch.stack([cache[(items[k][2], items[k][3])] for k in part]).to(dt)
-            R = op_apply(P0, G, P1)
+            lowbit = items[part[0]][0].prec.lowbit and items[part[0]][2].prec.lowbit and dt == torch.float32
+            with _exact(not lowbit):
+                R = op_apply(P0, G, P1)
             for j, k in enumerate(part):
                 out[k] = R[j]
     return out

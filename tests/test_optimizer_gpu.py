@@ -68,3 +68,25 @@ def test_state_objects_are_arena_views(native_lib):
     # per-parameter API (reference style) runs on the same state
     out = pre.preconditioned_grad(ps[0].grad)
     assert out.shape == ps[0].shape and torch.isfinite(out).all()
+
+
+def test_rank_deficient_statistics_stay_finite(native_lib):
+    """Non-square blocks give rank-deficient statistics whose small Rayleigh quotients must
+    stay accurate relative to the ridge matrix_eps * lambda_max; no NaN may appear."""
+    from optimizers.shampoo2 import ShampooAdamW
+    torch.manual_seed(3)
+    ps = [torch.nn.Parameter(torch.randn(1200, 320, device="cuda") * 0.02),
+          torch.nn.Parameter(torch.randn(256, 768, device="cuda") * 0.02)]
+    opt = ShampooAdamW(ps, prec_bits=4, stat_compute_steps=1, prec_compute_steps=1)
+    for step in range(3):
+        for p in ps:
+            p.grad = torch.randn_like(p) * 0.01
+        opt.step()
+        for p in ps:
+            assert torch.isfinite(p).all()
+    for p in ps:
+        pre = opt.state[p]["preconditioner"]
+        for q in pre.preconditioners:
+            assert torch.isfinite(q.dequantize()).all()
+        for s in pre.statistics:
+            assert torch.isfinite(s.Svalue).all() and float(s.Svalue.min()) > -1e-6 * float(s.max_eigenvalue)
