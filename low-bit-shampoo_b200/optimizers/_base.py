@@ -191,6 +191,24 @@ class Preconditioner:
         return self._active
 
 
+class RemotePreconditioner:
+    """Stand-in on the ranks that do not own a parameter's preconditioner state: it follows the
+    activation schedule so every rank agrees on when the owner ships a direction."""
+
+    def __init__(self, owner):
+        self.owner = owner
+        self.statistics = []
+        self.preconditioners = []
+        self._slots = []
+        self._active = False
+
+    def is_active(self):
+        return self._active
+
+    def set_device(self, device):
+        pass
+
+
 def _make_codebooks(prec_bits):
     name2qmap = {}
     if prec_bits in (4, 8):
@@ -207,8 +225,15 @@ class _ShampooBase(optim.Optimizer):
 
     preconditioner_cls = Preconditioner
 
-    def _setup(self, prec_bits):
+    def _setup(self, prec_bits, process_group=None):
         self.name2qmap = _make_codebooks(prec_bits)
+        self._pg = process_group
+        self._world, self._rank = 1, 0
+        self._plans = {}
+        if process_group is not None:
+            import torch.distributed as dist
+            self._world = dist.get_world_size(process_group)
+            self._rank = dist.get_rank(process_group)
 
     def load_state_dict(self, state_dict):
         super().load_state_dict(state_dict)
@@ -224,8 +249,14 @@ class _ShampooBase(optim.Optimizer):
         if not new:
             return
         flavour = self.preconditioner_cls.flavour
+        owners = [self._rank if preconditioner_orders(p.shape, group['prec_maxorder']) else -1 for p in new]
+        if self._world > 1:
+            from optimizers._sharding import assign_owners
+            owners, _ = assign_owners([tuple(p.shape) for p in new], self._world, group['prec_maxorder'])
         counts = defaultdict(int)
-        for p in new:
+        for p, owner in zip(new, owners):
+            if owner not in (-1, self._rank):
+                continue
             for n in preconditioner_orders(p.shape, group['prec_maxorder']):
                 counts[(p.device, n)] += 1
         bits = group['prec_bits']
@@ -238,9 +269,14 @@ class _ShampooBase(optim.Optimizer):
             classes.setdefault(device, {})[n] = E.OrderClass(
                 n, c, device, flavour, bits, group['quan_blocksize'], code, group['min_lowbit_size'],
                 group.get('rect_t1', 1), group.get('rect_t2', 4))
-        for p in new:
+        for p, owner in zip(new, owners):
             state = self.state[p]
             state['step'] = 0
+            state['owner'] = owner
+            if owner not in (-1, self._rank):
+                state['preconditioner'] = RemotePreconditioner(owner)
+                self._init_moments(p, state)
+                continue
             state['preconditioner'] = self.preconditioner_cls(
                 p, self.name2qmap,
                 stat_decay=group['stat_decay'], matrix_eps=group['matrix_eps'], prec_maxorder=group['prec_maxorder'],
@@ -292,14 +328,35 @@ class _ShampooBase(optim.Optimizer):
                 directions[k] = pre.merge(blocks[a:b])
             # grafting: rescale the direction to the gradient's norm (shampoo2.py:453).  For
             # parameters without preconditioners the direction IS the gradient, scaled in place.
-            ks = [k for k, _, _ in apply_list]
+            ks = [k for k, _, pre in apply_list if not isinstance(pre, RemotePreconditioner)]
             dirs = [directions[k] for k in ks]
-            gn = torch._foreach_norm([params[k].grad.data for k in ks])
-            dn = torch._foreach_norm(dirs)
-            torch._foreach_add_(dn, 1e-12)
-            torch._foreach_div_(gn, dn)
-            torch._foreach_mul_(dirs, gn)
+            if ks:
+                gn = torch._foreach_norm([params[k].grad.data for k in ks])
+                dn = torch._foreach_norm(dirs)
+                torch._foreach_add_(dn, 1e-12)
+                torch._foreach_div_(gn, dn)
+                torch._foreach_mul_(dirs, gn)
+            if self._world > 1:
+                self._exchange(params, directions, apply_list)
         return directions
+
+    def _exchange(self, params, directions, apply_list):
+        """All-gather of the owners' preconditioned, grafted directions (one collective)."""
+        from optimizers._sharding import GatherPlan
+        shipped = [(k, p) for k, p, pre in apply_list if self.state[p]['owner'] >= 0]
+        if not shipped:
+            return
+        sig = tuple(k for k, _ in shipped)
+        plan = self._plans.get((id(params[0]), sig))
+        if plan is None:
+            plan = GatherPlan([(k, p.numel(), self.state[p]['owner']) for k, p in shipped], self._world)
+            self._plans[(id(params[0]), sig)] = plan
+        local = {k: directions[k] for k, p in shipped if self.state[p]['owner'] == self._rank}
+        ref = params[shipped[0][0]]
+        got = plan.exchange(local, self._rank, self._pg, ref.device, torch.float32)
+        for k, p in shipped:
+            if self.state[p]['owner'] != self._rank:
+                directions[k] = got[k].view(p.shape).to(p.grad.dtype)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -318,14 +375,14 @@ class ShampooSGDBase(_ShampooBase):
     def __init__(self, params, lr=0.1, momentum=0.9, weight_decay=0.0, nesterov=False,
                  start_prec_step=1, stat_compute_steps=100, prec_compute_steps=500,
                  stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200,
-                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, **extra):
+                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, process_group=None, **extra):
         defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay, nesterov=nesterov,
                         start_prec_step=start_prec_step, stat_compute_steps=stat_compute_steps,
                         prec_compute_steps=prec_compute_steps, stat_decay=stat_decay, matrix_eps=matrix_eps,
                         prec_maxorder=prec_maxorder, prec_bits=prec_bits, min_lowbit_size=min_lowbit_size,
                         quan_blocksize=quan_blocksize, **extra)
         super().__init__(params, defaults)
-        self._setup(prec_bits)
+        self._setup(prec_bits, process_group)
 
     def _init_moments(self, p, state):
         state['momentum'] = torch.zeros_like(p, memory_format=torch.preserve_format)
@@ -346,14 +403,14 @@ class ShampooAdamWBase(_ShampooBase):
     def __init__(self, params, lr=0.001, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
                  start_prec_step=1, stat_compute_steps=100, prec_compute_steps=500,
                  stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200,
-                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, **extra):
+                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, process_group=None, **extra):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                         start_prec_step=start_prec_step, stat_compute_steps=stat_compute_steps,
                         prec_compute_steps=prec_compute_steps, stat_decay=stat_decay, matrix_eps=matrix_eps,
                         prec_maxorder=prec_maxorder, prec_bits=prec_bits, min_lowbit_size=min_lowbit_size,
                         quan_blocksize=quan_blocksize, **extra)
         super().__init__(params, defaults)
-        self._setup(prec_bits)
+        self._setup(prec_bits, process_group)
 
     def _init_moments(self, p, state):
         state['exp_avg'] = torch.zeros_like(p, memory_format=torch.preserve_format)

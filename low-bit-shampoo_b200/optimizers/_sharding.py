@@ -1,0 +1,68 @@
+"""Sharding of the preconditioner work across the GPUs of one node.
+
+The reference is single-device.  Here every parameter that has preconditioner matrices is
+owned by one rank (cost-balanced, longest-processing-time-first on a cost model of its
+blocks); only the owner holds that parameter's quantized state and runs the statistics
+refresh, the inverse root and the preconditioning products.  After the owners have produced
+their (norm-grafted) preconditioned gradients, one all-gather over a flat, rank-major fp32
+buffer gives every rank every direction, and the AdamW / SGD tail runs replicated.
+No other collective is used; gradients are assumed to be already averaged (data parallel).
+"""
+import torch
+
+from optimizers._base_shapes import block_shapes
+
+
+def param_cost(shape, prec_maxorder):
+    """Relative cost of one firing step for a parameter: sum n^3 over its preconditioner orders
+    (refresh + inverse root, ~17 n^3 flops each) plus the two apply products per block."""
+    cost = 0.0
+    for m, k in block_shapes(shape, prec_maxorder):
+        cost += 17.0 * (m ** 3 + k ** 3) + 2.0 * (m * m * k + m * k * k)
+    return cost
+
+
+def assign_owners(shapes, world_size, prec_maxorder):
+    """Owner rank per parameter (-1 for parameters without preconditioner matrices).
+
+    Deterministic: ties are broken by parameter position, so every rank computes the same map.
+    """
+    costs = [param_cost(s, prec_maxorder) for s in shapes]
+    owners = [-1] * len(shapes)
+    load = [0.0] * world_size
+    for i in sorted(range(len(shapes)), key=lambda i: (-costs[i], i)):
+        if costs[i] == 0.0:
+            continue
+        r = min(range(world_size), key=lambda r: (load[r], r))
+        owners[i] = r
+        load[r] += costs[i]
+    return owners, load
+
+
+class GatherPlan:
+    """Layout of the flat all-gather buffer: for rank r the directions of the parameters it
+    owns, back to back, every rank's slot padded to the largest one."""
+
+    def __init__(self, entries, world_size):
+        # entries: list of (key, numel, owner) in a fixed order shared by all ranks
+        self.world = world_size
+        fill = [0] * world_size
+        self.offset = {}
+        for key, numel, owner in entries:
+            self.offset[key] = (owner, fill[owner], numel)
+            fill[owner] += numel
+        self.slot = max(1, max(fill))
+        self.fill = fill
+
+    def exchange(self, local, rank, group, device, dtype):
+        """local: {key: tensor} for the keys this rank owns.  Returns {key: flat view} for all keys."""
+        import torch.distributed as dist
+        send = torch.zeros(self.slot, dtype=dtype, device=device)
+        for key, t in local.items():
+            owner, off, numel = self.offset[key]
+            assert owner == rank
+            send[off: off + numel].copy_(t.reshape(-1))
+        recv = torch.empty(self.world * self.slot, dtype=dtype, device=device)
+        dist.all_gather_into_tensor(recv, send, group=group)
+        recv = recv.view(self.world, self.slot)
+        return {key: recv[owner, off: off + numel] for key, (owner, off, numel) in self.offset.items()}
