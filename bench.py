@@ -198,6 +198,29 @@ def quantizer_roofline(torch, lib, device, iters=20):
     return res, bytes_per_launch, f"{count} matrices of order {n}, 4-bit diagreal, block {bs}"
 
 
+def gemm_roofline(torch, device, iters=20):
+    """tcgen05 product on the step's most common shape: 125 matrices of order 768 (V V^T)."""
+    from optimizers import _gemm
+    n, count = 768, 125
+    A = torch.randn(count, n, n, device=device)
+    P = _gemm.split(A)
+    out = torch.empty(count, n, n, device=device)
+    fn = lambda: _gemm.matmul(P, P, trans_b=True, out=out)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    flops = 2.0 * count * n ** 3
+    return {"us_per_launch": ms * 1e3, "tflops_algorithmic": flops / ms / 1e9, "tflops_executed": 3 * flops / ms / 1e9,
+            "flops_per_launch": flops, "case": f"{count} x ({n} x {n}) @ ({n} x {n})^T, bf16 hi/lo planes in, fp32 out"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -279,10 +302,20 @@ def run_ours(args):
 
     hbm_peak, tf_peak, peak_kind = measured_peaks()
     qres, qbytes, qdesc = quantizer_roofline(torch, lib, device)
-    roof = {"bound": "hbm", "kernel": "k_quantize_vec (4-bit diagreal, block 64)", "achieved": qres["quantize"]["gbs"],
-            "peak": hbm_peak, "unit": "GB/s", "frac": qres["quantize"]["gbs"] / hbm_peak, "peak_kind": f"of {peak_kind}",
-            "traffic": None, "bytes_per_launch": qbytes, "case": qdesc,
-            "dequantize": {"achieved": qres["dequantize"]["gbs"], "frac": qres["dequantize"]["gbs"] / hbm_peak}}
+    gres = gemm_roofline(torch, device)
+    # dominant kernel of the step: the tcgen05 product.  `achieved` counts algorithmic flops
+    # (2 M N K per product); the kernel executes three bf16 MMAs per product (hi*hi + hi*lo +
+    # lo*hi), so the tensor pipe runs at 3x that rate (`executed`).
+    roof = {"bound": "tensor", "kernel": "k_gemm_bf16x3 (tcgen05 kind::f16, bf16 x3 split, fp32 accumulate in TMEM)",
+            "achieved": gres["tflops_algorithmic"], "peak": tf_peak, "unit": "TFLOP/s",
+            "frac": gres["tflops_algorithmic"] / tf_peak, "peak_kind": f"of {peak_kind} (sustained bf16)",
+            "executed": gres["tflops_executed"], "frac_executed": gres["tflops_executed"] / tf_peak,
+            "emulation_factor": 3, "traffic": None, "flops_per_launch": gres["flops_per_launch"], "case": gres["case"],
+            "us_per_launch": gres["us_per_launch"],
+            "quantize": {"bound": "hbm", "achieved": qres["quantize"]["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                         "frac": qres["quantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc},
+            "dequantize": {"bound": "hbm", "achieved": qres["dequantize"]["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                           "frac": qres["dequantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc}}
     line = {"metric": METRIC, "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 arithmetic on 4-bit state", "data": "synthetic",
@@ -309,7 +342,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", default=None, choices=["quant"],
+    ap.add_argument("--profile-case", default=None, choices=["quant", "gemm"],
                     help="run only one small kernel case (for an ncu capture) and print its rates")
     args = ap.parse_args()
     if args.profile_case == "quant":
@@ -317,6 +350,12 @@ def main():
         from qtensor.cextension import get_lib
         res, nbytes, desc = quantizer_roofline(torch, get_lib(), torch.device("cuda", 0), iters=3)
         print(json.dumps({"case": desc, "bytes_per_launch": nbytes, **res}))
+        return
+    if args.profile_case == "gemm":
+        import torch
+        from qtensor.cextension import get_lib
+        get_lib()
+        print(json.dumps(gemm_roofline(torch, torch.device("cuda", 0), iters=3)))
         return
     if args.impl == "reference":
         run_reference(args)
