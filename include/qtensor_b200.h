@@ -108,6 +108,15 @@ int qt_dequantize_blockwise(const unsigned char *A, long long strideA,
                             int blocksize, int bits, void *stream);
 
 /*
+ * Self-test of the quantizer's division: the kernels replace x / absmax by an exact
+ * reciprocal plus two fused corrections; this entry point compares that sequence with the
+ * IEEE division on `pairs` pseudo-random operand pairs (seeded) and ADDS the number of
+ * bitwise mismatches to *mismatches (device pointer, caller-initialised).  Expected: 0.
+ * Additive; the reference divides directly (qtensor/functional.py:604).
+ */
+int qt_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches, void *stream);
+
+/*
  * One 32-column panel step of a batched Householder QR (compact-WY form), the building
  * block that replaces the per-matrix torch.linalg.qr of the eigenbasis refresh
  * (reference: qtensor/utils.py:157).  For each of `count` row-major order x order

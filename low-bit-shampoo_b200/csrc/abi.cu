@@ -92,6 +92,10 @@ int qt_dequantize_blockwise(const unsigned char *A, long long strideA, const flo
     return launch_dequantize(a, static_cast<cudaStream_t>(stream));
 }
 
+int qt_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches, void *stream) {
+    return launch_selftest_division(seed, pairs, mismatches, static_cast<cudaStream_t>(stream));
+}
+
 int qt_householder_panel(const float *A, long long strideA, int order, int count, int j0, int width,
                          float *V, long long strideV, float *T, long long strideT, void *stream) {
     return launch_householder_panel(A, strideA, order, count, j0, width, V, strideV, T, strideT,

@@ -9,11 +9,12 @@
 // hi*hi + hi*lo + lo*hi (the lo*lo term, below 2^-16 relative, is dropped).  Three
 // tcgen05.mma.kind::f16 instructions per k-slice share one TMEM accumulator.
 //
-// Kernel structure (one 128 x 128 output tile per CTA, one CTA per SM at a time):
+// Kernel structure (persistent: one CTA per SM walks over 128 x 128 output tiles; two TMEM
+// accumulators so the epilogue of tile i overlaps the main loop of tile i+1):
 //   warp 4      TMA producer: cp.async.bulk.tensor 3-D loads (batch is the third
 //               coordinate) of the four operand planes into a 3-stage shared-memory ring,
 //               128-byte swizzle, completion on mbarriers;
-//   warp 5      allocates 128 TMEM columns and issues the MMAs (one elected lane);
+//   warp 5      allocates 256 TMEM columns and issues the MMAs (one elected lane);
 //               tcgen05.commit releases ring slots and signals the epilogue;
 //   warps 0-3   epilogue: tcgen05.ld (32 lanes x 32 columns per instruction), then
 //               D = alpha * acc + beta * C in fp32, written as fp32 and/or as bf16 hi/lo
@@ -31,6 +32,7 @@ static constexpr int PLANE_TILE_BYTES = BM * BK * 2;                 // 16 KiB p
 static constexpr int STAGE_BYTES = 4 * PLANE_TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
 static constexpr int GEMM_THREADS = 192;
 static constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+static int g_gemm_sms = 0;
 static constexpr unsigned WAIT_LIMIT = 1u << 18;
 
 __device__ int g_gemm_error = 0;
@@ -64,6 +66,25 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     *abort_flag = 1;
     atomicExch(&g_gemm_error, QT_ERR_TIMEOUT);
     return false;
+}
+// Warp-collective wait: lane 0 polls with a short sleep between polls (the other 31 lanes and
+// the other warps' issue slots stay free for the MMA and TMA threads), result broadcast.
+__device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity, volatile int *abort_flag) {
+    unsigned ok = 0;
+    if ((threadIdx.x & 31) == 0) {
+        for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+            asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok) break;
+            if ((it & 255u) == 255u && *abort_flag) break;
+            __nanosleep(40);
+        }
+        if (!ok && !*abort_flag) {
+            *abort_flag = 1;
+            atomicExch(&g_gemm_error, QT_ERR_TIMEOUT);
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap *map, unsigned bar, int x, int y, int z) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -113,150 +134,220 @@ k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant_
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *aligned = smem_raw + (base - smem_u32(smem_raw));
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(aligned + STAGES * STAGE_BYTES);
-    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
-    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 2 * STAGES + 1);
+    // bars[0..S): full, [S..2S): empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
+    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const unsigned bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-    const unsigned acc_bar = bar0 + 8u * (2 * STAGES);
+    auto acc_full = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // a wait that expired in an earlier CTA (or launch) poisons the rest of the grid: drain fast
     if (*reinterpret_cast<volatile int *>(&g_gemm_error) != 0) return;
-    int tile = blockIdx.x;
-    const int tn = tile % p.tiles_n; tile /= p.tiles_n;
-    const int tm = tile % p.tiles_m;
-    const int b = tile / p.tiles_m;
-    const int m0 = tm * BM, n0 = tn * BN;
     const int num_kb = (p.K + BK - 1) / BK;
+    const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(acc_bar, 1);
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const unsigned tmem_acc = *tmem_slot;
+    const unsigned tmem_base = *tmem_slot;
 
     if (warp == 4) {
+        // ---------------- TMA producer: one ring of stages shared by all tiles of this CTA
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1, abort_flag)) break;
-                const unsigned stage = base + s * STAGE_BYTES;
-                mbar_expect_tx(full_bar(s), STAGE_BYTES);
-                const int k0 = kb * BK;
-                if (!A_MN) {
-                    tma_load_3d(stage, &mapAhi, full_bar(s), k0, m0, b);
-                    tma_load_3d(stage + PLANE_TILE_BYTES, &mapAlo, full_bar(s), k0, m0, b);
-                } else {
-                    for (int h = 0; h < 2; ++h) {
-                        tma_load_3d(stage + h * (PLANE_TILE_BYTES / 2), &mapAhi, full_bar(s), m0 + 64 * h, k0, b);
-                        tma_load_3d(stage + PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapAlo, full_bar(s), m0 + 64 * h, k0, b);
+            unsigned it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int tn = tile % p.tiles_n, tm = (tile / p.tiles_n) % p.tiles_m, b = tile / (p.tiles_n * p.tiles_m);
+                const int m0 = tm * BM, n0 = tn * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    const unsigned stage = base + s * STAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (!A_MN) {
+                        tma_load_3d(stage, &mapAhi, full_bar(s), k0, m0, b);
+                        tma_load_3d(stage + PLANE_TILE_BYTES, &mapAlo, full_bar(s), k0, m0, b);
+                    } else {
+                        for (int h = 0; h < 2; ++h) {
+                            tma_load_3d(stage + h * (PLANE_TILE_BYTES / 2), &mapAhi, full_bar(s), m0 + 64 * h, k0, b);
+                            tma_load_3d(stage + PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapAlo, full_bar(s), m0 + 64 * h, k0, b);
+                        }
                     }
-                }
-                if (!B_MN) {
-                    tma_load_3d(stage + 2 * PLANE_TILE_BYTES, &mapBhi, full_bar(s), k0, n0, b);
-                    tma_load_3d(stage + 3 * PLANE_TILE_BYTES, &mapBlo, full_bar(s), k0, n0, b);
-                } else {
-                    for (int h = 0; h < 2; ++h) {
-                        tma_load_3d(stage + 2 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBhi, full_bar(s), n0 + 64 * h, k0, b);
-                        tma_load_3d(stage + 3 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBlo, full_bar(s), n0 + 64 * h, k0, b);
+                    if (!B_MN) {
+                        tma_load_3d(stage + 2 * PLANE_TILE_BYTES, &mapBhi, full_bar(s), k0, n0, b);
+                        tma_load_3d(stage + 3 * PLANE_TILE_BYTES, &mapBlo, full_bar(s), k0, n0, b);
+                    } else {
+                        for (int h = 0; h < 2; ++h) {
+                            tma_load_3d(stage + 2 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBhi, full_bar(s), n0 + 64 * h, k0, b);
+                            tma_load_3d(stage + 3 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBlo, full_bar(s), n0 + 64 * h, k0, b);
+                        }
                     }
                 }
             }
         }
     } else if (warp == 5) {
+        // ---------------- MMA issuer: accumulator i&1 in TMEM columns [ (i&1)*BN, +BN )
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N, M
             const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                                    ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            // descriptors differ only in their 14-bit start-address field: build one per operand
+            // plane for stage 0, k-slice 0 and add (byte offset >> 4) afterwards
+            const unsigned a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
+            const unsigned long long dA_hi = smem_desc(base, a_lbo, 1024u);
+            const unsigned long long dA_lo = smem_desc(base + PLANE_TILE_BYTES, a_lbo, 1024u);
+            const unsigned long long dB_hi = smem_desc(base + 2 * PLANE_TILE_BYTES, b_lbo, 1024u);
+            const unsigned long long dB_lo = smem_desc(base + 3 * PLANE_TILE_BYTES, b_lbo, 1024u);
+            constexpr unsigned a_step = (A_MN ? 2048u : 32u) >> 4, b_step = (B_MN ? 2048u : 32u) >> 4;
+            unsigned it = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(full_bar(s), (kb / STAGES) & 1, abort_flag);
+            int i = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
+                const int acc = i & 1;
+                ok = mbar_wait(acc_empty(acc), ((i >> 1) & 1) ^ 1, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned stage = base + s * STAGE_BYTES;
-#pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
+                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     // K-major: 8-row groups 1024 B apart, a 16-element k-slice is 32 B further along the row.
                     // MN-major: 64-wide MN chunks 8192 B apart (LBO), 8-k-row groups 1024 B apart, a k-slice is 2048 B further.
-                    const unsigned a_off = A_MN ? k * 2048u : k * 32u;
-                    const unsigned b_off = B_MN ? k * 2048u : k * 32u;
-                    const unsigned a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
-                    const unsigned long long a_hi = smem_desc(stage + a_off, a_lbo, 1024u);
-                    const unsigned long long a_lo = smem_desc(stage + PLANE_TILE_BYTES + a_off, a_lbo, 1024u);
-                    const unsigned long long b_hi = smem_desc(stage + 2 * PLANE_TILE_BYTES + b_off, b_lbo, 1024u);
-                    const unsigned long long b_lo = smem_desc(stage + 3 * PLANE_TILE_BYTES + b_off, b_lbo, 1024u);
-                    umma_bf16(tmem_acc, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);
-                    umma_bf16(tmem_acc, a_hi, b_lo, idesc, 1u);
-                    umma_bf16(tmem_acc, a_hi, b_hi, idesc, 1u);
+                    const unsigned long long soff = (unsigned long long)((unsigned)(s * STAGE_BYTES) >> 4);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const unsigned long long a_hi = dA_hi + soff + k * a_step, a_lo = dA_lo + soff + k * a_step;
+                        const unsigned long long b_hi = dB_hi + soff + k * b_step, b_lo = dB_lo + soff + k * b_step;
+                        umma_bf16(tmem_acc, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);
+                        umma_bf16(tmem_acc, a_hi, b_lo, idesc, 1u);
+                        umma_bf16(tmem_acc, a_hi, b_hi, idesc, 1u);
+                    }
+                    umma_commit(empty_bar(s));
                 }
-                umma_commit(empty_bar(s));
+                if (ok) umma_commit(acc_full(acc));
             }
-            umma_commit(acc_bar);
         }
     } else {
-        // epilogue: warp q owns TMEM lanes 32q .. 32q+31, i.e. output rows m0 + 32q + lane
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_bar, 0, abort_flag));
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int row = m0 + warp * 32 + lane;
-        if (ok) {
+        // ---------------- epilogue: warp q owns TMEM lanes 32q .. 32q+31; lane = output row.
+        // Each thread combines and stores 32 consecutive columns of its own row with 128-bit
+        // accesses straight from registers: no shared-memory staging, because the tensor core's
+        // operand fetch already uses the whole shared-memory bandwidth.  C (beta != 0) is fetched
+        // one 32-column chunk ahead, the first chunk before waiting for the accumulator.  The
+        // epilogue of tile i overlaps the main loop of tile i+1.
+        const bool has_c = p.C != nullptr && p.beta != 0.0f;
+        const bool vec_ok = ((p.ldc | p.ldd | p.strideC | p.strideD) & 3) == 0 &&
+                            ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 15) == 0 &&
+                            ((p.ldp | p.strideP) & 7) == 0 &&
+                            ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dlo)) & 15) == 0;
+        int i = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
+            const int tn = tile % p.tiles_n, tm = (tile / p.tiles_n) % p.tiles_m, b = tile / (p.tiles_n * p.tiles_m);
+            const int m0 = tm * BM, n0 = tn * BN;
+            const int acc = i & 1;
+            const int row = m0 + warp * 32 + lane;
+            const bool row_ok = row < p.M;
+            const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
+            float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + n0;
+            __nv_bfloat16 *hrow = p.Dhi + (long long)b * p.strideP + (long long)row * p.ldp + n0;
+            __nv_bfloat16 *lrow = p.Dlo + (long long)b * p.strideP + (long long)row * p.ldp + n0;
+            float cv[32];
+            auto fetch_c = [&](int c, float (&dst)[32]) {
+                const int valid = p.N - (n0 + c * 32);
+                if (has_c && row_ok && valid > 0) {
+                    if (vec_ok && valid >= 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 t = __ldg(reinterpret_cast<const float4 *>(crow + c * 32 + j));
+                            dst[j] = t.x; dst[j + 1] = t.y; dst[j + 2] = t.z; dst[j + 3] = t.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) dst[j] = (j < valid) ? __ldg(crow + c * 32 + j) : 0.0f;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) dst[j] = 0.0f;
+                }
+            };
+            fetch_c(0, cv);
+            const bool ok = mbar_wait_warp(acc_full(acc), (i >> 1) & 1, abort_flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 float v[32];
                 tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(c * 32), v);
-                const int col0 = n0 + c * 32;
-                if (row < p.M && col0 < p.N) {
-                    const int valid = min(32, p.N - col0);
-                    if (p.C && p.beta != 0.0f) {
-                        const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + col0;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = (j < valid) ? fmaf(p.alpha, v[j], p.beta * crow[j]) : 0.0f;
-                    } else {
+                for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, cv[j], p.alpha * v[j]);
+                if (c + 1 < BN / 32) fetch_c(c + 1, cv);
+                const int valid = p.N - (n0 + c * 32);
+                if (row_ok && valid > 0) {
+                    if (vec_ok && valid >= 32) {
+                        if (p.D) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = p.alpha * v[j];
-                    }
-                    if (p.D) {
-                        float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + col0;
-                        if (valid == 32 && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(drow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) if (j < valid) drow[j] = v[j];
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4 *>(drow + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                         }
-                    }
-                    if (p.Dhi) {
-                        __nv_bfloat16 *hrow = p.Dhi + (long long)b * p.strideP + (long long)row * p.ldp + col0;
-                        __nv_bfloat16 *lrow = p.Dlo + (long long)b * p.strideP + (long long)row * p.ldp + col0;
+                        if (p.Dhi) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                unsigned h[4], l[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const __nv_bfloat16 h0 = __float2bfloat16_rn(v[j + 2 * q]), h1 = __float2bfloat16_rn(v[j + 2 * q + 1]);
+                                    const __nv_bfloat16 l0 = __float2bfloat16_rn(v[j + 2 * q] - __bfloat162float(h0));
+                                    const __nv_bfloat16 l1 = __float2bfloat16_rn(v[j + 2 * q + 1] - __bfloat162float(h1));
+                                    h[q] = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
+                                    l[q] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
+                                }
+                                *reinterpret_cast<uint4 *>(hrow + c * 32 + j) = make_uint4(h[0], h[1], h[2], h[3]);
+                                *reinterpret_cast<uint4 *>(lrow + c * 32 + j) = make_uint4(l[0], l[1], l[2], l[3]);
+                            }
+                        }
+                    } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             if (j < valid) {
-                                const __nv_bfloat16 h = __float2bfloat16_rn(v[j]);
-                                hrow[j] = h;
-                                lrow[j] = __float2bfloat16_rn(v[j] - __bfloat162float(h));
+                                if (p.D) drow[c * 32 + j] = v[j];
+                                if (p.Dhi) {
+                                    const __nv_bfloat16 h = __float2bfloat16_rn(v[j]);
+                                    hrow[c * 32 + j] = h;
+                                    lrow[c * 32 + j] = __float2bfloat16_rn(v[j] - __bfloat162float(h));
+                                }
                             }
                         }
                     }
                 }
             }
+            // this warp has drained its quarter of the accumulator: let the MMA warp reuse it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
     if (warp == 5) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
@@ -379,7 +470,13 @@ int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) {
         if (!good) return record(QT_ERR_LAUNCH);
         attr_done = true;
     }
-    const unsigned grid = (unsigned)ctas;
+    if (g_gemm_sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        g_gemm_sms = n;
+    }
+    const unsigned grid = (unsigned)(ctas < g_gemm_sms ? ctas : g_gemm_sms);     // persistent: one CTA per SM
     if (!a.a_mn && !a.b_mn) k_gemm_bf16x3<false, false><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
     else if (!a.a_mn && a.b_mn) k_gemm_bf16x3<false, true><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
     else if (a.a_mn && !a.b_mn) k_gemm_bf16x3<true, false><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);

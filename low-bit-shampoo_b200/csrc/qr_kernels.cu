@@ -16,7 +16,7 @@
 namespace qt {
 
 static constexpr int kPanel = 32;
-static constexpr int kQrThreads = 512;
+static constexpr int kQrThreads = 1024;
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -33,7 +33,8 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
     float *P = sm;                                         // [kPanel][mpad], column-major panel
     float *red = P + kPanel * mpad;                        // [32]
     float *tau = red + 32;                                 // [kPanel]
-    float *G = tau + kPanel;                               // [kPanel][kPanel + 1], V^T V (strict upper part)
+    float *colscale = tau + kPanel;                        // [kPanel]
+    float *G = colscale + kPanel;                          // [kPanel][kPanel + 1], V^T V (strict upper part)
     float *Ts = G + kPanel * (kPanel + 1);                 // [kPanel][kPanel + 1]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kQrThreads >> 5;
     const float *A = Abase + (long long)blockIdx.x * strideA + (long long)j0 * n + j0;
@@ -43,16 +44,26 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
     for (int i = tid; i < kPanel * (kPanel + 1); i += kQrThreads) { G[i] = 0.0f; Ts[i] = 0.0f; }
     __syncthreads();
 
+    // sum of squares below the diagonal of column 0; later columns get theirs from the warp
+    // that updates them (one block-wide barrier per column step)
+    float *sig = red;                                      // sig[0..1]: double-buffered sigma
+    {
+        float s0 = 0.0f;
+        for (int r = 1 + tid; r < m; r += kQrThreads) { float v = P[r]; s0 = fmaf(v, v, s0); }
+        s0 = warp_sum(s0);
+        if (lane == 0) G[warp] = s0;                       // G is free until the Gram step
+        __syncthreads();
+        if (tid == 0) {
+            float t = 0.0f;
+            for (int k = 0; k < nwarps; ++k) t += G[k];
+            sig[0] = t;
+        }
+        __syncthreads();
+        if (tid < nwarps) G[tid] = 0.0f;
+    }
     for (int c = 0; c < w; ++c) {
         float *x = P + c * mpad;
-        float s = 0.0f;
-        for (int r = c + 1 + tid; r < m; r += kQrThreads) { float v = x[r]; s = fmaf(v, v, s); }
-        s = warp_sum(s);
-        if (lane == 0) red[warp] = s;
-        __syncthreads();
-        float sigma = 0.0f;
-#pragma unroll
-        for (int k = 0; k < kQrThreads / 32; ++k) sigma += red[k];
+        const float sigma = sig[c & 1];
         const float alpha = x[c];
         float tc = 0.0f, scale = 0.0f;
         if (sigma != 0.0f) {
@@ -60,7 +71,7 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
             tc = (beta - alpha) / beta;
             scale = 1.0f / (alpha - beta);
         }
-        if (tid == 0) tau[c] = tc;
+        if (tid == 0) { tau[c] = tc; colscale[c] = scale; }
         // apply H_c = I - tau v v^T to the remaining panel columns (v = [1; scale * x_below])
         for (int cp = c + 1 + warp; cp < w; cp += nwarps) {
             float *y = P + cp * mpad;
@@ -71,10 +82,24 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
             __syncwarp();
             if (lane == 0) y[c] -= f;
             const float g = f * scale;
-            for (int r = c + 1 + lane; r < m; r += 32) y[r] = fmaf(-g, x[r], y[r]);
+            float s2 = 0.0f;
+            for (int r = c + 1 + lane; r < m; r += 32) {
+                const float yn = fmaf(-g, x[r], y[r]);
+                y[r] = yn;
+                if (r > c + 1) s2 = fmaf(yn, yn, s2);
+            }
+            if (cp == c + 1) {                             // next pivot column: publish its sigma
+                s2 = warp_sum(s2);
+                if (lane == 0) sig[(c + 1) & 1] = s2;
+            }
         }
         __syncthreads();
-        for (int r = c + 1 + tid; r < m; r += kQrThreads) x[r] *= scale;    // x_below becomes v_below
+    }
+    // x_below becomes v_below = scale * x_below
+    for (int c = warp; c < w; c += nwarps) {
+        float *x = P + c * mpad;
+        const float scale = colscale[c];
+        for (int r = c + 1 + lane; r < m; r += 32) x[r] *= scale;
     }
     __syncthreads();
 
@@ -119,7 +144,7 @@ int launch_householder_panel(const float *A, long long strideA, int n, int count
     if (count == 0) return record(QT_OK);
     const int m = n - j0;
     const int mpad = ((m + 31) & ~31) + 1;
-    const size_t smem = sizeof(float) * ((size_t)kPanel * mpad + 32 + kPanel + 2 * kPanel * (kPanel + 1));
+    const size_t smem = sizeof(float) * ((size_t)kPanel * mpad + 32 + 2 * kPanel + 2 * kPanel * (kPanel + 1));
     if (smem > 227 * 1024) return record(QT_ERR_UNSUPPORTED);
     static bool attr_set = false;
     if (!attr_set) {

@@ -39,6 +39,8 @@ struct DequantArgs {
 
 int launch_quantize(const QuantArgs &a, cudaStream_t stream);
 int launch_dequantize(const DequantArgs &a, cudaStream_t stream);
+int launch_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches_dev,
+                             cudaStream_t stream);
 int launch_householder_panel(const float *A, long long strideA, int n, int count, int j0, int w,
                              float *V, long long strideV, float *T, long long strideT, cudaStream_t stream);
 

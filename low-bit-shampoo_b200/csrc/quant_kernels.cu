@@ -41,6 +41,8 @@ struct CodeTables {
     int perm_identity;
     int need_clamp;
     int lut_bad;
+    int tiny_thr;             // some decision threshold has |t| < 2^-50: quotients must be exact even when tiny
+    int thr_cell[NC];         // lookup-table cell of each threshold
     float2 lut[NC == 16 ? kLutCells : 1];   // {threshold inside the cell or +inf, base index bits}
 };
 
@@ -61,7 +63,7 @@ template <int NC>
 __device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) {
     const int tid = threadIdx.x;
     for (int i = tid; i < NC; i += blockDim.x) t.raw[i] = code[i];
-    if (tid == 0) { t.lut_bad = 0; }
+    if (tid == 0) { t.lut_bad = 0; t.tiny_thr = 0; }
     __syncthreads();
     // stable rank sort (the reference sorts only when the codebook is not ascending;
     // sorting an ascending codebook is the identity, functional.py:561-565)
@@ -89,6 +91,8 @@ __device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) 
             if (up) b = m; else a = m;
         }
         t.thr[j] = key_float(b);
+        t.thr_cell[j] = lut_cell(t.thr[j]);
+        if (fabsf(t.thr[j]) < 8.8817842e-16f) t.tiny_thr = 1;             // 2^-50
     }
     if (tid == 0) {
         bool ident = true;
@@ -104,7 +108,7 @@ __device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) 
             int base = 0, inside = 0;
             float th = CUDART_INF_F;
             for (int j = 0; j < NC - 1; ++j) {
-                int cj = lut_cell(t.thr[j]);
+                const int cj = t.thr_cell[j];
                 base += (cj < k);
                 if (cj == k) { ++inside; th = t.thr[j]; }
             }
@@ -134,6 +138,33 @@ __device__ __forceinline__ int code_index(const CodeTables<NC> &t, float q, bool
         }
     }
     return code_index_search<NC>(t, q);
+}
+
+// x / d rounded to nearest, given r = RN(1/d): one reciprocal multiply and two FMA
+// corrections (Markstein).  Exact whenever no intermediate underflows; callers guarantee
+// 2^-40 <= d <= 2^60 and treat |quotient| < 2^-60 as "sign only" (see k_quantize_vec).
+__device__ __forceinline__ float div_by_recip(float x, float d, float r) {
+    float q = x * r;
+    q = fmaf(fmaf(-q, d, x), r, q);
+    q = fmaf(fmaf(-q, d, x), r, q);
+    return q;
+}
+
+// Per-lane quantization of EPL elements for every case the lean path of k_quantize_vec does
+// not cover (any codebook, clamp, permutation, extreme scales).  Kept out of line on purpose.
+template <int NC, int EPL>
+__device__ __noinline__ void quantize_lane_generic(const CodeTables<NC> &tab, const float (&x)[EPL], float amax,
+                                                   int (&idx)[EPL]) {
+    const bool use_lut = (NC == 16) && !tab.lut_bad;
+    for (int j = 0; j < EPL; ++j) {
+        int k = 0;
+        if (amax != 0.0f) {
+            float q = __fdiv_rn(x[j], amax);
+            if (tab.need_clamp) q = fminf(fmaxf(q, tab.cmin), tab.cmax);
+            k = tab.perm[code_index<NC>(tab, q, use_lut)];
+        }
+        idx[j] = k;
+    }
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
@@ -170,7 +201,7 @@ __device__ __forceinline__ void load_vec(const T *p, float (&x)[EPL]) {
 // Quantize, vector path.  Requires n % EPL == 0 and vector-aligned buffers.
 // ------------------------------------------------------------------------------------
 template <typename T, int BITS, int EPL, int LPU>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__restrict__ code,
                int n, int nb, float *__restrict__ absmax_base, long long stride_absmax,
                float *__restrict__ diag_base, long long stride_diag,
@@ -203,10 +234,8 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
         if (u < units && c < n) { load_vec<T, EPL>(A + (long long)r * n + c, x); have = true; }
     }
     build_tables<NC>(tab, code);
-    const bool use_lut = (NC == 16) && !tab.lut_bad;
-    const bool clampq = tab.need_clamp;
-    const bool permute = !tab.perm_identity;
-    const float cmin = tab.cmin, cmax = tab.cmax;
+    const bool lean_launch = (NC == 16) && !tab.lut_bad && !tab.need_clamp && tab.perm_identity && !tab.tiny_thr;
+    const float2 *lut16 = tab.lut;
 
     for (; u_warp < units; u_warp += G) {
         const int c = b * BS + lane_u * EPL;
@@ -231,20 +260,31 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
         if (unit_ok && lane_u == 0) absmax[(long long)r * nb + b] = amax;
 
+        // Lean path (the hot one: 16-entry sorted codebook covering [-1, 1], no threshold within
+        // 2^-50 of zero, every block scale of the warp in [2^-40, 2^60] or zero): q = x / absmax
+        // through an exact reciprocal and two FMA corrections - bit-identical to the IEEE
+        // division (functional.py:604) while nothing underflows; a |q| below 2^-60 only has to
+        // keep its sign.  Anything else takes the out-of-line generic routine.
+        const bool scale_ok = (amax >= 9.094947e-13f && amax <= 1.1529215e18f) || amax == 0.0f;
+        const bool lean = lean_launch && __all_sync(0xffffffffu, scale_ok);
         if (lane_ok) {
             int idx[EPL];
-            if (amax == 0.0f) {                               // functional.py:600-602
-#pragma unroll
-                for (int j = 0; j < EPL; ++j) idx[j] = 0;
-            } else {
+            if (lean) {
+                const float d = (amax == 0.0f) ? 1.0f : amax;
+                const float rcp = __frcp_rn(d);
 #pragma unroll
                 for (int j = 0; j < EPL; ++j) {
-                    float q = __fdiv_rn(x[j], amax);          // functional.py:604
-                    if (clampq) q = fminf(fmaxf(q, cmin), cmax);
-                    int k = code_index<NC>(tab, q, use_lut);
-                    if (permute) k = tab.perm[k];
-                    idx[j] = k;
+                    const float q = div_by_recip(x[j], d, rcp);
+                    const int cell = __float2int_rz(fmaf(q, (float)kLutScale, (float)kLutScale));
+                    const float2 e2 = lut16[cell];
+                    idx[j] = __float_as_int(e2.y) + (q >= e2.x ? 1 : 0);
                 }
+                if (amax == 0.0f) {                           // functional.py:600-602
+#pragma unroll
+                    for (int j = 0; j < EPL; ++j) idx[j] = 0;
+                }
+            } else {
+                quantize_lane_generic<NC, EPL>(tab, x, amax, idx);
             }
             const long long e = (long long)r * n + c;         // flat element index, multiple of EPL
             if constexpr (BITS == 4) {
@@ -468,6 +508,45 @@ k_dequantize_generic(const unsigned char *__restrict__ in_base, long long stride
 }
 
 // ------------------------------------------------------------------------------------
+// Self-test of the fast division: counts pairs (x, d), d in [2^-40, 2^60], |x| <= d, whose
+// reciprocal-based quotient differs in any bit from the IEEE division (quotients below 2^-60
+// in magnitude are exempt, as in the quantizer).  Pairs come from a counter-based hash.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned mix32(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull; z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return (unsigned)((z ^ (z >> 31)) >> 16);
+}
+__global__ void k_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches) {
+    unsigned long long bad = 0;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned a = mix32(seed + 2 * i), b = mix32(seed + 2 * i + 1);
+        // d: exponent in [-40, 60), random mantissa; x = d * (fraction in [-1, 1]) with a random small exponent drop
+        const int ed = (int)(a % 100u) - 40 + 127;
+        const float d = __uint_as_float(((unsigned)ed << 23) | (b & 0x7FFFFFu));
+        const unsigned c = mix32(seed ^ (i * 0xD1342543DE82EF95ull));
+        const int drop = (c >> 24) % 40;                       // |x| spans 40 binades below d
+        float x = __uint_as_float(((unsigned)(ed - drop) << 23) | (c & 0x7FFFFFu));
+        if (fabsf(x) > d) x = d;
+        if (a & 0x80000000u) x = -x;
+        if ((c & 0xFF00u) == 0) x = (c & 1) ? d : -d;           // exact +-1 quotients
+        const float q_ref = __fdiv_rn(x, d);
+        const float q = div_by_recip(x, d, __frcp_rn(d));
+        if (fabsf(q_ref) >= 8.6736174e-19f && __float_as_uint(q) != __float_as_uint(q_ref)) ++bad;   // 2^-60
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
+int launch_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches_dev,
+                             cudaStream_t s) {
+    if (!mismatches_dev) return record(QT_ERR_ARG);
+    k_selftest_division<<<148 * 8, 256, 0, s>>>(seed, pairs, mismatches_dev);
+    count_launch(1);
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------------
 // Host launchers.
 // ------------------------------------------------------------------------------------
 static int g_sm_count = 0;
@@ -514,7 +593,12 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
     if (epl) {
         const int lpu = a.bs / epl;
         const long long units = (long long)n * nb;
-        dim3 grid(grid_x_for(units * lpu, a.count, 4), a.count);
+        // every CTA builds the code tables once: keep the grid near one resident wave
+        long long per_matrix = ((long long)sm_count() * 8 + a.count - 1) / a.count;
+        const long long needed = (units * lpu + kThreads - 1) / kThreads;
+        if (per_matrix > needed) per_matrix = needed;
+        if (per_matrix < 1) per_matrix = 1;
+        dim3 grid((unsigned)per_matrix, a.count);
 #define QT_LAUNCH_Q(E, L)                                                                          \
         k_quantize_vec<T, BITS, E, L><<<grid, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.absmax, \
             a.stride_absmax, a.diag, a.stride_diag, a.out, a.stride_out)

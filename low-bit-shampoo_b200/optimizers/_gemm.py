@@ -21,19 +21,39 @@ def _pitch(cols):
 
 
 class Planes:
-    """(batch, rows, cols) fp32 values as bf16 hi/lo planes of pitch `ld`."""
+    """(batch, rows, cols) fp32 values as bf16 hi/lo planes of pitch `ld`.
 
-    def __init__(self, batch, rows, cols, device):
+    `offset` (elements) selects a sub-matrix of a parent's storage: window() shares memory."""
+
+    def __init__(self, batch, rows, cols, device, _share=None):
         self.batch, self.rows, self.cols = batch, rows, cols
+        if _share is not None:
+            self.hi, self.lo, self.ld, self.stride, self.offset = _share
+            return
         self.ld = _pitch(cols)
-        self.rows_alloc = rows
-        self.stride = self.rows_alloc * self.ld
+        self.stride = rows * self.ld
+        self.offset = 0
         buf = torch.empty(2, batch, self.stride, dtype=torch.bfloat16, device=device)
         self.hi, self.lo = buf[0], buf[1]
 
+    def window(self, row0, col0, rows, cols):
+        """Planes of the sub-matrix [row0:row0+rows, col0:col0+cols]; col0 must be a multiple of 8."""
+        assert col0 % 8 == 0 and row0 + rows <= self.rows and col0 + cols <= self.cols
+        return Planes(self.batch, rows, cols, self.hi.device,
+                      _share=(self.hi, self.lo, self.ld, self.stride, self.offset + row0 * self.ld + col0))
+
+    def ptr_hi(self):
+        return ct.c_void_p(self.hi.data_ptr() + 2 * self.offset)
+
+    def ptr_lo(self):
+        return ct.c_void_p(self.lo.data_ptr() + 2 * self.offset)
+
     def to_float(self):
-        v = (self.hi.float() + self.lo.float()).view(self.batch, self.rows_alloc, self.ld)
-        return v[:, : self.rows, : self.cols]
+        n = (self.rows - 1) * self.ld + self.cols
+        idx = self.hi[:, self.offset: self.offset + n].float() + self.lo[:, self.offset: self.offset + n].float()
+        full = torch.zeros(self.batch, self.rows * self.ld, device=idx.device)
+        full[:, :n] = idx
+        return full.view(self.batch, self.rows, self.ld)[:, :, : self.cols]
 
 
 def split(X):
@@ -42,14 +62,14 @@ def split(X):
     b, r, c = X.shape
     P = Planes(b, r, c, X.device)
     with torch.cuda.device(X.device):
-        rc = F.lib.qt_split_bf16(_ptr(X), X.stride(1), X.stride(0), r, c, b, _ptr(P.hi), _ptr(P.lo), P.ld, P.stride,
+        rc = F.lib.qt_split_bf16(_ptr(X), X.stride(1), X.stride(0), r, c, b, P.ptr_hi(), P.ptr_lo(), P.ld, P.stride,
                                  F._stream(X))
     F._check(rc, "split_bf16")
     return P
 
 
 def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=None, want_planes=False,
-           want_float=True):
+           want_float=True, out_planes=None):
     """alpha * op(A) @ op(B) + beta * C for batches held as Planes.
 
     A holds (b, M, K) (or (b, K, M) with trans_a); B holds (b, K, N) (or (b, N, K) with
@@ -66,7 +86,9 @@ def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=
     if want_float:
         D = out if out is not None else torch.empty(b, M, N, dtype=torch.float32, device=dev)
         assert D.stride(2) == 1
-    P = Planes(b, M, N, dev) if want_planes else None
+    P = out_planes if out_planes is not None else (Planes(b, M, N, dev) if want_planes else None)
+    if P is not None:
+        assert P.rows == M and P.cols == N and P.batch == b
     if C is not None:
         assert C.stride(2) == 1
     # kernel view: A logically M x K (a_mn: stored [K][M]); B logically N x K (b_mn: stored [K][N])
@@ -74,12 +96,12 @@ def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=
     b_mn = 0 if trans_b else 1
     with torch.cuda.device(dev):
         rc = F.lib.qt_gemm_bf16x3(
-            _ptr(A.hi), _ptr(A.lo), A.ld, A.stride, a_mn,
-            _ptr(B.hi), _ptr(B.lo), B.ld, B.stride, b_mn,
+            A.ptr_hi(), A.ptr_lo(), A.ld, A.stride, a_mn,
+            B.ptr_hi(), B.ptr_lo(), B.ld, B.stride, b_mn,
             M, N, K, b, float(alpha), float(beta),
             _ptr(C), C.stride(1) if C is not None else 0, C.stride(0) if C is not None else 0,
             _ptr(D), D.stride(1) if D is not None else 0, D.stride(0) if D is not None else 0,
-            _ptr(P.hi) if P else None, _ptr(P.lo) if P else None, P.ld if P else 0, P.stride if P else 0,
+            P.ptr_hi() if P else None, P.ptr_lo() if P else None, P.ld if P else 0, P.stride if P else 0,
             F._stream(A.hi))
     F._check(rc, "gemm_bf16x3")
     return D, P

@@ -21,7 +21,7 @@ LEGACY_SYMBOLS = tuple(
 )
 EXTRA_SYMBOLS = (
     "qt_version", "qt_launch_count", "qt_last_error", "qt_error_string", "qt_set_stream",
-    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel", "qt_split_bf16", "qt_gemm_bf16x3", "qt_device_error",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel", "qt_selftest_division", "qt_split_bf16", "qt_gemm_bf16x3", "qt_device_error",
 )
 
 _lib = None
@@ -44,6 +44,8 @@ def _declare(lib):
     lib.qt_quantize_blockwise.argtypes = [vp, i32, i64, vp, i32, i32, vp, i64, vp, i64, vp, i64, i32, i32, vp]
     lib.qt_dequantize_blockwise.restype = i32
     lib.qt_dequantize_blockwise.argtypes = [vp, i64, vp, i32, i32, vp, i64, vp, i64, vp, i32, i64, i32, i32, vp]
+    lib.qt_selftest_division.restype = i32
+    lib.qt_selftest_division.argtypes = [ct.c_ulonglong, ct.c_ulonglong, vp, vp]
     lib.qt_householder_panel.restype = i32
     lib.qt_householder_panel.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, i64, vp]
     f32 = ct.c_float

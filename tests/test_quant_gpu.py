@@ -253,3 +253,14 @@ def test_output_canaries_untouched(F):
         deq = torch.full((n * n + 32,), -3.0, device=dev)
         F.dequantize_blockwise(out[:nbytes], code, n, absmax[: n * nb], out=deq[: n * n].view(n, n), blocksize=64, bits=4)
         assert bool((deq[n * n:] == -3.0).all())
+
+
+def test_fast_division_is_bit_identical_to_ieee_division(native_lib):
+    """2^31 pseudo-random (x, absmax) pairs: reciprocal + two FMA corrections == x / absmax, bit for bit."""
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda:0")
+    for seed in (1, 2):
+        rc = native_lib.qt_selftest_division(seed, 1 << 30, ct.c_void_p(counter.data_ptr()),
+                                             ct.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+    torch.cuda.synchronize()
+    assert int(counter.item()) == 0
