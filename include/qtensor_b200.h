@@ -125,8 +125,8 @@ int qt_selftest_division(unsigned long long seed, unsigned long long pairs, unsi
  *   V + m*strideV : order x order row-major; the block rows j0.., columns j0..j0+width-1
  *                   receives the Householder vectors (zeros above the diagonal, ones on it);
  *   T + m*strideT : 32 x 32 row-major upper-triangular factor with H_1..H_w = I - V T V^T.
- * A itself is only read.  Orders above about 1700 are refused with QT_ERR_UNSUPPORTED
- * (the panel must fit in shared memory).
+ * A itself is only read.  Panels taller than 1216 rows are refused with QT_ERR_UNSUPPORTED
+ * (the panel is held in registers, 38 rows per lane).
  */
 int qt_householder_panel(const float *A, long long strideA, int order, int count, int j0, int width,
                          float *V, long long strideV, float *T, long long strideT, void *stream);
@@ -161,6 +161,22 @@ int qt_gemm_bf16x3(const void *Ahi, const void *Alo, long long lda, long long st
                    const float *C, long long ldc, long long strideC,
                    float *D, long long ldd, long long strideD,
                    void *Dhi, void *Dlo, long long ldp, long long strideP, void *stream);
+
+/*
+ * D = alpha * op(A) * op(B) + beta * C for fp32 row-major operands in one call: splits both
+ * operands into bf16 planes inside `scratch` (caller-owned device memory of at least
+ * qt_matmul_f32_scratch_bytes(...) bytes), then runs qt_gemm_bf16x3.  op(A) is M x K
+ * (trans_a: A is stored K x M), op(B) is K x N (trans_b: B is stored N x K); lda/ldb/ldc/ldd in
+ * floats, `batch` matrices stride* floats apart.  Same products of the reference as
+ * qt_gemm_bf16x3 (e.g. qtensor/utils.py:196, optimizers/shampoo2.py:265-268).
+ */
+unsigned long long qt_matmul_f32_scratch_bytes(int M, int N, int K, int batch, int trans_a, int trans_b);
+int qt_matmul_f32(const float *A, long long lda, long long strideA, int trans_a,
+                  const float *B, long long ldb, long long strideB, int trans_b,
+                  int M, int N, int K, int batch, float alpha, float beta,
+                  const float *C, long long ldc, long long strideC,
+                  float *D, long long ldd, long long strideD,
+                  void *scratch, unsigned long long scratch_bytes, void *stream);
 
 /* Sticky device-side error word (QT_OK or QT_ERR_TIMEOUT); synchronises the device.
  * clear != 0 resets it.  Additive; the reference has no device-side waits. */

@@ -351,7 +351,35 @@ k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant_
     }
 }
 
-// fp32 -> (hi, lo) bf16 planes, optionally transposing nothing: plain elementwise pass.
+// fp32 -> (hi, lo) bf16 planes.  Vector variant: 8 consecutive elements per thread (two 128-bit
+// loads, two 128-bit stores); scalar variant for unaligned or ragged rows.
+__device__ __forceinline__ void split2(float a, float b, unsigned &h, unsigned &l) {
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(a), h1 = __float2bfloat16_rn(b);
+    const __nv_bfloat16 l0 = __float2bfloat16_rn(a - __bfloat162float(h0));
+    const __nv_bfloat16 l1 = __float2bfloat16_rn(b - __bfloat162float(h1));
+    h = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
+    l = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
+}
+
+__global__ void __launch_bounds__(256)
+k_split_bf16_vec(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols8,
+                 __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, long long ldp, long long strideP) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    __nv_bfloat16 *h = hi + (long long)b * strideP, *l = lo + (long long)b * strideP;
+    const long long total = (long long)rows * cols8;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / cols8), c = (int)(e - (long long)r * cols8) * 8;
+        const float4 v0 = __ldg(reinterpret_cast<const float4 *>(x + (long long)r * ldx + c));
+        const float4 v1 = __ldg(reinterpret_cast<const float4 *>(x + (long long)r * ldx + c + 4));
+        uint4 H, L;
+        split2(v0.x, v0.y, H.x, L.x); split2(v0.z, v0.w, H.y, L.y);
+        split2(v1.x, v1.y, H.z, L.z); split2(v1.z, v1.w, H.w, L.w);
+        *reinterpret_cast<uint4 *>(h + (long long)r * ldp + c) = H;
+        *reinterpret_cast<uint4 *>(l + (long long)r * ldp + c) = L;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 k_split_bf16(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
              __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, long long ldp, long long strideP) {
@@ -406,12 +434,21 @@ int launch_split_bf16(const float *X, long long ldx, long long strideX, int rows
     if (rows < 0 || cols < 0 || batch < 0 || batch > 65535) return record(QT_ERR_ARG);
     if (rows == 0 || cols == 0 || batch == 0) return record(QT_OK);
     if (!X || !hi || !lo || ldx < cols || ldp < cols) return record(QT_ERR_ARG);
-    long long total = (long long)rows * cols;
-    long long ctas = (total + 256 * 8 - 1) / (256 * 8);
-    if (ctas > 148 * 16) ctas = 148 * 16;
+    const bool vec = cols % 8 == 0 && ldx % 4 == 0 && strideX % 4 == 0 && ldp % 8 == 0 && strideP % 8 == 0 &&
+                     (reinterpret_cast<uintptr_t>(X) & 15) == 0 && (reinterpret_cast<uintptr_t>(hi) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(lo) & 15) == 0;
+    const long long total = vec ? (long long)rows * (cols / 8) : (long long)rows * cols;
+    long long ctas = (total + 256 * 4 - 1) / (256 * 4);
+    const long long cap = (148LL * 32 + batch - 1) / batch;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
     dim3 grid((unsigned)ctas, batch);
-    k_split_bf16<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, static_cast<__nv_bfloat16 *>(hi),
-                                       static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    if (vec)
+        k_split_bf16_vec<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols / 8, static_cast<__nv_bfloat16 *>(hi),
+                                               static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    else
+        k_split_bf16<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, static_cast<__nv_bfloat16 *>(hi),
+                                           static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
     count_launch(1);
     return check_launch();
 }
@@ -485,6 +522,50 @@ int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) {
     return check_launch();
 }
 
+// fp32 operands in, fp32 out: both operands are split into bf16 planes inside `scratch`
+// (global memory owned by the caller), then multiplied on the tensor cores.
+static inline long long pitch8(long long cols) { return (cols + 7) / 8 * 8; }
+
+size_t matmul_f32_scratch_bytes(int M, int N, int K, int batch, int trans_a, int trans_b) {
+    const long long a_rows = trans_a ? K : M, a_cols = trans_a ? M : K;
+    const long long b_rows = trans_b ? N : K, b_cols = trans_b ? K : N;
+    const long long elems = (long long)batch * (a_rows * pitch8(a_cols) + b_rows * pitch8(b_cols));
+    return (size_t)elems * 2 /*planes*/ * 2 /*bytes*/ + 64;
+}
+
+struct MatmulF32Args {
+    const float *A; long long lda, strideA; int trans_a;
+    const float *B; long long ldb, strideB; int trans_b;
+    int M, N, K, batch; float alpha, beta;
+    const float *C; long long ldc, strideC;
+    float *D; long long ldd, strideD;
+};
+
+int launch_matmul_f32(const MatmulF32Args &a, void *scratch, size_t scratch_bytes, cudaStream_t s) {
+    if (a.M < 0 || a.N < 0 || a.K <= 0 || a.batch < 0) return record(QT_ERR_ARG);
+    if (a.M == 0 || a.N == 0 || a.batch == 0) return record(QT_OK);
+    if (!a.A || !a.B || !a.D || !scratch) return record(QT_ERR_ARG);
+    if (scratch_bytes < matmul_f32_scratch_bytes(a.M, a.N, a.K, a.batch, a.trans_a, a.trans_b)) return record(QT_ERR_ARG);
+    const long long a_rows = a.trans_a ? a.K : a.M, a_cols = a.trans_a ? a.M : a.K;
+    const long long b_rows = a.trans_b ? a.N : a.K, b_cols = a.trans_b ? a.K : a.N;
+    const long long lpa = pitch8(a_cols), lpb = pitch8(b_cols);
+    const long long spa = a_rows * lpa, spb = b_rows * lpb;              // plane strides per matrix
+    unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~(uintptr_t)15);
+    __nv_bfloat16 *Ahi = reinterpret_cast<__nv_bfloat16 *>(base);
+    __nv_bfloat16 *Alo = Ahi + (long long)a.batch * spa;
+    __nv_bfloat16 *Bhi = Alo + (long long)a.batch * spa;
+    __nv_bfloat16 *Blo = Bhi + (long long)a.batch * spb;
+    int rc = launch_split_bf16(a.A, a.lda, a.strideA, (int)a_rows, (int)a_cols, a.batch, Ahi, Alo, lpa, spa, s);
+    if (rc != QT_OK) return rc;
+    rc = launch_split_bf16(a.B, a.ldb, a.strideB, (int)b_rows, (int)b_cols, a.batch, Bhi, Blo, lpb, spb, s);
+    if (rc != QT_OK) return rc;
+    // kernel convention: A logically M x K (a_mn: stored [K][M]); B logically N x K (b_mn: stored [K][N])
+    GemmArgs g{Ahi, Alo, lpa, spa, a.trans_a ? 1 : 0, Bhi, Blo, lpb, spb, a.trans_b ? 0 : 1,
+               a.M, a.N, a.K, a.batch, a.alpha, a.beta, a.C, a.ldc, a.strideC, a.D, a.ldd, a.strideD,
+               nullptr, nullptr, 0, 0};
+    return launch_gemm_bf16x3(g, s);
+}
+
 int read_gemm_error(bool clear) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return QT_ERR_LAUNCH;
@@ -515,6 +596,21 @@ int qt_gemm_bf16x3(const void *Ahi, const void *Alo, long long lda, long long st
     GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, M, N, K, batch, alpha, beta,
                C, ldc, strideC, D, ldd, strideD, Dhi, Dlo, ldp, strideP};
     return launch_gemm_bf16x3(a, static_cast<cudaStream_t>(stream));
+}
+
+unsigned long long qt_matmul_f32_scratch_bytes(int M, int N, int K, int batch, int trans_a, int trans_b) {
+    return (unsigned long long)matmul_f32_scratch_bytes(M, N, K, batch, trans_a, trans_b);
+}
+
+int qt_matmul_f32(const float *A, long long lda, long long strideA, int trans_a,
+                  const float *B, long long ldb, long long strideB, int trans_b,
+                  int M, int N, int K, int batch, float alpha, float beta,
+                  const float *C, long long ldc, long long strideC,
+                  float *D, long long ldd, long long strideD,
+                  void *scratch, unsigned long long scratch_bytes, void *stream) {
+    MatmulF32Args a{A, lda, strideA, trans_a, B, ldb, strideB, trans_b, M, N, K, batch, alpha, beta,
+                    C, ldc, strideC, D, ldd, strideD};
+    return launch_matmul_f32(a, scratch, (size_t)scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int qt_device_error(int clear) { return read_gemm_error(clear != 0); }

@@ -14,18 +14,21 @@ import torch
 import qtensor.functional as F
 
 PANEL = 32
-MAX_ORDER = 1700            # the panel kernel keeps a (rows x 32) panel in shared memory
+MAX_ORDER = 1216            # the panel kernel keeps a (rows x 32) panel in registers, 38 rows per lane
 
 
 def _ptr(t):
     return ct.c_void_p(t.data_ptr())
 
 
-USE_TENSOR_CORES = False     # trailing updates: rank-32 products are memory-bound; fp32 library products are faster here
+OUTER = 128                 # columns per outer block (four panels): trailing updates are rank-128
+USE_TENSOR_CORES = True     # rank-128 far updates on the tcgen05 kernel (panel-local rank-32 ones stay fp32)
 
 
-def _reflect(lib, stream, Vk, Tk, target, target_planes, transpose_t):
-    """target <- (I - Vk T Vk^T) target (or with T^T), fp32 in place, planes kept in step."""
+def _reflect(Vk, Tk, target, target_planes, transpose_t):
+    """target <- (I - Vk T Vk^T) target (or with T^T), fp32 in place; when `target_planes` (the
+    bf16 planes of `target`) is given the two large products run on the tensor cores and the
+    planes are kept in step with the fp32 values."""
     from optimizers import _gemm
     if target_planes is None:
         W = torch.bmm(Vk.transpose(1, 2), target)
@@ -38,6 +41,23 @@ def _reflect(lib, stream, Vk, Tk, target, target_planes, transpose_t):
     _gemm.matmul(Pv, _gemm.split(W), alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
 
 
+def _merge_t(Vo, Tp, widths):
+    """Triangular factor of a block of panels: H_1 .. H_p = I - Vo T Vo^T from the panels' own
+    factors Tp[k] (LAPACK larft recurrence on blocks): T[:c, c:c+w] = -T[:c, :c] (Vo[:, :c]^T Vo[:, c:c+w]) Tk."""
+    B = Vo.shape[0]
+    wo = sum(widths)
+    T = torch.zeros(B, wo, wo, dtype=torch.float32, device=Vo.device)
+    G = torch.bmm(Vo.transpose(1, 2), Vo) if len(widths) > 1 else None
+    c = 0
+    for k, w in enumerate(widths):
+        Tk = Tp[:, k, :w, :w]
+        T[:, c:c + w, c:c + w] = Tk
+        if c:
+            T[:, :c, c:c + w] = -torch.bmm(torch.bmm(T[:, :c, :c], G[:, :c, c:c + w]), Tk)
+        c += w
+    return T
+
+
 def householder_q(X):
     """Q of the QR factorisation of each X[b] (X: (B, n, n) fp32 CUDA, overwritten)."""
     B, n, _ = X.shape
@@ -48,27 +68,34 @@ def householder_q(X):
     lib = F.lib
     from optimizers import _gemm
     tc = USE_TENSOR_CORES
-    panels = list(range(0, n, PANEL))
+    npan = (n + PANEL - 1) // PANEL
     V = torch.zeros(B, n, n, dtype=torch.float32, device=X.device)
-    T = torch.empty(B, len(panels), PANEL, PANEL, dtype=torch.float32, device=X.device)
+    T = torch.empty(B, npan, PANEL, PANEL, dtype=torch.float32, device=X.device)
     stream = F._stream(X)
+    blocks = []                                           # (J0, wo, T_big)
     with torch.cuda.device(X.device):
         Xp = _gemm.split(X) if tc else None
-        for k, j0 in enumerate(panels):
-            w = min(PANEL, n - j0)
-            rc = lib.qt_householder_panel(_ptr(X), n * n, n, B, j0, w, _ptr(V), n * n,
-                                          _ptr(T[:, k]), len(panels) * PANEL * PANEL, stream)
-            F._check(rc, "householder panel")
-            if j0 + w < n:
-                m, t = n - j0, n - j0 - w
-                _reflect(lib, stream, V[:, j0:, j0:j0 + w], T[:, k, :w, :w], X[:, j0:, j0 + w:],
-                         Xp.window(j0, j0 + w, m, t) if tc else None, transpose_t=True)
+        for J0 in range(0, n, OUTER):
+            wo = min(OUTER, n - J0)
+            widths = []
+            for j0 in range(J0, J0 + wo, PANEL):
+                w = min(PANEL, n - j0)
+                k = j0 // PANEL
+                rc = lib.qt_householder_panel(_ptr(X), n * n, n, B, j0, w, _ptr(V), n * n,
+                                              _ptr(T[:, k]), npan * PANEL * PANEL, stream)
+                F._check(rc, "householder panel")
+                widths.append(w)
+                if j0 + w < J0 + wo:                      # rest of this outer block: rank-32 update in fp32
+                    _reflect(V[:, j0:, j0:j0 + w], T[:, k, :w, :w], X[:, j0:, j0 + w:J0 + wo], None, True)
+            Vo = V[:, J0:, J0:J0 + wo]
+            Tb = _merge_t(Vo, T[:, J0 // PANEL:], widths)
+            blocks.append((J0, wo, Tb))
+            if J0 + wo < n:
+                m, t = n - J0, n - J0 - wo
+                _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True)
         Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
         Qp = _gemm.split(Q) if tc else None
-        for k in reversed(range(len(panels))):
-            j0 = panels[k]
-            w = min(PANEL, n - j0)
-            m = n - j0
-            _reflect(lib, stream, V[:, j0:, j0:j0 + w], T[:, k, :w, :w], Q[:, j0:, j0:],
-                     Qp.window(j0, j0, m, m) if tc else None, transpose_t=False)
+        for J0, wo, Tb in reversed(blocks):
+            m = n - J0
+            _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False)
     return Q

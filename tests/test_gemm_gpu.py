@@ -56,3 +56,28 @@ def test_split_planes_are_exact_to_16_bits(native_lib):
     P = _gemm.split(X)
     err = (P.to_float() - X).abs() / X.abs().clamp_min(1e-30)
     assert float(err.max()) < 2.0 ** -15
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True)])
+def test_matmul_f32_entry_point_with_caller_scratch(native_lib, trans_a, trans_b):
+    """qt_matmul_f32: fp32 operands, planes built in caller-provided scratch memory."""
+    import ctypes as ct
+    lib = native_lib
+    g = torch.Generator(device="cuda").manual_seed(17)
+    b, M, N, K = 3, 320, 200, 456
+    A = torch.randn((b, K, M) if trans_a else (b, M, K), device="cuda", generator=g)
+    B = torch.randn((b, N, K) if trans_b else (b, K, N), device="cuda", generator=g)
+    C = torch.randn(b, M, N, device="cuda", generator=g)
+    D = torch.empty(b, M, N, device="cuda")
+    need = lib.qt_matmul_f32_scratch_bytes(M, N, K, b, int(trans_a), int(trans_b))
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    P = lambda t: ct.c_void_p(t.data_ptr())
+    st = ct.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.qt_matmul_f32(P(A), A.stride(1), A.stride(0), int(trans_a), P(B), B.stride(1), B.stride(0), int(trans_b),
+                           M, N, K, b, 2.0, -1.0, P(C), N, M * N, P(D), N, M * N, P(scratch), need, st)
+    assert rc == 0 and device_ok(lib)
+    ref = 2.0 * ((A.transpose(1, 2) if trans_a else A).double() @ (B.transpose(1, 2) if trans_b else B).double()) - C.double()
+    assert rel(D, ref) < TOL
+    # too little scratch is refused before anything is launched
+    assert lib.qt_matmul_f32(P(A), A.stride(1), A.stride(0), int(trans_a), P(B), B.stride(1), B.stride(0), int(trans_b),
+                             M, N, K, b, 1.0, 0.0, None, 0, 0, P(D), N, M * N, P(scratch), need - 4096, st) == 1
