@@ -39,6 +39,10 @@ extern "C" {
 #define QT_ERR_DTYPE          5   /* dtype tag not QT_F32 / QT_BF16                      */
 #define QT_ERR_UNSUPPORTED    6   /* shape outside what the kernel family supports       */
 #define QT_ERR_TIMEOUT        7   /* a bounded device-side wait gave up                  */
+#define QT_ERR_TOO_LARGE      8   /* operands exceed the fixed scratch of a *_static call */
+
+/* Size of the built-in scratch array used by qt_matmul_f32_static (16 MiB per GPU). */
+#define QT_STATIC_SCRATCH_BYTES (16u << 20)
 
 #define QT_F32   0
 #define QT_BF16  1
@@ -177,6 +181,34 @@ int qt_matmul_f32(const float *A, long long lda, long long strideA, int trans_a,
                   const float *C, long long ldc, long long strideC,
                   float *D, long long ldd, long long strideD,
                   void *scratch, unsigned long long scratch_bytes, void *stream);
+
+/*
+ * qt_matmul_f32 for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Who needs it: a host that gave its whole device-memory budget to a fixed arena
+ * at start-up and has no allocator to ask at call time; a plain-C embedding with no tensor
+ * library behind it; a latency-critical loop where an allocation (which may synchronise the
+ * device or fail under fragmentation) is not acceptable.  Such callers still own A, B, C and D;
+ * what they cannot supply is the temporary room for the bf16 operand planes.  This entry point
+ * keeps that room inside the library: a fixed QT_STATIC_SCRATCH_BYTES (16 MiB) array in device
+ * memory, present on every GPU that loads the library for the life of the process.
+ *   - Arguments and result are those of qt_matmul_f32 without `scratch`; the output is
+ *     bit-identical to qt_matmul_f32 on the same inputs.
+ *   - Limit: qt_matmul_f32_scratch_bytes(M, N, K, batch, trans_a, trans_b) must not exceed
+ *     QT_STATIC_SCRATCH_BYTES (e.g. two 1024 x 1024 operands, or 16 pairs of 256 x 256);
+ *     larger requests return QT_ERR_TOO_LARGE and launch nothing.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress with that device current).  Make that first call during set-up,
+ *     before any stream capture is begun on that device.
+ *   - All calls on one GPU share the one array, which keeps whatever the previous call left in
+ *     it; nothing in it needs to be cleared between calls.  Two calls whose kernels can overlap
+ *     on the GPU (different streams, no ordering between them) race on the array: order them.
+ */
+int qt_matmul_f32_static(const float *A, long long lda, long long strideA, int trans_a,
+                         const float *B, long long ldb, long long strideB, int trans_b,
+                         int M, int N, int K, int batch, float alpha, float beta,
+                         const float *C, long long ldc, long long strideC,
+                         float *D, long long ldd, long long strideD, void *stream);
 
 /* Sticky device-side error word (QT_OK or QT_ERR_TIMEOUT); synchronises the device.
  * clear != 0 resets it.  Additive; the reference has no device-side waits. */

@@ -71,6 +71,7 @@ const char *qt_error_string(int status) {
         case QT_ERR_DTYPE: return "dtype tag must be QT_F32 or QT_BF16";
         case QT_ERR_UNSUPPORTED: return "shape not supported by this kernel family";
         case QT_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case QT_ERR_TOO_LARGE: return "operands need more scratch than the library's fixed 16 MiB array holds";
         default: return "unknown status";
     }
 }

@@ -566,6 +566,50 @@ int launch_matmul_f32(const MatmulF32Args &a, void *scratch, size_t scratch_byte
     return launch_gemm_bf16x3(g, s);
 }
 
+// ------------------------------------------------------------------------------------
+// Allocation-free variant of launch_matmul_f32: the bf16 planes live in a fixed array that is
+// part of the library image, so a caller that cannot obtain device memory at call time can
+// still multiply fp32 matrices.  Every GPU that loads the library holds the array until the
+// process exits.
+// ------------------------------------------------------------------------------------
+static constexpr size_t kStaticScratchBytes = (size_t)QT_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static constexpr int kMaxDevices = 64;
+static void *g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the CURRENT device.  In host code the array's name is
+// only a handle; the address a kernel can use comes from cudaGetSymbolAddress, looked up once
+// per device with that device current.
+static int static_scratch_address(void **out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return QT_ERR_LAUNCH;
+    if (!g_static_scratch_addr[dev]) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return QT_ERR_LAUNCH;
+        }
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return QT_OK;
+}
+
+int launch_matmul_f32_static(const MatmulF32Args &a, cudaStream_t s) {
+    if (a.M < 0 || a.N < 0 || a.K <= 0 || a.batch < 0) return record(QT_ERR_ARG);
+    if (a.M == 0 || a.N == 0 || a.batch == 0) return record(QT_OK);
+    if (matmul_f32_scratch_bytes(a.M, a.N, a.K, a.batch, a.trans_a, a.trans_b) > kStaticScratchBytes)
+        return record(QT_ERR_TOO_LARGE);
+    void *scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != QT_OK) return record(rc);
+    // Nothing in the scratch has to start at zero: the split kernels overwrite every plane
+    // element the product reads (TMA never reads the pitch padding), so stale contents of an
+    // earlier call are harmless.
+    return launch_matmul_f32(a, scratch, kStaticScratchBytes, s);
+}
+
 int read_gemm_error(bool clear) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return QT_ERR_LAUNCH;
@@ -611,6 +655,16 @@ int qt_matmul_f32(const float *A, long long lda, long long strideA, int trans_a,
     MatmulF32Args a{A, lda, strideA, trans_a, B, ldb, strideB, trans_b, M, N, K, batch, alpha, beta,
                     C, ldc, strideC, D, ldd, strideD};
     return launch_matmul_f32(a, scratch, (size_t)scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int qt_matmul_f32_static(const float *A, long long lda, long long strideA, int trans_a,
+                         const float *B, long long ldb, long long strideB, int trans_b,
+                         int M, int N, int K, int batch, float alpha, float beta,
+                         const float *C, long long ldc, long long strideC,
+                         float *D, long long ldd, long long strideD, void *stream) {
+    MatmulF32Args a{A, lda, strideA, trans_a, B, ldb, strideB, trans_b, M, N, K, batch, alpha, beta,
+                    C, ldc, strideC, D, ldd, strideD};
+    return launch_matmul_f32_static(a, static_cast<cudaStream_t>(stream));
 }
 
 int qt_device_error(int clear) { return read_gemm_error(clear != 0); }

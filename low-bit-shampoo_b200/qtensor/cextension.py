@@ -21,7 +21,7 @@ LEGACY_SYMBOLS = tuple(
 )
 EXTRA_SYMBOLS = (
     "qt_version", "qt_launch_count", "qt_last_error", "qt_error_string", "qt_set_stream",
-    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel", "qt_selftest_division", "qt_split_bf16", "qt_gemm_bf16x3", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_device_error",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel", "qt_selftest_division", "qt_split_bf16", "qt_gemm_bf16x3", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error",
 )
 
 _lib = None
@@ -59,6 +59,9 @@ def _declare(lib):
     lib.qt_matmul_f32.restype = i32
     lib.qt_matmul_f32.argtypes = [vp, i64, i64, i32, vp, i64, i64, i32, i32, i32, i32, i32, f32, f32,
                                   vp, i64, i64, vp, i64, i64, vp, ct.c_ulonglong, vp]
+    lib.qt_matmul_f32_static.restype = i32
+    lib.qt_matmul_f32_static.argtypes = [vp, i64, i64, i32, vp, i64, i64, i32, i32, i32, i32, i32, f32, f32,
+                                         vp, i64, i64, vp, i64, i64, vp]
     lib.qt_device_error.restype = i32
     lib.qt_device_error.argtypes = [i32]
     for name in LEGACY_SYMBOLS:
