@@ -152,19 +152,25 @@ __device__ __forceinline__ float div_by_recip(float x, float d, float r) {
 
 // Per-lane quantization of EPL elements for every case the lean path of k_quantize_vec does
 // not cover (any codebook, clamp, permutation, extreme scales).  Kept out of line on purpose.
+// Operands and results travel by value (registers): passing the caller's arrays by reference
+// would force them into local memory on the hot path as well.
+template <int EPL> struct LaneVals { float v[EPL]; };
+
 template <int NC, int EPL>
-__device__ __noinline__ void quantize_lane_generic(const CodeTables<NC> &tab, const float (&x)[EPL], float amax,
-                                                   int (&idx)[EPL]) {
+__device__ __noinline__ unsigned long long quantize_lane_generic(const CodeTables<NC> &tab, LaneVals<EPL> x, float amax) {
     const bool use_lut = (NC == 16) && !tab.lut_bad;
+    unsigned long long packed = 0;                        // one byte per element
+#pragma unroll
     for (int j = 0; j < EPL; ++j) {
         int k = 0;
         if (amax != 0.0f) {
-            float q = __fdiv_rn(x[j], amax);
+            float q = __fdiv_rn(x.v[j], amax);
             if (tab.need_clamp) q = fminf(fmaxf(q, tab.cmin), tab.cmax);
             k = tab.perm[code_index<NC>(tab, q, use_lut)];
         }
-        idx[j] = k;
+        packed |= (unsigned long long)(unsigned)k << (8 * j);
     }
+    return packed;
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
@@ -181,13 +187,16 @@ __device__ __forceinline__ void load_vec(const T *p, float (&x)[EPL]) {
             x[j] = v.x; x[j + 1] = v.y; x[j + 2] = v.z; x[j + 3] = v.w;
         }
     } else {
-        if constexpr (EPL == 8) {
-            uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
-            unsigned w[4] = {v.x, v.y, v.z, v.w};
+        if constexpr (EPL >= 8) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                x[2 * j] = __uint_as_float(w[j] << 16);
-                x[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            for (int h = 0; h < EPL / 8; ++h) {
+                uint4 v = __ldg(reinterpret_cast<const uint4 *>(p + 8 * h));
+                unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    x[8 * h + 2 * j] = __uint_as_float(w[j] << 16);
+                    x[8 * h + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                }
             }
         } else {
             uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
@@ -201,7 +210,7 @@ __device__ __forceinline__ void load_vec(const T *p, float (&x)[EPL]) {
 // Quantize, vector path.  Requires n % EPL == 0 and vector-aligned buffers.
 // ------------------------------------------------------------------------------------
 template <typename T, int BITS, int EPL, int LPU>
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, (EPL == 16 ? 3 : 4))
 k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__restrict__ code,
                int n, int nb, float *__restrict__ absmax_base, long long stride_absmax,
                float *__restrict__ diag_base, long long stride_diag,
@@ -284,10 +293,27 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
                     for (int j = 0; j < EPL; ++j) idx[j] = 0;
                 }
             } else {
-                quantize_lane_generic<NC, EPL>(tab, x, amax, idx);
+                constexpr int PART = EPL > 8 ? 8 : EPL;
+#pragma unroll
+                for (int h = 0; h < EPL / PART; ++h) {
+                    LaneVals<PART> xv;
+#pragma unroll
+                    for (int j = 0; j < PART; ++j) xv.v[j] = x[h * PART + j];
+                    const unsigned long long pk = quantize_lane_generic<NC, PART>(tab, xv, amax);
+#pragma unroll
+                    for (int j = 0; j < PART; ++j) idx[h * PART + j] = (int)((pk >> (8 * j)) & 255u);
+                }
             }
             const long long e = (long long)r * n + c;         // flat element index, multiple of EPL
-            if constexpr (BITS == 4) {
+            if constexpr (BITS == 4 && EPL == 16) {
+                unsigned w0 = 0, w1 = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    w0 |= (unsigned)((idx[j] << 4) | idx[j + 1]) << (4 * j);
+                    w1 |= (unsigned)((idx[8 + j] << 4) | idx[8 + j + 1]) << (4 * j);
+                }
+                *reinterpret_cast<uint2 *>(out + (e >> 1)) = make_uint2(w0, w1);
+            } else if constexpr (BITS == 4) {
                 unsigned w = 0;
 #pragma unroll
                 for (int j = 0; j < EPL; j += 2)
@@ -590,6 +616,10 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
         if (n % 8 == 0 && ptr_ok8 && (!many || strides_ok8)) epl = 8;
         else if (n % 4 == 0 && ptr_ok4 && (!many || strides_ok4) && a.bs <= 128) epl = 4;
     }
+    // 4-bit, block 64 (the optimizers' configuration): 16 elements per lane, 4 lanes per block
+    if (BITS == 4 && a.bs == 64 && epl == 8 && n % 16 == 0 && aligned(a.out, 8) && (!many || a.stride_out % 8 == 0) &&
+        (!many || (a.strideA * (long long)esz) % 16 == 0))
+        epl = 16;
     if (epl) {
         const int lpu = a.bs / epl;
         const long long units = (long long)n * nb;
@@ -602,6 +632,7 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
 #define QT_LAUNCH_Q(E, L)                                                                          \
         k_quantize_vec<T, BITS, E, L><<<grid, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.absmax, \
             a.stride_absmax, a.diag, a.stride_diag, a.out, a.stride_out)
+        if constexpr (BITS == 4) { if (epl == 16) { QT_LAUNCH_Q(16, 4); count_launch(1); return; } }
         if (epl == 8 && lpu == 8) QT_LAUNCH_Q(8, 8);
         else if (epl == 8 && lpu == 16) QT_LAUNCH_Q(8, 16);
         else if (epl == 8 && lpu == 32) QT_LAUNCH_Q(8, 32);
