@@ -459,6 +459,7 @@ k_dequantize_vec(const unsigned char *__restrict__ in_base, long long stride_in,
     int t = blockIdx.x * kThreads + threadIdx.x;
     int r = t / chunks_per_row, cc = t - r * chunks_per_row;
     const int dr = S / chunks_per_row, dc = S - dr * chunks_per_row;
+#pragma unroll 4
     for (; t < chunks; t += S) {
         const int c = cc * EPL;
         const long long e = (long long)r * n + c;
