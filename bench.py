@@ -242,6 +242,7 @@ def run_ours(args):
     model = workloads.vit_base_patch32_224().to(device)
     params = [p for p in model.parameters()]
     kwargs = dict(HYPER)
+    kwargs["cuda_graph"] = not args.no_graph       # the step is replayed as one CUDA graph after the first step
     if world > 1:
         kwargs["process_group"] = dist.group.WORLD
     opt = ShampooAdamW(params, **kwargs)
@@ -321,6 +322,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "f32 arithmetic on 4-bit state", "data": "synthetic",
             "config": {"workload": WORKLOAD, "gradients": "one bf16-autocast cross-entropy backward, batch 256 per GPU of "
                        "N(0,1) 224x224 images, uniform labels (computed once, reused every step)",
+                       "execution": "eager" if args.no_graph else "whole step captured once per schedule phase and replayed as a CUDA graph (ShampooAdamW(cuda_graph=True))",
                        "l2": "per-step working set (4-bit state 130 MB + fp32 temporaries > 2 GB) exceeds the 126 MB L2",
                        "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in HYPER.items()}},
             "clocks": clocks.summary(),
@@ -342,6 +344,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of as a captured CUDA graph")
     ap.add_argument("--profile-case", default=None, choices=["quant", "gemm"],
                     help="run only one small kernel case (for an ncu capture) and print its rates")
     args = ap.parse_args()

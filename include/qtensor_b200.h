@@ -80,6 +80,11 @@ int qt_version(void);
  * Additive; the reference has no counterpart. */
 unsigned long long qt_launch_count(void);
 
+/* Accounting hook for callers that captured this library's launches in a CUDA graph: a replay
+ * launches the captured kernels again without passing through the library, so the caller
+ * reports how many of them one replay contained.  Additive; no counterpart in the reference. */
+void qt_note_graph_replay(unsigned long long kernels);
+
 /* Status of the most recent call made by this thread (legacy or qt_*), and its text.
  * Replaces the reference's fprintf + exit(1) (cudaC_python/csrc/ops.cuh:20-26). */
 int qt_last_error(void);

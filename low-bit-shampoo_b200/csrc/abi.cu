@@ -60,6 +60,7 @@ void cdequantize_blockwise_diagreal_4bit_fp32(unsigned char *A, float *code, int
 
 int qt_version(void) { return 100; }
 unsigned long long qt_launch_count(void) { return qt::g_launches.load(std::memory_order_relaxed); }
+void qt_note_graph_replay(unsigned long long kernels) { qt::count_launch((int)kernels); }
 int qt_last_error(void) { return tl_last_error; }
 const char *qt_error_string(int status) {
     switch (status) {

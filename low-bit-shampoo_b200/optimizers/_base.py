@@ -230,6 +230,8 @@ class _ShampooBase(optim.Optimizer):
         self._pg = process_group
         self._world, self._rank = 1, 0
         self._plans = {}
+        self._use_graph = False
+        self._graph_state = None
         if process_group is not None:
             import torch.distributed as dist
             self._world = dist.get_world_size(process_group)
@@ -367,8 +369,88 @@ class _ShampooBase(optim.Optimizer):
                     raise RuntimeError('Shampoo does not support sparse yet')
             if not params:
                 continue
+            fresh = any(len(self.state[p]) == 0 for p in params)
             self._create_states(group, params)
-            self._apply_update(group, params)
+            if self._use_graph and not fresh and self._graph_eligible(group, params):
+                self._graph_step(group, params)
+            else:
+                self._apply_update(group, params)
+
+    # ---- optional CUDA-graph execution of the step --------------------------------------
+    def enable_cuda_graph(self, on=True):
+        """Replay the whole step (statistics refresh, inverse roots, apply, exchange, AdamW tail)
+        as a CUDA graph.  One graph is captured per schedule phase (which intervals fire); the
+        first step is always eager (it creates state).  Gradients are copied into buffers owned
+        by the optimizer, so parameters' .grad tensors may change address between steps."""
+        self._use_graph = bool(on)
+        if not on:
+            self._graph_state = None
+
+    def _graph_eligible(self, group, params):
+        if len(self.param_groups) != 1 or not hasattr(self, "_graph_scalars"):
+            return False
+        if self.preconditioner_cls.flavour != "s2" or group.get('inv_root_mode', 0) != 0:
+            return False                                  # the Schur-Newton loop synchronises with the host
+        dev = params[0].device
+        if dev.type != "cuda" or any(p.device != dev or p.grad.dtype != torch.float32 for p in params):
+            return False
+        return len({self.state[p]['step'] for p in params}) == 1
+
+    def _graph_step(self, group, params):
+        gs = self._graph_state
+        ids = tuple(id(p) for p in params)
+        if gs is None or gs["ids"] != ids:
+            gs = self._graph_state = {
+                "ids": ids, "graphs": {},
+                "grads": [torch.empty_like(p.grad) for p in params],
+                "scalars": torch.zeros(2, device=params[0].device),
+                "host": torch.zeros(2).pin_memory(),
+            }
+        step = self.state[params[0]]['step'] + 1
+        fires_stat = step % group['stat_compute_steps'] == 0
+        fires_root = step % group['prec_compute_steps'] == 0
+        active = tuple(self.state[p]['preconditioner'].is_active() for p in params)
+        key = (fires_stat, fires_root, all(active), any(active), step >= group['start_prec_step'])
+        self._graph_scalars(group, step, gs["host"])
+        gs["scalars"].copy_(gs["host"], non_blocking=True)
+        torch._foreach_copy_(gs["grads"], [p.grad for p in params])
+        user_grads = [p.grad for p in params]
+        for p, g in zip(params, gs["grads"]):
+            p.grad = g
+        try:
+            entry = gs["graphs"].get(key)
+            if entry is None:
+                book = [(self.state[p]['step'], self.state[p]['preconditioner']._active) for p in params]
+                lib = F.lib
+                before = lib.qt_launch_count() if lib is not None else 0
+                graph = torch.cuda.CUDAGraph()
+                try:
+                    with torch.cuda.graph(graph):
+                        self._apply_update(group, params, scalars=gs["scalars"])
+                except Exception:
+                    for p, (st, act) in zip(params, book):      # capture failed: undo bookkeeping, go eager
+                        self.state[p]['step'] = st
+                        self.state[p]['preconditioner']._active = act
+                    self._use_graph = False
+                    self._graph_state = None
+                    self._apply_update(group, params)
+                    return
+                launches = (lib.qt_launch_count() - before) if lib is not None else 0
+                gs["graphs"][key] = (graph, launches)
+                graph.replay()
+            else:
+                graph, launches = entry
+                for p in params:                                # host-side bookkeeping of the captured step
+                    st = self.state[p]
+                    st['step'] += 1
+                    if fires_root:
+                        st['preconditioner']._active = True
+                graph.replay()
+                if F.lib is not None and launches:
+                    F.lib.qt_note_graph_replay(launches)
+        finally:
+            for p, g in zip(params, user_grads):
+                p.grad = g
 
 
 class ShampooSGDBase(_ShampooBase):
@@ -403,7 +485,8 @@ class ShampooAdamWBase(_ShampooBase):
     def __init__(self, params, lr=0.001, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
                  start_prec_step=1, stat_compute_steps=100, prec_compute_steps=500,
                  stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200,
-                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, process_group=None, **extra):
+                 prec_bits=32, min_lowbit_size=4096, quan_blocksize=64, process_group=None, cuda_graph=False,
+                 **extra):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                         start_prec_step=start_prec_step, stat_compute_steps=stat_compute_steps,
                         prec_compute_steps=prec_compute_steps, stat_decay=stat_decay, matrix_eps=matrix_eps,
@@ -411,12 +494,20 @@ class ShampooAdamWBase(_ShampooBase):
                         quan_blocksize=quan_blocksize, **extra)
         super().__init__(params, defaults)
         self._setup(prec_bits, process_group)
+        self._use_graph = bool(cuda_graph)
 
     def _init_moments(self, p, state):
         state['exp_avg'] = torch.zeros_like(p, memory_format=torch.preserve_format)
         state['exp_avg_sq'] = torch.zeros_like(p, memory_format=torch.preserve_format)
 
-    def _apply_update(self, group, params):
+    def _graph_scalars(self, group, step, out):
+        """Step-dependent scalars of the tail, written where a captured graph reads them:
+        out[0] = 1 / sqrt(1 - beta2^t), out[1] = -lr / (1 - beta1^t)."""
+        beta1, beta2 = group['betas']
+        out[0] = 1.0 / math.sqrt(1 - beta2 ** step)
+        out[1] = -(group['lr'] / (1 - beta1 ** step))
+
+    def _apply_update(self, group, params, scalars=None):
         # decoupled weight decay first, as in the reference (shampoo2.py:441)
         torch._foreach_mul_(params, 1 - group['lr'] * group['weight_decay'])
         directions = self._precondition(group, params)
@@ -436,6 +527,13 @@ class ShampooAdamWBase(_ShampooBase):
             torch._foreach_mul_(m2, beta2)
             torch._foreach_addcmul_(m2, ds, ds, value=1 - beta2)
             denom = torch._foreach_sqrt(m2)
-            torch._foreach_div_(denom, math.sqrt(bc2))
-            torch._foreach_add_(denom, group['eps'])
-            torch._foreach_addcdiv_(ps, m1, denom, value=-(group['lr'] / bc1))
+            if scalars is None:
+                torch._foreach_div_(denom, math.sqrt(bc2))
+                torch._foreach_add_(denom, group['eps'])
+                torch._foreach_addcdiv_(ps, m1, denom, value=-(group['lr'] / bc1))
+            else:                                           # captured graph: scalars live on the device
+                torch._foreach_mul_(denom, scalars[0])
+                torch._foreach_add_(denom, group['eps'])
+                upd = torch._foreach_div(m1, denom)
+                torch._foreach_mul_(upd, scalars[1])
+                torch._foreach_add_(ps, upd)

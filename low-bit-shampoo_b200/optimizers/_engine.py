@@ -231,7 +231,7 @@ def op_ema_gram(L, G, axis, w1, w2):
 def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
     quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
-    V = householder_q(mm(L, Vt, trans_b=True).f32)
+    V = householder_q(mm(L, Vt, trans_b=True).f32, tensor_cores=_tc(L.f32))
     LV = mm(L, Mat(V), exact=True).f32          # Rayleigh quotients need fp32 (see op_ema_gram)
     eigs = (LV * V).sum(dim=1)
     return V, eigs
@@ -267,6 +267,19 @@ def _gather_rows(Vt, idx):
     return torch.gather(Vt, 1, idx.unsqueeze(2).expand(-1, -1, n))
 
 
+_INDEX_CACHE = {}
+
+
+def _index_tensor(ks, device):
+    """Device copy of a small index list, cached: the same lists recur every step, and a
+    host-to-device copy is not allowed while a CUDA graph is being captured."""
+    key = (str(device), tuple(ks))
+    t = _INDEX_CACHE.get(key)
+    if t is None:
+        t = _INDEX_CACHE[key] = torch.tensor(ks, device=device)
+    return t
+
+
 def _ema_update(L, grads_axes, w1, w2):
     """L[k] <- w1 L[k] + w2 * (G_k G_k^T | G_k^T G_k); blocks of equal shape are stacked."""
     groups = defaultdict(list)
@@ -277,7 +290,7 @@ def _ema_update(L, grads_axes, w1, w2):
         if len(ks) == L.shape[0]:
             L = op_ema_gram(L, Gs, axis, w1, w2)
         else:
-            sel = torch.tensor(ks, device=L.device)
+            sel = _index_tensor(ks, L.device)
             L[sel] = op_ema_gram(L[sel], Gs, axis, w1, w2)
     return L
 

@@ -58,16 +58,17 @@ def _merge_t(Vo, Tp, widths):
     return T
 
 
-def householder_q(X):
-    """Q of the QR factorisation of each X[b] (X: (B, n, n) fp32 CUDA, overwritten)."""
+def householder_q(X, tensor_cores=True):
+    """Q of the QR factorisation of each X[b] (X: (B, n, n) fp32 CUDA, overwritten).
+    `tensor_cores=False` keeps every product in fp32."""
     B, n, _ = X.shape
-    if (not X.is_cuda) or n > MAX_ORDER or n < 2 * PANEL:
+    if (not X.is_cuda) or n > MAX_ORDER or n < 2:
         return torch.linalg.qr(X).Q
     F._require_lib(X)
     X = X.contiguous()
     lib = F.lib
     from optimizers import _gemm
-    tc = USE_TENSOR_CORES
+    tc = USE_TENSOR_CORES and tensor_cores
     npan = (n + PANEL - 1) // PANEL
     V = torch.zeros(B, n, n, dtype=torch.float32, device=X.device)
     T = torch.empty(B, npan, PANEL, PANEL, dtype=torch.float32, device=X.device)

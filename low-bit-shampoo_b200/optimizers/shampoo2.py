@@ -45,10 +45,10 @@ class ShampooAdamW(ShampooAdamWBase):
                  start_prec_step=1, stat_compute_steps=100, prec_compute_steps=500,
                  stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200,
                  prec_bits=32, min_lowbit_size=4096, quan_blocksize=64,
-                 rect_t1=1, rect_t2=4, inv_root_mode=0, process_group=None):
+                 rect_t1=1, rect_t2=4, inv_root_mode=0, process_group=None, cuda_graph=False):
         super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                          start_prec_step=start_prec_step, stat_compute_steps=stat_compute_steps,
                          prec_compute_steps=prec_compute_steps, stat_decay=stat_decay, matrix_eps=matrix_eps,
                          prec_maxorder=prec_maxorder, prec_bits=prec_bits, min_lowbit_size=min_lowbit_size,
                          quan_blocksize=quan_blocksize, rect_t1=rect_t1, rect_t2=rect_t2, inv_root_mode=inv_root_mode,
-                         process_group=process_group)
+                         process_group=process_group, cuda_graph=cuda_graph)

@@ -20,7 +20,7 @@ LEGACY_SYMBOLS = tuple(
     for dt in ("fp32", "bf16")
 )
 EXTRA_SYMBOLS = (
-    "qt_version", "qt_launch_count", "qt_last_error", "qt_error_string", "qt_set_stream",
+    "qt_version", "qt_launch_count", "qt_note_graph_replay", "qt_last_error", "qt_error_string", "qt_set_stream",
     "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_householder_panel", "qt_selftest_division", "qt_split_bf16", "qt_gemm_bf16x3", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error",
 )
 
@@ -36,6 +36,8 @@ def _declare(lib):
     lib.qt_version.restype = i32
     lib.qt_last_error.restype = i32
     lib.qt_launch_count.restype = ct.c_ulonglong
+    lib.qt_note_graph_replay.restype = None
+    lib.qt_note_graph_replay.argtypes = [ct.c_ulonglong]
     lib.qt_error_string.restype = ct.c_char_p
     lib.qt_error_string.argtypes = [i32]
     lib.qt_set_stream.restype = None

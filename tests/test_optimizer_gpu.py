@@ -90,3 +90,28 @@ def test_rank_deficient_statistics_stay_finite(native_lib):
             assert torch.isfinite(q.dequantize()).all()
         for s in pre.statistics:
             assert torch.isfinite(s.Svalue).all() and float(s.Svalue.min()) > -1e-6 * float(s.max_eigenvalue)
+
+
+def test_cuda_graph_step_equals_eager_step(native_lib):
+    """Optional graph replay of the whole step: same parameters as the eager step, while the
+    parameters' .grad tensors are re-created every step and the schedule alternates phases."""
+    from optimizers.shampoo2 import ShampooAdamW
+    shapes = [(192, 128), (128,), (96, 320), (64, 64), (1, 1, 48)]
+    hyper = dict(lr=1e-2, weight_decay=0.05, prec_bits=4, stat_compute_steps=1, prec_compute_steps=2)
+
+    def run(graph):
+        g = torch.Generator().manual_seed(5)
+        ps = [torch.nn.Parameter((torch.randn(s, generator=g) * 0.3).cuda()) for s in shapes]
+        opt = ShampooAdamW(ps, cuda_graph=graph, **hyper)
+        for step in range(6):
+            for p in ps:
+                p.grad = (torch.randn(p.shape, generator=g) * 0.1).cuda()     # new tensor every step
+            opt.step()
+        torch.cuda.synchronize()
+        return [p.detach().cpu() for p in ps], opt
+
+    eager, _ = run(False)
+    graphed, opt = run(True)
+    assert opt._graph_state is not None and len(opt._graph_state["graphs"]) >= 2
+    for a, b in zip(graphed, eager):
+        assert float((a - b).norm() / b.norm()) < 1e-5
