@@ -172,6 +172,22 @@ int qt_gemm_bf16x3(const void *Ahi, const void *Alo, long long lda, long long st
                    void *Dhi, void *Dlo, long long ldp, long long strideP, void *stream);
 
 /*
+ * Three-plane variants (hi, mid, lo: x = hi + mid + lo to 24 bits; six MMAs per k-slice): the
+ * same product at fp32-level accuracy (~1e-7 relative), for the two products of the hot path
+ * whose result must resolve eigenvalues down to 1e-7 of the largest one
+ * (beta L + (1-beta) G G^T, optimizers/shampoo2.py:188-199, and L V of the Rayleigh quotients,
+ * qtensor/utils.py:158).  Arguments as qt_split_bf16 / qt_gemm_bf16x3 with one more plane;
+ * only an fp32 D is produced.
+ */
+int qt_split_bf16_3(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                    void *hi, void *mid, void *lo, long long ldp, long long strideP, void *stream);
+int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long lda, long long strideA, int a_mn,
+                   const void *Bhi, const void *Bmid, const void *Blo, long long ldb, long long strideB, int b_mn,
+                   int M, int N, int K, int batch, float alpha, float beta,
+                   const float *C, long long ldc, long long strideC,
+                   float *D, long long ldd, long long strideD, void *stream);
+
+/*
  * D = alpha * op(A) * op(B) + beta * C for fp32 row-major operands in one call: splits both
  * operands into bf16 planes inside `scratch` (caller-owned device memory of at least
  * qt_matmul_f32_scratch_bytes(...) bytes), then runs qt_gemm_bf16x3.  op(A) is M x K

@@ -27,11 +27,12 @@
 
 namespace qt {
 
-static constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3;
+static constexpr int BM = 128, BN = 128, BK = 64;
 static constexpr int PLANE_TILE_BYTES = BM * BK * 2;                 // 16 KiB per plane tile
-static constexpr int STAGE_BYTES = 4 * PLANE_TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
+static constexpr int RING_BYTES = 12 * PLANE_TILE_BYTES;             // 3 stages x 4 tiles (two planes per operand)
+                                                                     // or 2 stages x 6 tiles (three planes)
 static constexpr int GEMM_THREADS = 192;
-static constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+static constexpr int GEMM_SMEM = RING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 static int g_gemm_sms = 0;
 static constexpr unsigned WAIT_LIMIT = 1u << 18;
 
@@ -125,11 +126,20 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
     return d;
 }
 
-template <bool A_MN, bool B_MN>
+// NP = planes per operand: 2 -> hi, lo (three products, ~1e-5); 3 -> hi, mid, lo (six products,
+// fp32-level accuracy).  Plane 0 is the most significant one.
+struct GemmMaps { CUtensorMap a[3]; CUtensorMap b[3]; };
+
+template <bool A_MN, bool B_MN, int NP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
-              const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo,
-              const GemmParams p) {
+k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+    constexpr int STAGES = NP == 2 ? 3 : 2;
+    constexpr int STAGE_BYTES = 2 * NP * PLANE_TILE_BYTES;
+    // The tensor core's fp32 accumulation truncates: its error grows linearly with the length of
+    // one accumulation chain (measured 6.5e-9 * K relative).  The three-plane variant therefore
+    // accumulates at most KC k-blocks (128 k) per TMEM accumulator and adds the partial sums in
+    // fp32 registers in the epilogue warps; the two-plane variant (1e-5 target) uses one chain.
+    constexpr int KC = NP == 3 ? 2 : 0;
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -179,22 +189,20 @@ k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant_
                     const unsigned stage = base + s * STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
                     const int k0 = kb * BK;
-                    if (!A_MN) {
-                        tma_load_3d(stage, &mapAhi, full_bar(s), k0, m0, b);
-                        tma_load_3d(stage + PLANE_TILE_BYTES, &mapAlo, full_bar(s), k0, m0, b);
-                    } else {
-                        for (int h = 0; h < 2; ++h) {
-                            tma_load_3d(stage + h * (PLANE_TILE_BYTES / 2), &mapAhi, full_bar(s), m0 + 64 * h, k0, b);
-                            tma_load_3d(stage + PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapAlo, full_bar(s), m0 + 64 * h, k0, b);
+#pragma unroll
+                    for (int pl = 0; pl < NP; ++pl) {
+                        const unsigned ta = stage + pl * PLANE_TILE_BYTES, tb = stage + (NP + pl) * PLANE_TILE_BYTES;
+                        if (!A_MN) {
+                            tma_load_3d(ta, &maps.a[pl], full_bar(s), k0, m0, b);
+                        } else {
+                            tma_load_3d(ta, &maps.a[pl], full_bar(s), m0, k0, b);
+                            tma_load_3d(ta + PLANE_TILE_BYTES / 2, &maps.a[pl], full_bar(s), m0 + 64, k0, b);
                         }
-                    }
-                    if (!B_MN) {
-                        tma_load_3d(stage + 2 * PLANE_TILE_BYTES, &mapBhi, full_bar(s), k0, n0, b);
-                        tma_load_3d(stage + 3 * PLANE_TILE_BYTES, &mapBlo, full_bar(s), k0, n0, b);
-                    } else {
-                        for (int h = 0; h < 2; ++h) {
-                            tma_load_3d(stage + 2 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBhi, full_bar(s), n0 + 64 * h, k0, b);
-                            tma_load_3d(stage + 3 * PLANE_TILE_BYTES + h * (PLANE_TILE_BYTES / 2), &mapBlo, full_bar(s), n0 + 64 * h, k0, b);
+                        if (!B_MN) {
+                            tma_load_3d(tb, &maps.b[pl], full_bar(s), k0, n0, b);
+                        } else {
+                            tma_load_3d(tb, &maps.b[pl], full_bar(s), n0, k0, b);
+                            tma_load_3d(tb + PLANE_TILE_BYTES / 2, &maps.b[pl], full_bar(s), n0 + 64, k0, b);
                         }
                     }
                 }
@@ -209,39 +217,53 @@ k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant_
             // descriptors differ only in their 14-bit start-address field: build one per operand
             // plane for stage 0, k-slice 0 and add (byte offset >> 4) afterwards
             const unsigned a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
-            const unsigned long long dA_hi = smem_desc(base, a_lbo, 1024u);
-            const unsigned long long dA_lo = smem_desc(base + PLANE_TILE_BYTES, a_lbo, 1024u);
-            const unsigned long long dB_hi = smem_desc(base + 2 * PLANE_TILE_BYTES, b_lbo, 1024u);
-            const unsigned long long dB_lo = smem_desc(base + 3 * PLANE_TILE_BYTES, b_lbo, 1024u);
+            unsigned long long dA[NP], dB[NP];
+#pragma unroll
+            for (int pl = 0; pl < NP; ++pl) {
+                dA[pl] = smem_desc(base + pl * PLANE_TILE_BYTES, a_lbo, 1024u);
+                dB[pl] = smem_desc(base + (NP + pl) * PLANE_TILE_BYTES, b_lbo, 1024u);
+            }
             constexpr unsigned a_step = (A_MN ? 2048u : 32u) >> 4, b_step = (B_MN ? 2048u : 32u) >> 4;
             unsigned it = 0;
             bool ok = true;
-            int i = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
-                const int acc = i & 1;
-                ok = mbar_wait(acc_empty(acc), ((i >> 1) & 1) ^ 1, abort_flag);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
+            int j = 0;                                      // accumulator hand-offs so far
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int nchunks = KC ? (num_kb + KC - 1) / KC : 1;
+                int kb = 0;
+                for (int ch = 0; ch < nchunks && ok; ++ch, ++j) {
+                    const int acc = j & 1;
+                    ok = mbar_wait(acc_empty(acc), ((j >> 1) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // K-major: 8-row groups 1024 B apart, a 16-element k-slice is 32 B further along the row.
-                    // MN-major: 64-wide MN chunks 8192 B apart (LBO), 8-k-row groups 1024 B apart, a k-slice is 2048 B further.
-                    const unsigned long long soff = (unsigned long long)((unsigned)(s * STAGE_BYTES) >> 4);
+                    const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
+                    const int kend = KC ? min(num_kb, kb + KC) : num_kb;
+                    for (bool fresh = true; kb < kend; ++kb, ++it, fresh = false) {
+                        const int s = it % STAGES;
+                        ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        // K-major: 8-row groups 1024 B apart, a 16-element k-slice is 32 B further along the row.
+                        // MN-major: 64-wide MN chunks 8192 B apart (LBO), 8-k-row groups 1024 B apart, a k-slice is 2048 B further.
+                        const unsigned long long soff = (unsigned long long)((unsigned)(s * STAGE_BYTES) >> 4);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        const unsigned long long a_hi = dA_hi + soff + k * a_step, a_lo = dA_lo + soff + k * a_step;
-                        const unsigned long long b_hi = dB_hi + soff + k * b_step, b_lo = dB_lo + soff + k * b_step;
-                        umma_bf16(tmem_acc, a_lo, b_hi, idesc, (kb | k) ? 1u : 0u);
-                        umma_bf16(tmem_acc, a_hi, b_lo, idesc, 1u);
-                        umma_bf16(tmem_acc, a_hi, b_hi, idesc, 1u);
+                        for (int k = 0; k < BK / 16; ++k) {
+                            const unsigned long long ao = soff + k * a_step, bo = soff + k * b_step;
+                            // every pair of planes whose combined significance is above the dropped
+                            // residual: index sum <= NP - 1, least significant pairs first
+                            bool first = fresh && k == 0;
+#pragma unroll
+                            for (int sum = NP - 1; sum >= 0; --sum) {
+#pragma unroll
+                                for (int ia = 0; ia <= sum; ++ia) {
+                                    umma_bf16(tmem_acc, dA[ia] + ao, dB[sum - ia] + bo, idesc, first ? 0u : 1u);
+                                    first = false;
+                                }
+                            }
+                        }
+                        umma_commit(empty_bar(s));
                     }
-                    umma_commit(empty_bar(s));
+                    if (ok) umma_commit(acc_full(acc));
                 }
-                if (ok) umma_commit(acc_full(acc));
             }
         }
     } else {
@@ -256,6 +278,59 @@ k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant_
                             ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 15) == 0 &&
                             ((p.ldp | p.strideP) & 7) == 0 &&
                             ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dlo)) & 15) == 0;
+        if constexpr (KC > 0) {
+            // chunked accumulation: partial sums of KC k-blocks are added in registers
+            int j = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                const int tn = tile % p.tiles_n, tm = (tile / p.tiles_n) % p.tiles_m, b = tile / (p.tiles_n * p.tiles_m);
+                const int m0 = tm * BM, n0 = tn * BN;
+                const int row = m0 + warp * 32 + lane;
+                const bool row_ok = row < p.M;
+                float sum[BN];
+#pragma unroll
+                for (int q = 0; q < BN; ++q) sum[q] = 0.0f;
+                const int nchunks = (num_kb + KC - 1) / KC;
+                bool ok = true;
+                for (int ch = 0; ch < nchunks; ++ch, ++j) {
+                    const int acc = j & 1;
+                    ok = mbar_wait_warp(acc_full(acc), (j >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
+#pragma unroll
+                    for (int c = 0; c < BN / 32; ++c) {
+                        float v[32];
+                        tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(c * 32), v);
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
+                }
+                if (!ok) break;
+                if (row_ok && p.D) {
+                    const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
+                    float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + n0;
+                    const int valid = min(BN, p.N - n0);
+#pragma unroll
+                    for (int q = 0; q < BN; q += 4) {
+                        if (vec_ok && q + 4 <= valid) {
+                            float4 cval = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (has_c) cval = __ldg(reinterpret_cast<const float4 *>(crow + q));
+                            *reinterpret_cast<float4 *>(drow + q) =
+                                make_float4(fmaf(p.beta, cval.x, p.alpha * sum[q]), fmaf(p.beta, cval.y, p.alpha * sum[q + 1]),
+                                            fmaf(p.beta, cval.z, p.alpha * sum[q + 2]), fmaf(p.beta, cval.w, p.alpha * sum[q + 3]));
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (q + t < valid)
+                                    drow[q + t] = fmaf(p.beta, has_c ? __ldg(crow + q + t) : 0.0f, p.alpha * sum[q + t]);
+                        }
+                    }
+                }
+            }
+        } else {
         int i = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
             const int tn = tile % p.tiles_n, tm = (tile / p.tiles_n) % p.tiles_m, b = tile / (p.tiles_n * p.tiles_m);
@@ -341,6 +416,7 @@ k_gemm_bf16x3(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant_
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
+        }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
@@ -453,6 +529,41 @@ int launch_split_bf16(const float *X, long long ldx, long long strideX, int rows
     return check_launch();
 }
 
+// fp32 -> three bf16 planes (hi, mid, lo): x = hi + mid + lo to 24 bits.
+__global__ void __launch_bounds__(256)
+k_split_bf16_3(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
+               __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ mid, __nv_bfloat16 *__restrict__ lo,
+               long long ldp, long long strideP) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    const long long po = (long long)b * strideP;
+    const long long total = (long long)rows * cols;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / cols), c = (int)(e - (long long)r * cols);
+        const float v = x[(long long)r * ldx + c];
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        const float r1 = v - __bfloat162float(h);
+        const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+        const long long o = po + (long long)r * ldp + c;
+        hi[o] = h; mid[o] = m; lo[o] = __float2bfloat16_rn(r1 - __bfloat162float(m));
+    }
+}
+
+int launch_split_bf16_3(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                        void *hi, void *mid, void *lo, long long ldp, long long strideP, cudaStream_t s) {
+    if (rows < 0 || cols < 0 || batch < 0 || batch > 65535) return record(QT_ERR_ARG);
+    if (rows == 0 || cols == 0 || batch == 0) return record(QT_OK);
+    if (!X || !hi || !mid || !lo || ldx < cols || ldp < cols) return record(QT_ERR_ARG);
+    long long ctas = ((long long)rows * cols + 1023) / 1024;
+    const long long cap = (148LL * 32 + batch - 1) / batch;
+    if (ctas > cap) ctas = cap;
+    dim3 grid((unsigned)(ctas < 1 ? 1 : ctas), batch);
+    k_split_bf16_3<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, static_cast<__nv_bfloat16 *>(hi),
+                                         static_cast<__nv_bfloat16 *>(mid), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    count_launch(1);
+    return check_launch();
+}
+
 struct GemmArgs {
     const void *Ahi, *Alo; long long lda, strideA; int a_mn;
     const void *Bhi, *Blo; long long ldb, strideB; int b_mn;
@@ -464,30 +575,28 @@ struct GemmArgs {
 
 static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) {
+// a.Ahi/Alo (+ amid/bmid for three planes: order hi, mid, lo).
+int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cudaStream_t s) {
+    const int np = (Amid && Bmid) ? 3 : 2;
     if (a.M < 0 || a.N < 0 || a.K < 0 || a.batch < 0) return record(QT_ERR_ARG);
     if (a.M == 0 || a.N == 0 || a.batch == 0) return record(QT_OK);
     if (a.K == 0) return record(QT_ERR_UNSUPPORTED);
     if (!a.Ahi || !a.Alo || !a.Bhi || !a.Blo || (!a.D && !a.Dhi)) return record(QT_ERR_ARG);
-    if ((a.Dhi == nullptr) != (a.Dlo == nullptr)) return record(QT_ERR_ARG);
+    if ((a.Dhi == nullptr) != (a.Dlo == nullptr) || (Amid == nullptr) != (Bmid == nullptr)) return record(QT_ERR_ARG);
+    const void *Ap[3] = {a.Ahi, np == 3 ? Amid : a.Alo, a.Alo};
+    const void *Bp[3] = {a.Bhi, np == 3 ? Bmid : a.Blo, a.Blo};
     // TMA: 16-byte aligned bases, row pitches and batch strides
-    if (!al16(a.Ahi) || !al16(a.Alo) || !al16(a.Bhi) || !al16(a.Blo)) return record(QT_ERR_ARG);
+    for (int i = 0; i < np; ++i)
+        if (!al16(Ap[i]) || !al16(Bp[i])) return record(QT_ERR_ARG);
     if (a.lda % 8 || a.ldb % 8 || a.strideA % 8 || a.strideB % 8) return record(QT_ERR_ARG);
-    CUtensorMap mAhi, mAlo, mBhi, mBlo;
+    GemmMaps maps;
     bool ok = true;
-    if (!a.a_mn) {       // stored [M][K]
-        ok = ok && make_map(&mAhi, a.Ahi, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);
-        ok = ok && make_map(&mAlo, a.Alo, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);
-    } else {             // stored [K][M]
-        ok = ok && make_map(&mAhi, a.Ahi, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);
-        ok = ok && make_map(&mAlo, a.Alo, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);
-    }
-    if (!a.b_mn) {       // stored [N][K]
-        ok = ok && make_map(&mBhi, a.Bhi, a.K, a.N, a.batch, a.ldb, a.strideB, BK, BN);
-        ok = ok && make_map(&mBlo, a.Blo, a.K, a.N, a.batch, a.ldb, a.strideB, BK, BN);
-    } else {             // stored [K][N]
-        ok = ok && make_map(&mBhi, a.Bhi, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);
-        ok = ok && make_map(&mBlo, a.Blo, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);
+    for (int i = 0; i < 3; ++i) {
+        const void *pa = Ap[i < np ? i : 0], *pb = Bp[i < np ? i : 0];
+        if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);   // stored [M][K]
+        else         ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);   // stored [K][M]
+        if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, a.batch, a.ldb, a.strideB, BK, BN);   // stored [N][K]
+        else         ok = ok && make_map(&maps.b[i], pb, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);   // stored [K][N]
     }
     if (!ok) return record(QT_ERR_LAUNCH);
     GemmParams p;
@@ -498,13 +607,16 @@ int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) {
     p.tiles_m = (a.M + BM - 1) / BM; p.tiles_n = (a.N + BN - 1) / BN;
     const long long ctas = (long long)p.tiles_m * p.tiles_n * a.batch;
     if (ctas > 0x7fffffffLL) return record(QT_ERR_UNSUPPORTED);
+    typedef void (*Kern)(const GemmMaps, const GemmParams);
+    static const Kern kernels[2][2][2] = {
+        {{k_gemm_bf16x3<false, false, 2>, k_gemm_bf16x3<false, true, 2>}, {k_gemm_bf16x3<true, false, 2>, k_gemm_bf16x3<true, true, 2>}},
+        {{k_gemm_bf16x3<false, false, 3>, k_gemm_bf16x3<false, true, 3>}, {k_gemm_bf16x3<true, false, 3>, k_gemm_bf16x3<true, true, 3>}}};
     static bool attr_done = false;
     if (!attr_done) {
-        bool good = cudaFuncSetAttribute(k_gemm_bf16x3<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
-        good = good && cudaFuncSetAttribute(k_gemm_bf16x3<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
-        good = good && cudaFuncSetAttribute(k_gemm_bf16x3<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
-        good = good && cudaFuncSetAttribute(k_gemm_bf16x3<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) == cudaSuccess;
-        if (!good) return record(QT_ERR_LAUNCH);
+        for (int i = 0; i < 8; ++i)
+            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(kernels[i >> 2][(i >> 1) & 1][i & 1]),
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
+                return record(QT_ERR_LAUNCH);
         attr_done = true;
     }
     if (g_gemm_sms == 0) {
@@ -514,13 +626,12 @@ int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) {
         g_gemm_sms = n;
     }
     const unsigned grid = (unsigned)(ctas < g_gemm_sms ? ctas : g_gemm_sms);     // persistent: one CTA per SM
-    if (!a.a_mn && !a.b_mn) k_gemm_bf16x3<false, false><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
-    else if (!a.a_mn && a.b_mn) k_gemm_bf16x3<false, true><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
-    else if (a.a_mn && !a.b_mn) k_gemm_bf16x3<true, false><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
-    else k_gemm_bf16x3<true, true><<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(mAhi, mAlo, mBhi, mBlo, p);
+    kernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
     count_launch(1);
     return check_launch();
 }
+
+int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) { return launch_gemm_planes(a, nullptr, nullptr, s); }
 
 // fp32 operands in, fp32 out: both operands are split into bf16 planes inside `scratch`
 // (global memory owned by the caller), then multiplied on the tensor cores.
@@ -640,6 +751,22 @@ int qt_gemm_bf16x3(const void *Ahi, const void *Alo, long long lda, long long st
     GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, M, N, K, batch, alpha, beta,
                C, ldc, strideC, D, ldd, strideD, Dhi, Dlo, ldp, strideP};
     return launch_gemm_bf16x3(a, static_cast<cudaStream_t>(stream));
+}
+
+int qt_split_bf16_3(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                    void *hi, void *mid, void *lo, long long ldp, long long strideP, void *stream) {
+    return launch_split_bf16_3(X, ldx, strideX, rows, cols, batch, hi, mid, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
+}
+
+int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long lda, long long strideA, int a_mn,
+                   const void *Bhi, const void *Bmid, const void *Blo, long long ldb, long long strideB, int b_mn,
+                   int M, int N, int K, int batch, float alpha, float beta,
+                   const float *C, long long ldc, long long strideC,
+                   float *D, long long ldd, long long strideD, void *stream) {
+    if (!Amid || !Bmid) return record(QT_ERR_ARG);
+    GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, M, N, K, batch, alpha, beta,
+               C, ldc, strideC, D, ldd, strideD, nullptr, nullptr, 0, 0};
+    return launch_gemm_planes(a, Amid, Bmid, static_cast<cudaStream_t>(stream));
 }
 
 unsigned long long qt_matmul_f32_scratch_bytes(int M, int N, int K, int batch, int trans_a, int trans_b) {

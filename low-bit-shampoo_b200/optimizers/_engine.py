@@ -176,6 +176,13 @@ class Mat:
         self.f32, self._planes = f32, planes
 
     @property
+    def planes3(self):
+        if getattr(self, "_planes3", None) is None:
+            x = self.f32 if self.f32.stride(2) == 1 else self.f32.contiguous()
+            self._planes3 = _gemm.split3(x)
+        return self._planes3
+
+    @property
     def planes(self):
         if self._planes is None:
             x = self.f32 if self.f32.stride(2) == 1 else self.f32.contiguous()
@@ -192,6 +199,10 @@ def mm(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, want_flo
     """alpha * op(A) @ op(B) + beta * C over a batch; A, B are Mat, C an fp32 tensor.
     `exact` forces an fp32 product (operands must then be available as fp32)."""
     ref = A.f32 if A.f32 is not None else A._planes.hi
+    if exact and _tc(ref) and A.f32 is not None and B.f32 is not None:
+        # fp32-level accuracy on the tensor cores: three bf16 planes per operand, six MMAs per k-slice
+        D, _ = _gemm.matmul(A.planes3, B.planes3, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C)
+        return Mat(D)
     if _tc(ref) and not exact:
         D, P = _gemm.matmul(A.planes, B.planes, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C,
                             want_float=want_float, want_planes=want_planes)

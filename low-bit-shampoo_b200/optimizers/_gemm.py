@@ -25,16 +25,19 @@ class Planes:
 
     `offset` (elements) selects a sub-matrix of a parent's storage: window() shares memory."""
 
-    def __init__(self, batch, rows, cols, device, _share=None):
+    def __init__(self, batch, rows, cols, device, _share=None, planes=2):
         self.batch, self.rows, self.cols = batch, rows, cols
+        self.mid = None
         if _share is not None:
             self.hi, self.lo, self.ld, self.stride, self.offset = _share
             return
         self.ld = _pitch(cols)
         self.stride = rows * self.ld
         self.offset = 0
-        buf = torch.empty(2, batch, self.stride, dtype=torch.bfloat16, device=device)
-        self.hi, self.lo = buf[0], buf[1]
+        buf = torch.empty(planes, batch, self.stride, dtype=torch.bfloat16, device=device)
+        self.hi, self.lo = buf[0], buf[planes - 1]
+        if planes == 3:
+            self.mid = buf[1]
 
     def window(self, row0, col0, rows, cols):
         """Planes of the sub-matrix [row0:row0+rows, col0:col0+cols]; col0 must be a multiple of 8."""
@@ -54,6 +57,18 @@ class Planes:
         full = torch.zeros(self.batch, self.rows * self.ld, device=idx.device)
         full[:, :n] = idx
         return full.view(self.batch, self.rows, self.ld)[:, :, : self.cols]
+
+
+def split3(X):
+    """fp32 (batch, rows, cols) tensor -> three-plane Planes (hi, mid, lo; 24 significant bits)."""
+    assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
+    b, r, c = X.shape
+    P = Planes(b, r, c, X.device, planes=3)
+    with torch.cuda.device(X.device):
+        rc = F.lib.qt_split_bf16_3(_ptr(X), X.stride(1), X.stride(0), r, c, b, P.ptr_hi(), _ptr(P.mid), P.ptr_lo(),
+                                   P.ld, P.stride, F._stream(X))
+    F._check(rc, "split_bf16_3")
+    return P
 
 
 def split(X):
@@ -94,6 +109,17 @@ def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=
     # kernel view: A logically M x K (a_mn: stored [K][M]); B logically N x K (b_mn: stored [K][N])
     a_mn = 1 if trans_a else 0
     b_mn = 0 if trans_b else 1
+    if A.mid is not None or B.mid is not None:
+        assert A.mid is not None and B.mid is not None and P is None and D is not None
+        with torch.cuda.device(dev):
+            rc = F.lib.qt_gemm_bf16x6(
+                A.ptr_hi(), _ptr(A.mid), A.ptr_lo(), A.ld, A.stride, a_mn,
+                B.ptr_hi(), _ptr(B.mid), B.ptr_lo(), B.ld, B.stride, b_mn,
+                M, N, K, b, float(alpha), float(beta),
+                _ptr(C), C.stride(1) if C is not None else 0, C.stride(0) if C is not None else 0,
+                _ptr(D), D.stride(1), D.stride(0), F._stream(A.hi))
+        F._check(rc, "gemm_bf16x6")
+        return D, None
     with torch.cuda.device(dev):
         rc = F.lib.qt_gemm_bf16x3(
             A.ptr_hi(), A.ptr_lo(), A.ld, A.stride, a_mn,

@@ -81,3 +81,25 @@ def test_matmul_f32_entry_point_with_caller_scratch(native_lib, trans_a, trans_b
     # too little scratch is refused before anything is launched
     assert lib.qt_matmul_f32(P(A), A.stride(1), A.stride(0), int(trans_a), P(B), B.stride(1), B.stride(0), int(trans_b),
                              M, N, K, b, 1.0, 0.0, None, 0, 0, P(D), N, M * N, P(scratch), need - 4096, st) == 1
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (True, False), (False, False)])
+def test_three_plane_product_reaches_fp32_accuracy(native_lib, trans_a, trans_b):
+    """hi/mid/lo planes, six MMAs per k-slice: at least as accurate as an fp32 library product."""
+    from optimizers import _gemm
+    g = torch.Generator(device="cuda").manual_seed(31)
+    b, M, N, K = 2, 328, 264, 1200
+    A = torch.randn((b, K, M) if trans_a else (b, M, K), device="cuda", generator=g)
+    B = torch.randn((b, N, K) if trans_b else (b, K, N), device="cuda", generator=g)
+    C = torch.randn(b, M, N, device="cuda", generator=g)
+    D, _ = _gemm.matmul(_gemm.split3(A), _gemm.split3(B), trans_a=trans_a, trans_b=trans_b, alpha=0.05, beta=0.95, C=C)
+    assert device_ok(native_lib)
+    opA = A.transpose(1, 2) if trans_a else A
+    opB = B.transpose(1, 2) if trans_b else B
+    ref = 0.05 * (opA.double() @ opB.double()) + 0.95 * C.double()
+    fp32 = torch.baddbmm(C, opA, opB, beta=0.95, alpha=0.05)
+    assert rel(D, ref) < 2e-6, rel(D, ref)               # measured 8e-7, independent of K
+    assert rel(D, ref) < 4 * rel(fp32, ref) + 1e-6
+    P = _gemm.split3(A)
+    back = P.hi.float() + P.mid.float() + P.lo.float()
+    assert float((back.view(-1)[: A.numel()].view_as(A) - A).abs().max() / A.abs().max()) < 2.0 ** -22
