@@ -389,6 +389,8 @@ class _ShampooBase(optim.Optimizer):
     def _graph_eligible(self, group, params):
         if len(self.param_groups) != 1 or not hasattr(self, "_graph_scalars"):
             return False
+        if self._world > 1:
+            return False                                  # the all-gather is not captured: sharded steps run eagerly
         if self.preconditioner_cls.flavour != "s2" or group.get('inv_root_mode', 0) != 0:
             return False                                  # the Schur-Newton loop synchronises with the host
         dev = params[0].device
