@@ -115,3 +115,62 @@ def test_cuda_graph_step_equals_eager_step(native_lib):
     assert opt._graph_state is not None and len(opt._graph_state["graphs"]) >= 2
     for a, b in zip(graphed, eager):
         assert float((a - b).norm() / b.norm()) < 1e-5
+
+
+def _sharded_worker(rank, world, port, out):
+    import os
+    import sys
+    import torch.distributed as dist
+    from conftest import PKG, ROOT
+    for p in (ROOT, PKG):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from optimizers.shampoo2 import ShampooAdamW
+        shapes = [(256, 192), (192,), (128, 320), (64, 64), (96, 96)]
+        hyper = dict(lr=1e-2, weight_decay=0.05, prec_bits=4, stat_compute_steps=1, prec_compute_steps=1)
+
+        def run(group):
+            g = torch.Generator().manual_seed(9)
+            ps = [torch.nn.Parameter((torch.randn(s, generator=g) * 0.3).cuda()) for s in shapes]
+            opt = ShampooAdamW(ps, process_group=group, **hyper)
+            for _ in range(3):
+                for p in ps:
+                    p.grad = (torch.randn(p.shape, generator=g) * 0.1).cuda()
+                opt.step()
+            torch.cuda.synchronize()
+            return [p.detach().cpu() for p in ps]
+
+        sharded, single = run(dist.group.WORLD), run(None)
+        err = max(float((a - b).norm() / b.norm()) for a, b in zip(sharded, single))
+        out.put((rank, err))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_step_on_two_gpus_equals_single_gpu(native_lib):
+    """Owner-computes sharding + NCCL all-gather on two GPUs gives the single-GPU parameters.
+    (Skipped on a one-GPU machine; the same logic runs on CPU ranks in tests/test_sharding_cpu.py.)"""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_sharded_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err in results:
+        assert err < 1e-5, (rank, err)
