@@ -306,6 +306,34 @@ def _ema_update(L, grads_axes, w1, w2):
     return L
 
 
+PARALLEL_CLASSES = True        # order classes are independent: run them on separate CUDA streams
+_STREAMS = {}
+
+
+def _over_classes(by_class):
+    """Yields (cls, payload) for every order class; on CUDA each class is issued on one of a few
+    side streams so that the latency-bound work of small classes (a QR of 12 matrices is 35
+    sequential panel steps) overlaps with the other classes.  Joined back before returning."""
+    classes = sorted(by_class.items(), key=lambda kv: -(kv[0].n ** 3) * len(kv[1]))
+    dev = classes[0][0].device if classes else None
+    if not PARALLEL_CLASSES or len(classes) < 2 or dev is None or torch.device(dev).type != "cuda":
+        for cls, payload in classes:
+            yield cls, payload
+        return
+    pool = _STREAMS.get(str(dev))
+    if pool is None:
+        pool = _STREAMS[str(dev)] = [torch.cuda.Stream(device=dev) for _ in range(4)]
+    main = torch.cuda.current_stream(dev)
+    used = pool[: min(len(pool), len(classes))]
+    for s in used:
+        s.wait_stream(main)
+    for i, (cls, payload) in enumerate(classes):
+        with torch.cuda.stream(used[i % len(used)]):
+            yield cls, payload
+    for s in used:
+        main.wait_stream(s)
+
+
 def add_statistics(items, w1, w2, eps=1e-6, exact=False):
     """items: list of (OrderClass, slot, grad_block, axis).  Refreshes the statistics.
     `exact` keeps every product in fp32 (used when the inverse root is the Schur-Newton
@@ -313,7 +341,7 @@ def add_statistics(items, w1, w2, eps=1e-6, exact=False):
     by_class = defaultdict(list)
     for cls, slot, g, axis in items:
         by_class[cls].append((slot, g, axis))
-    for cls, entries in by_class.items():
+    for cls, entries in _over_classes(by_class):
         runs = _runs([e[0] for e in entries])
         for a, b, pos in _split_runs(runs, cls.sub_batch()):
           # the dense flavour re-quantises L itself and then runs the Newton iteration on it:
@@ -347,7 +375,7 @@ def compute_preconditioners(items, eps, inv_root_mode, exponent=4):
     by_class = defaultdict(list)
     for cls, slot in items:
         by_class[cls].append(slot)
-    for cls, slots in by_class.items():
+    for cls, slots in _over_classes(by_class):
         for a, b, _ in _split_runs(_runs(slots), cls.sub_batch()):
           with _exact((not cls.stat.lowbit) or cls.flavour == "s1" or inv_root_mode != 0):
             if cls.flavour == "s1":
