@@ -322,7 +322,7 @@ def _over_classes(by_class):
         return
     pool = _STREAMS.get(str(dev))
     if pool is None:
-        pool = _STREAMS[str(dev)] = [torch.cuda.Stream(device=dev) for _ in range(4)]
+        pool = _STREAMS[str(dev)] = [torch.cuda.Stream(device=dev) for _ in range(6)]
     main = torch.cuda.current_stream(dev)
     used = pool[: min(len(pool), len(classes))]
     for s in used:
