@@ -301,16 +301,15 @@ class _ShampooBase(optim.Optimizer):
             pre = state['preconditioner']
             if state['step'] % t1 == 0 and pre.statistics:
                 stat_items += pre.statistics_items(p.grad.data)
-        if stat_items:
-            E.add_statistics(stat_items, w1, w2, eps=group['matrix_eps'], exact=(group.get('inv_root_mode', 0) != 0))
         for p in params:
             state = self.state[p]
             pre = state['preconditioner']
             if state['step'] % t2 == 0:
                 root_items += pre._slots
                 pre._active = True
-        if root_items:
-            E.compute_preconditioners(root_items, group['matrix_eps'], group.get('inv_root_mode', 0))
+        if stat_items or root_items:
+            E.refresh(stat_items, root_items, w1, w2, group['matrix_eps'], group.get('inv_root_mode', 0),
+                      exact=(group.get('inv_root_mode', 0) != 0))
         directions = []
         for p in params:
             state = self.state[p]

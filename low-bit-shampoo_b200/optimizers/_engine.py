@@ -310,15 +310,17 @@ PARALLEL_CLASSES = True        # order classes are independent: run them on sepa
 _STREAMS = {}
 
 
-def _over_classes(by_class):
+def _over_classes(by_class, payload=None):
     """Yields (cls, payload) for every order class; on CUDA each class is issued on one of a few
     side streams so that the latency-bound work of small classes (a QR of 12 matrices is 35
     sequential panel steps) overlaps with the other classes.  Joined back before returning."""
     classes = sorted(by_class.items(), key=lambda kv: -(kv[0].n ** 3) * len(kv[1]))
     dev = classes[0][0].device if classes else None
+    if payload is not None:
+        classes = [(cls, payload[cls]) for cls, _ in classes]
     if not PARALLEL_CLASSES or len(classes) < 2 or dev is None or torch.device(dev).type != "cuda":
-        for cls, payload in classes:
-            yield cls, payload
+        for cls, item in classes:
+            yield cls, item
         return
     pool = _STREAMS.get(str(dev))
     if pool is None:
@@ -327,9 +329,9 @@ def _over_classes(by_class):
     used = pool[: min(len(pool), len(classes))]
     for s in used:
         s.wait_stream(main)
-    for i, (cls, payload) in enumerate(classes):
+    for i, (cls, item) in enumerate(classes):
         with torch.cuda.stream(used[i % len(used)]):
-            yield cls, payload
+            yield cls, item
     for s in used:
         main.wait_stream(s)
 
@@ -342,6 +344,10 @@ def add_statistics(items, w1, w2, eps=1e-6, exact=False):
     for cls, slot, g, axis in items:
         by_class[cls].append((slot, g, axis))
     for cls, entries in _over_classes(by_class):
+        _class_statistics(cls, entries, w1, w2, eps, exact)
+
+
+def _class_statistics(cls, entries, w1, w2, eps, exact):
         runs = _runs([e[0] for e in entries])
         for a, b, pos in _split_runs(runs, cls.sub_batch()):
           # the dense flavour re-quantises L itself and then runs the Newton iteration on it:
@@ -376,6 +382,27 @@ def compute_preconditioners(items, eps, inv_root_mode, exponent=4):
     for cls, slot in items:
         by_class[cls].append(slot)
     for cls, slots in _over_classes(by_class):
+        _class_roots(cls, slots, eps, inv_root_mode, exponent)
+
+
+def refresh(stat_items, root_items, w1, w2, eps, inv_root_mode, exact=False, exponent=4):
+    """add_statistics followed by compute_preconditioners, pipelined per order class: a class
+    starts its inverse roots as soon as its own statistics are done, on the same stream."""
+    stats, roots = defaultdict(list), defaultdict(list)
+    for cls, slot, g, axis in stat_items:
+        stats[cls].append((slot, g, axis))
+    for cls, slot in root_items:
+        roots[cls].append(slot)
+    merged = {cls: (stats.get(cls, []), roots.get(cls, [])) for cls in list(stats) + [c for c in roots if c not in stats]}
+    weight = {cls: (len(v[0]) + len(v[1])) for cls, v in merged.items()}
+    for cls, (entries, slots) in _over_classes({cls: [None] * weight[cls] for cls in merged}, payload=merged):
+        if entries:
+            _class_statistics(cls, entries, w1, w2, eps, exact)
+        if slots:
+            _class_roots(cls, slots, eps, inv_root_mode, exponent)
+
+
+def _class_roots(cls, slots, eps, inv_root_mode, exponent):
         for a, b, _ in _split_runs(_runs(slots), cls.sub_batch()):
           with _exact((not cls.stat.lowbit) or cls.flavour == "s1" or inv_root_mode != 0):
             if cls.flavour == "s1":
