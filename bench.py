@@ -296,6 +296,24 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / args.steps
 
+    # ---- steady-state step: no interval fires (the common step at T1=100, T2=500): only the
+    # preconditioned direction P_L G P_R, grafting, the exchange and the AdamW tail run
+    for g in opt.param_groups:
+        g['stat_compute_steps'] = g['prec_compute_steps'] = 10 ** 9
+    for _ in range(2):
+        opt.step()
+    barrier()
+    e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e4.record()
+    for _ in range(args.steps):
+        opt.step()
+    e5.record()
+    barrier()
+    t = torch.tensor([e4.elapsed_time(e5)], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    steady_ms = float(t.item()) / args.steps
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -328,6 +346,8 @@ def run_ours(args):
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": grad_bytes, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
+            "steady_state_step": {"value": steady_ms, "unit": "ms/step",
+                                  "what": "same optimizer with no interval firing (apply + grafting + AdamW tail only)"},
             "quant_gbs": qres["quantize"]["gbs"], "dequant_gbs": qres["dequantize"]["gbs"],
             "roofline": roof, "loss": loss}
     if world == 1:
