@@ -24,8 +24,7 @@
 
 namespace qt {
 
-static constexpr int kLutScale = 512;
-static constexpr int kLutCells = 2 * kLutScale + 1;
+static constexpr int kLutAlloc = 2048;        // cells allocated; the finest grid uses 2*512+1 of them
 static constexpr int kThreads = 256;
 
 // ------------------------------------------------------------------------------------
@@ -43,7 +42,13 @@ struct CodeTables {
     int lut_bad;
     int tiny_thr;             // some decision threshold has |t| < 2^-50: quotients must be exact even when tiny
     int thr_cell[NC];         // lookup-table cell of each threshold
-    float2 lut[NC == 16 ? kLutCells : 1];   // {threshold inside the cell or +inf, base index bits}
+    float lut_scale;          // cells per unit of q: 128 when that separates the thresholds, else 512
+    // One 32-bit word per cell of q in [-1, 1]: bits 31..4 = the threshold inside the cell (or +inf)
+    // with its low four mantissa bits cleared, bits 3..0 = number of thresholds in lower cells.
+    // A 4-byte cell halves the shared-memory wavefronts of a warp's 32 scattered lookups compared
+    // with {float threshold, int base}; the 16-ulp bucket around the threshold that the cleared bits
+    // cannot resolve is decided against the exact threshold (rare).
+    unsigned lut[NC == 16 ? kLutAlloc : 1];
 };
 
 __device__ __forceinline__ long long float_key(float f) {
@@ -54,9 +59,11 @@ __device__ __forceinline__ float key_float(long long k) {
     int i = (int)k;
     return __int_as_float(i >= 0 ? i : (i ^ 0x7fffffff));
 }
-__device__ __forceinline__ int lut_cell(float v) {
-    int c = __float2int_rz(fmaf(v, (float)kLutScale, (float)kLutScale));
-    return min(max(c, 0), 2 * kLutScale);
+// Cell of q in [-1, 1] on a grid of `scale` cells per unit: round(q*scale + scale), taken from the
+// mantissa of the sum with 2^23 (no float-to-int conversion).  Monotone in q, which is all the table
+// needs.  The caller masks the result with kLutAlloc-1, which also removes the exponent bits.
+__device__ __forceinline__ int lut_cell_raw(float v, float scale) {
+    return __float_as_int(fmaf(v, scale, scale + 8388608.0f));
 }
 
 template <int NC>
@@ -91,7 +98,6 @@ __device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) 
             if (up) b = m; else a = m;
         }
         t.thr[j] = key_float(b);
-        t.thr_cell[j] = lut_cell(t.thr[j]);
         if (fabsf(t.thr[j]) < 8.8817842e-16f) t.tiny_thr = 1;             // 2^-50
     }
     if (tid == 0) {
@@ -104,19 +110,45 @@ __device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) 
     }
     __syncthreads();
     if (NC == 16) {
-        for (int k = tid; k < kLutCells; k += blockDim.x) {
-            int base = 0, inside = 0;
-            float th = CUDART_INF_F;
-            for (int j = 0; j < NC - 1; ++j) {
-                const int cj = t.thr_cell[j];
-                base += (cj < k);
-                if (cj == k) { ++inside; th = t.thr[j]; }
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            const float scale = attempt ? 512.0f : 128.0f;
+            const int last = 2 * (int)scale;                 // highest cell a quotient can reach
+            if (tid == 0) { t.lut_bad = 0; t.lut_scale = scale; }
+            if (tid < NC - 1) {
+                const float th = t.thr[tid];
+                int c;
+                if (th > 1.0f) c = last + 1;                  // never reached
+                else if (!(th >= -1.0f)) c = -1;              // below every quotient
+                else c = lut_cell_raw(th, scale) - 0x4B000000;
+                t.thr_cell[tid] = c;
             }
-            if (inside > 1) t.lut_bad = 1;
-            t.lut[k] = make_float2(th, __int_as_float(base));
+            __syncthreads();
+            for (int k = tid; k <= last + 1; k += blockDim.x) {   // cells a finite quotient can index
+                int base = 0, inside = 0;
+                unsigned thb = 0x7f800000u;                   // +inf: no threshold in this cell
+                for (int j = 0; j < NC - 1; ++j) {
+                    const int cj = t.thr_cell[j];
+                    base += (cj < k);
+                    if (cj == k) { ++inside; thb = __float_as_uint(t.thr[j]); }
+                }
+                if (inside > 1 && k <= last) t.lut_bad = 1;
+                t.lut[k] = (thb & ~15u) | (unsigned)min(base, 15);
+            }
+            __syncthreads();
+            if (!t.lut_bad) break;                            // uniform: read after the barrier
+            __syncthreads();                                  // everyone has read lut_bad before it is reset
         }
-        __syncthreads();
     }
+}
+
+// Index of q (|q| <= 1, finite) in the sorted 16-entry codebook through the packed table.
+__device__ __forceinline__ int lut_index(const CodeTables<16> &t, const unsigned *lut, float scale, float q) {
+    const unsigned e = lut[lut_cell_raw(q, scale) & (kLutAlloc - 1)];
+    const int base = (int)(e & 15u);
+    int idx = base + (q >= __uint_as_float(e & ~15u) ? 1 : 0);
+    // q in the same 16-ulp bucket as the threshold: the cleared bits matter, use the exact value
+    if (((__float_as_uint(q) ^ e) & ~15u) == 0u) idx = base + (q >= t.thr[base] ? 1 : 0);
+    return idx;
 }
 
 // Number of thresholds <= q (== index into the sorted codebook).
@@ -127,17 +159,6 @@ __device__ __forceinline__ int code_index_search(const CodeTables<NC> &t, float 
     for (int step = NC / 2; step > 0; step >>= 1)
         if (t.thr[lo + step - 1] <= q) lo += step;
     return lo;
-}
-template <int NC>
-__device__ __forceinline__ int code_index(const CodeTables<NC> &t, float q, bool use_lut) {
-    if constexpr (NC == 16) {
-        if (use_lut) {
-            int cell = __float2int_rz(fmaf(q, (float)kLutScale, (float)kLutScale));
-            float2 e = t.lut[cell];
-            return __float_as_int(e.y) + (q >= e.x ? 1 : 0);
-        }
-    }
-    return code_index_search<NC>(t, q);
 }
 
 // x / d rounded to nearest, given r = RN(1/d): one reciprocal multiply and two FMA
@@ -158,7 +179,6 @@ template <int EPL> struct LaneVals { float v[EPL]; };
 
 template <int NC, int EPL>
 __device__ __noinline__ unsigned long long quantize_lane_generic(const CodeTables<NC> &tab, LaneVals<EPL> x, float amax) {
-    const bool use_lut = (NC == 16) && !tab.lut_bad;
     unsigned long long packed = 0;                        // one byte per element
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
@@ -166,7 +186,7 @@ __device__ __noinline__ unsigned long long quantize_lane_generic(const CodeTable
         if (amax != 0.0f) {
             float q = __fdiv_rn(x.v[j], amax);
             if (tab.need_clamp) q = fminf(fmaxf(q, tab.cmin), tab.cmax);
-            k = tab.perm[code_index<NC>(tab, q, use_lut)];
+            k = tab.perm[code_index_search<NC>(tab, q)];
         }
         packed |= (unsigned long long)(unsigned)k << (8 * j);
     }
@@ -212,54 +232,54 @@ __device__ __forceinline__ void load_vec(const T *p, float (&x)[EPL]) {
 template <typename T, int BITS, int EPL, int LPU>
 __global__ void __launch_bounds__(kThreads, (EPL == 16 ? 3 : 4))
 k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__restrict__ code,
-               int n, int nb, float *__restrict__ absmax_base, long long stride_absmax,
+               int n, int nb, int count, float *__restrict__ absmax_base, long long stride_absmax,
                float *__restrict__ diag_base, long long stride_diag,
                unsigned char *__restrict__ out_base, long long stride_out) {
     constexpr int NC = 1 << BITS;
     constexpr int BS = EPL * LPU;
     __shared__ CodeTables<NC> tab;
 
-    const int m = blockIdx.y;
-    const T *A = Abase + (long long)m * strideA;
-    float *absmax = absmax_base + (long long)m * stride_absmax;
-    float *diag = diag_base ? diag_base + (long long)m * stride_diag : nullptr;
-    unsigned char *out = out_base + (long long)m * stride_out;
-
-    const int units = n * nb;
+    // Units (one block of one row) are numbered across the whole batch, matrix-major, and the
+    // grid is one resident wave striding over them: the tables are built once per resident CTA
+    // and no second wave of CTAs trails behind.  (m, r, b) = matrix, row, block of a unit.
+    const int units = n * nb;                               // per matrix
+    const int total = units * count;                        // launcher keeps this below 2^31
     const int groups_per_cta = kThreads / LPU;
-    const int G = gridDim.x * groups_per_cta;               // groups striding over this matrix
+    const int G = gridDim.x * groups_per_cta;               // groups striding over the batch
     const int lane_u = threadIdx.x % LPU;
     int u = blockIdx.x * groups_per_cta + threadIdx.x / LPU;
     // first unit of this thread's warp: uniform loop bound so shuffles see full warps
     int u_warp = blockIdx.x * groups_per_cta + (threadIdx.x / 32) * (32 / LPU);
-    int r = u / nb, b = u - r * nb;
-    const int dr = G / nb, db = G - dr * nb;
+    int m = u / units;
+    int r = (u - m * units) / nb, b = u - m * units - r * nb;
+    const int dm = G / units, dr = (G - dm * units) / nb, db = G - dm * units - dr * nb;
 
     // issue the first loads before the table build so its latency is hidden
     float x[EPL];
     bool have = false;
     {
         const int c = b * BS + lane_u * EPL;
-        if (u < units && c < n) { load_vec<T, EPL>(A + (long long)r * n + c, x); have = true; }
+        if (u < total && c < n) { load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x); have = true; }
     }
     build_tables<NC>(tab, code);
     const bool lean_launch = (NC == 16) && !tab.lut_bad && !tab.need_clamp && tab.perm_identity && !tab.tiny_thr;
-    const float2 *lut16 = tab.lut;
+    const unsigned *lut16 = tab.lut;
+    const float lut_scale = tab.lut_scale;
 
-    for (; u_warp < units; u_warp += G) {
+    for (; u_warp < total; u_warp += G) {
         const int c = b * BS + lane_u * EPL;
-        const bool unit_ok = u < units;
+        const bool unit_ok = u < total;
         const bool lane_ok = unit_ok && c < n;
         if (!have) {
 #pragma unroll
             for (int j = 0; j < EPL; ++j) x[j] = 0.0f;
-            if (lane_ok) load_vec<T, EPL>(A + (long long)r * n + c, x);
+            if (lane_ok) load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x);
         }
         have = false;
-        if (diag && lane_ok && r >= c && r < c + EPL) {       // functional.py:574-578
+        if (diag_base && lane_ok && (unsigned)(r - c) < (unsigned)EPL) {   // functional.py:574-578
 #pragma unroll
             for (int j = 0; j < EPL; ++j)
-                if (c + j == r) { diag[r] = x[j]; x[j] = 0.0f; }
+                if (c + j == r) { diag_base[(long long)m * stride_diag + r] = x[j]; x[j] = 0.0f; }
         }
         float amax = 0.0f;
 #pragma unroll
@@ -267,7 +287,7 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
 #pragma unroll
         for (int off = LPU / 2; off > 0; off >>= 1)
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        if (unit_ok && lane_u == 0) absmax[(long long)r * nb + b] = amax;
+        if (unit_ok && lane_u == 0) absmax_base[(long long)m * stride_absmax + (long long)r * nb + b] = amax;
 
         // Lean path (the hot one: 16-entry sorted codebook covering [-1, 1], no threshold within
         // 2^-50 of zero, every block scale of the warp in [2^-40, 2^60] or zero): q = x / absmax
@@ -284,13 +304,16 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
 #pragma unroll
                 for (int j = 0; j < EPL; ++j) {
                     const float q = div_by_recip(x[j], d, rcp);
-                    const int cell = __float2int_rz(fmaf(q, (float)kLutScale, (float)kLutScale));
-                    const float2 e2 = lut16[cell];
-                    idx[j] = __float_as_int(e2.y) + (q >= e2.x ? 1 : 0);
+                    if constexpr (NC == 16) idx[j] = lut_index(tab, lut16, lut_scale, q);
+                    else idx[j] = 0;                          // lean_launch is false for other codebook sizes
                 }
                 if (amax == 0.0f) {                           // functional.py:600-602
+                    if constexpr (BITS == 4 && EPL == 16) {
+                        // every quotient is +-0 here and lands on one index: clear the words below instead
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < EPL; ++j) idx[j] = 0;
+                        for (int j = 0; j < EPL; ++j) idx[j] = 0;
+                    }
                 }
             } else {
                 constexpr int PART = EPL > 8 ? 8 : EPL;
@@ -305,6 +328,7 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
                 }
             }
             const long long e = (long long)r * n + c;         // flat element index, multiple of EPL
+            unsigned char *out = out_base + (long long)m * stride_out;
             if constexpr (BITS == 4 && EPL == 16) {
                 unsigned w0 = 0, w1 = 0;
 #pragma unroll
@@ -312,6 +336,7 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
                     w0 |= (unsigned)((idx[j] << 4) | idx[j + 1]) << (4 * j);
                     w1 |= (unsigned)((idx[8 + j] << 4) | idx[8 + j + 1]) << (4 * j);
                 }
+                if (lean && amax == 0.0f) { w0 = 0; w1 = 0; }
                 *reinterpret_cast<uint2 *>(out + (e >> 1)) = make_uint2(w0, w1);
             } else if constexpr (BITS == 4) {
                 unsigned w = 0;
@@ -333,8 +358,9 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
                 }
             }
         }
-        u += G; r += dr; b += db;
+        u += G; b += db; r += dr; m += dm;
         if (b >= nb) { b -= nb; r += 1; }
+        if (r >= n) { r -= n; m += 1; }
     }
 }
 
@@ -383,7 +409,6 @@ k_encode_generic(const T *__restrict__ Abase, long long strideA, const float *__
     unsigned char *out = out_base + (long long)m * stride_out;
     const long long total = (long long)n * n;
     const long long nbytes = (total + PER - 1) / PER;
-    const bool use_lut = (NC == 16) && !tab.lut_bad;
     for (long long byte = (long long)blockIdx.x * kThreads + threadIdx.x; byte < nbytes;
          byte += (long long)gridDim.x * kThreads) {
         unsigned v = 0;
@@ -399,7 +424,7 @@ k_encode_generic(const T *__restrict__ Abase, long long strideA, const float *__
                 if (amax != 0.0f) {
                     float q = __fdiv_rn(x, amax);
                     if (tab.need_clamp) q = fminf(fmaxf(q, tab.cmin), tab.cmax);
-                    k = tab.perm[code_index<NC>(tab, q, use_lut)];
+                    k = tab.perm[code_index_search<NC>(tab, q)];
                 }
             }
             v = (BITS == 4) ? ((v << 4) | (unsigned)k) : (unsigned)k;
@@ -624,14 +649,29 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
     if (epl) {
         const int lpu = a.bs / epl;
         const long long units = (long long)n * nb;
-        // every CTA builds the code tables once: keep the grid near one resident wave
-        long long per_matrix = ((long long)sm_count() * 8 + a.count - 1) / a.count;
-        const long long needed = (units * lpu + kThreads - 1) / kThreads;
-        if (per_matrix > needed) per_matrix = needed;
-        if (per_matrix < 1) per_matrix = 1;
-        dim3 grid((unsigned)per_matrix, a.count);
+        // every CTA builds the code tables once: exactly one resident wave (or fewer CTAs when the
+        // batch is small), striding over the units of the whole batch
+        if (units * a.count >= (1ll << 31) - (1ll << 24) && a.count > 1) {   // unit numbers are 32-bit in the kernel
+            const int half = a.count / 2;
+            QuantArgs lo = a, hi = a;
+            lo.count = half;
+            hi.count = a.count - half;
+            hi.A = (const char *)a.A + (long long)half * a.strideA * (long long)esz;
+            hi.absmax = a.absmax + (long long)half * a.stride_absmax;
+            hi.diag = a.diag ? a.diag + (long long)half * a.stride_diag : nullptr;
+            hi.out = a.out + (long long)half * a.stride_out;
+            launch_quantize_typed<T, BITS>(lo, s);
+            launch_quantize_typed<T, BITS>(hi, s);
+            return;
+        }
+        const int resident = (epl == 16) ? 3 : 4;            // the kernels' launch bounds
+        long long ctas = (long long)sm_count() * resident;
+        const long long needed = (units * a.count * lpu + kThreads - 1) / kThreads;
+        if (ctas > needed) ctas = needed;
+        if (ctas < 1) ctas = 1;
+        dim3 grid((unsigned)ctas);
 #define QT_LAUNCH_Q(E, L)                                                                          \
-        k_quantize_vec<T, BITS, E, L><<<grid, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.absmax, \
+        k_quantize_vec<T, BITS, E, L><<<grid, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.count, a.absmax, \
             a.stride_absmax, a.diag, a.stride_diag, a.out, a.stride_out)
         if constexpr (BITS == 4) { if (epl == 16) { QT_LAUNCH_Q(16, 4); count_launch(1); return; } }
         if (epl == 8 && lpu == 8) QT_LAUNCH_Q(8, 8);
