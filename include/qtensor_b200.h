@@ -188,6 +188,28 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
                    float *D, long long ldd, long long strideD, void *stream);
 
 /*
+ * The same six-product GEMM with 4-bit blockwise state (block size 64, the byte format of
+ * qt_quantize_blockwise) as its C operand and as its result, square n x n, n a multiple of 16:
+ *     state_out = quantize( alpha * op(A) * op(B) + beta * dequantize(state_in) )
+ * The old state is dequantized and the new one quantized inside the epilogue, so no fp32 copy of
+ * the state is written to or read from device memory; the bytes equal those of
+ * qt_dequantize_blockwise -> qt_gemm_bf16x6 -> qt_quantize_blockwise.  This is the fused form of
+ * the statistics update L <- beta L + (1-beta) G G^T (optimizers/shampoo1.py:163-179: product,
+ * dequantize, mul_/add_, quantize) and of storing a product as a low-bit preconditioner
+ * (optimizers/shampoo2.py:231).
+ * q_in == NULL: no C operand (beta ignored).  diag_out != NULL selects the diagreal variant for
+ * the result, diag_in != NULL for the operand.  q_out may equal q_in (update in place).
+ * Strides are per matrix: stride_codes in bytes (a multiple of 8), stride_absmax and stride_diag
+ * in floats; code pointers must be 8-byte aligned.
+ */
+int qt_gemm_bf16x6_q4(const void *Ahi, const void *Amid, const void *Alo, long long lda, long long strideA, int a_mn,
+                      const void *Bhi, const void *Bmid, const void *Blo, long long ldb, long long strideB, int b_mn,
+                      int n, int K, int batch, float alpha, float beta, const float *code,
+                      const unsigned char *q_in, const float *absmax_in, const float *diag_in,
+                      unsigned char *q_out, float *absmax_out, float *diag_out,
+                      long long stride_codes, long long stride_absmax, long long stride_diag, void *stream);
+
+/*
  * D = alpha * op(A) * op(B) + beta * C for fp32 row-major operands in one call: splits both
  * operands into bf16 planes inside `scratch` (caller-owned device memory of at least
  * qt_matmul_f32_scratch_bytes(...) bytes), then runs qt_gemm_bf16x3.  op(A) is M x K

@@ -22,7 +22,7 @@
 // Operands may be K-major (row = M or N index, K contiguous) or MN-major (row = K index).
 // Out-of-range rows / columns / k are zero-filled by TMA; the epilogue masks its stores.
 // Every wait is bounded: on expiry the kernel records an error word and drains.
-#include "qt_common.cuh"
+#include "quant_device.cuh"
 #include <cuda.h>
 
 namespace qt {
@@ -45,7 +45,15 @@ struct GemmParams {
     float *D; long long ldd, strideD;
     __nv_bfloat16 *Dhi, *Dlo; long long ldp, strideP;
     int tiles_m, tiles_n;
+    // 4-bit state as C operand and as result (QOUT kernels only): block size 64, order N == M
+    const unsigned char *q_in; const float *q_absmax_in, *q_diag_in;      // q_in == nullptr: no C operand
+    unsigned char *q_out; float *q_absmax_out, *q_diag_out;                // q_diag_out == nullptr: plain variant
+    long long q_stride_codes, q_stride_absmax, q_stride_diag;             // per matrix: bytes, floats, floats
+    const float *q_code; int q_nb;
 };
+
+template <bool Q> struct QuantTablesHolder { CodeTables<16> t; };
+template <> struct QuantTablesHolder<false> { int unused; };
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -130,9 +138,106 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
 // fp32-level accuracy).  Plane 0 is the most significant one.
 struct GemmMaps { CUtensorMap a[3]; CUtensorMap b[3]; };
 
-template <bool A_MN, bool B_MN, int NP>
+// Epilogue of the kernels whose C operand and result are 4-bit blockwise state (block 64, packed
+// as the stand-alone quantizer packs them).  `sum` holds this thread's row of the 128-column tile,
+// i.e. two whole quantization blocks: the old state is dequantized in registers exactly as
+// k_dequantize_vec does, combined as beta*old + alpha*sum, and quantized exactly as k_quantize_vec
+// does (diagonal side channel, block scale, exact division, threshold table).  The result equals
+// quantize(fp32 epilogue output) bit for bit and no fp32 copy of the state touches HBM.
+// In-place use (q_out == q_in) is safe: a block's bytes, scale and diagonal entry are read and
+// written by this thread only, reads first.
+__device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, const GemmParams &p, float (&sum)[BN],
+                                                    int b, int row, int n0) {
+    const bool lean_launch = !tab.lut_bad && !tab.need_clamp && tab.perm_identity && !tab.tiny_thr;
+    const float lut_scale = tab.lut_scale;
+#pragma unroll
+    for (int h = 0; h < BN / 64; ++h) {
+        const int c0 = n0 + h * 64;
+        const int valid = p.N - c0;                            // a multiple of 16 (launcher)
+        if (valid <= 0) continue;
+        const int blk = c0 >> 6;
+        const long long e0 = (long long)row * p.N + c0;        // flat element index, a multiple of 16
+        const bool on_diag = (unsigned)(row - c0) < 64u;
+        if (p.q_in) {
+            const float am = __ldg(p.q_absmax_in + (long long)b * p.q_stride_absmax + (long long)row * p.q_nb + blk);
+            const float z = (am == 0.0f) ? 0.0f : -0.0f;       // all-zero block dequantizes to +0.0
+            const unsigned char *cin = p.q_in + (long long)b * p.q_stride_codes + (e0 >> 1);
+            const bool has_d = p.q_diag_in != nullptr && on_diag;
+            const float dold = has_d ? __ldg(p.q_diag_in + (long long)b * p.q_stride_diag + row) : 0.0f;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                if (g * 16 < valid) {
+                    const uint2 w = __ldg(reinterpret_cast<const uint2 *>(cin + 8 * g));
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const unsigned byte = ((j < 8 ? w.x : w.y) >> (8 * ((j & 7) >> 1))) & 255u;
+                        const unsigned idx = (j & 1) ? (byte & 15u) : (byte >> 4);
+                        float old = fmaf(tab.raw[idx], am, z);
+                        if (has_d && c0 + g * 16 + j == row) old = dold;
+                        sum[h * 64 + g * 16 + j] = fmaf(p.beta, old, p.alpha * sum[h * 64 + g * 16 + j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sum[h * 64 + g * 16 + j] = 0.0f;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) sum[h * 64 + j] = (j < valid) ? fmaf(p.beta, 0.0f, p.alpha * sum[h * 64 + j]) : 0.0f;
+        }
+        if (p.q_diag_out != nullptr && on_diag) {              // functional.py:574-578
+            float dnew = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+                if (c0 + j == row) { dnew = sum[h * 64 + j]; sum[h * 64 + j] = 0.0f; }
+            p.q_diag_out[(long long)b * p.q_stride_diag + row] = dnew;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) amax = fmaxf(amax, fabsf(sum[h * 64 + j]));
+        p.q_absmax_out[(long long)b * p.q_stride_absmax + (long long)row * p.q_nb + blk] = amax;
+        const bool scale_ok = (amax >= 9.094947e-13f && amax <= 1.1529215e18f) || amax == 0.0f;
+        const bool lean = lean_launch && scale_ok;
+        unsigned char *cout = p.q_out + (long long)b * p.q_stride_codes + (e0 >> 1);
+        const float d = (amax == 0.0f) ? 1.0f : amax;
+        const float rcp = __frcp_rn(d);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if (g * 16 >= valid) continue;
+            unsigned w0 = 0, w1 = 0;
+            if (lean) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const int i0 = lut_index(tab, tab.lut, lut_scale, div_by_recip(sum[h * 64 + g * 16 + j], d, rcp));
+                    const int i1 = lut_index(tab, tab.lut, lut_scale, div_by_recip(sum[h * 64 + g * 16 + j + 1], d, rcp));
+                    const unsigned byte = (unsigned)((i0 << 4) | i1);
+                    if (j < 8) w0 |= byte << (4 * j); else w1 |= byte << (4 * (j - 8));
+                }
+                if (amax == 0.0f) { w0 = 0; w1 = 0; }          // functional.py:600-602
+            } else {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    LaneVals<8> xv;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) xv.v[j] = sum[h * 64 + g * 16 + q * 8 + j];
+                    const unsigned long long pk = quantize_lane_generic<16, 8>(tab, xv, amax);
+                    unsigned w = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2)
+                        w |= (unsigned)((((pk >> (8 * j)) & 15u) << 4) | ((pk >> (8 * (j + 1))) & 15u)) << (4 * j);
+                    if (q == 0) w0 = w; else w1 = w;
+                }
+            }
+            *reinterpret_cast<uint2 *>(cout + 8 * g) = make_uint2(w0, w1);
+        }
+    }
+}
+
+template <bool A_MN, bool B_MN, int NP, bool QOUT = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+    static_assert(!QOUT || NP == 3, "the quantizing epilogue needs the whole row of the tile in registers");
+    __shared__ QuantTablesHolder<QOUT> qtab;
     constexpr int STAGES = NP == 2 ? 3 : 2;
     constexpr int STAGE_BYTES = 2 * NP * PLANE_TILE_BYTES;
     // The tensor core's fp32 accumulation truncates: its error grows linearly with the length of
@@ -173,6 +278,7 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
+    if constexpr (QOUT) build_tables<16>(qtab.t, p.q_code);    // all threads; ends with a barrier
 
     if (warp == 4) {
         // ---------------- TMA producer: one ring of stages shared by all tiles of this CTA
@@ -309,6 +415,9 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
                 }
                 if (!ok) break;
+                if constexpr (QOUT) {
+                    if (row_ok) quantizing_epilogue(qtab.t, p, sum, b, row, n0);
+                } else
                 if (row_ok && p.D) {
                     const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
                     float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + n0;
@@ -575,13 +684,30 @@ struct GemmArgs {
 
 static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// a.Ahi/Alo (+ amid/bmid for three planes: order hi, mid, lo).
-int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cudaStream_t s) {
+// 4-bit state operands of the quantizing variant (all device pointers; see GemmParams).
+struct QuantStateArgs {
+    const float *code;
+    const unsigned char *q_in; const float *absmax_in, *diag_in;
+    unsigned char *q_out; float *absmax_out, *diag_out;
+    long long stride_codes, stride_absmax, stride_diag;
+};
+
+// a.Ahi/Alo (+ amid/bmid for three planes: order hi, mid, lo).  With `qs` the result (and the C
+// operand, if qs->q_in) is 4-bit state instead of a.C / a.D.
+int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cudaStream_t s, const QuantStateArgs *qs) {
     const int np = (Amid && Bmid) ? 3 : 2;
+    if (qs) {
+        if (np != 3 || a.M != a.N || a.N % 16 != 0) return record(QT_ERR_UNSUPPORTED);
+        if (!qs->code || !qs->q_out || !qs->absmax_out) return record(QT_ERR_ARG);
+        if (qs->q_in && !qs->absmax_in) return record(QT_ERR_ARG);
+        // 8-byte code words per 16 elements
+        if ((reinterpret_cast<uintptr_t>(qs->q_out) | reinterpret_cast<uintptr_t>(qs->q_in)) & 7) return record(QT_ERR_ARG);
+        if (a.batch > 1 && (qs->stride_codes & 7)) return record(QT_ERR_ARG);
+    }
     if (a.M < 0 || a.N < 0 || a.K < 0 || a.batch < 0) return record(QT_ERR_ARG);
     if (a.M == 0 || a.N == 0 || a.batch == 0) return record(QT_OK);
     if (a.K == 0) return record(QT_ERR_UNSUPPORTED);
-    if (!a.Ahi || !a.Alo || !a.Bhi || !a.Blo || (!a.D && !a.Dhi)) return record(QT_ERR_ARG);
+    if (!a.Ahi || !a.Alo || !a.Bhi || !a.Blo || (!qs && !a.D && !a.Dhi)) return record(QT_ERR_ARG);
     if ((a.Dhi == nullptr) != (a.Dlo == nullptr) || (Amid == nullptr) != (Bmid == nullptr)) return record(QT_ERR_ARG);
     const void *Ap[3] = {a.Ahi, np == 3 ? Amid : a.Alo, a.Alo};
     const void *Bp[3] = {a.Bhi, np == 3 ? Bmid : a.Blo, a.Blo};
@@ -605,16 +731,31 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     p.Dhi = static_cast<__nv_bfloat16 *>(a.Dhi); p.Dlo = static_cast<__nv_bfloat16 *>(a.Dlo);
     p.ldp = a.ldp; p.strideP = a.strideP;
     p.tiles_m = (a.M + BM - 1) / BM; p.tiles_n = (a.N + BN - 1) / BN;
+    p.q_in = nullptr; p.q_absmax_in = p.q_diag_in = nullptr; p.q_out = nullptr; p.q_absmax_out = p.q_diag_out = nullptr;
+    p.q_stride_codes = p.q_stride_absmax = p.q_stride_diag = 0; p.q_code = nullptr; p.q_nb = 0;
+    if (qs) {
+        p.q_in = qs->q_in; p.q_absmax_in = qs->absmax_in; p.q_diag_in = qs->q_in ? qs->diag_in : nullptr;
+        p.q_out = qs->q_out; p.q_absmax_out = qs->absmax_out; p.q_diag_out = qs->diag_out;
+        p.q_stride_codes = qs->stride_codes; p.q_stride_absmax = qs->stride_absmax; p.q_stride_diag = qs->stride_diag;
+        p.q_code = qs->code; p.q_nb = (a.N + 63) / 64;
+    }
     const long long ctas = (long long)p.tiles_m * p.tiles_n * a.batch;
     if (ctas > 0x7fffffffLL) return record(QT_ERR_UNSUPPORTED);
     typedef void (*Kern)(const GemmMaps, const GemmParams);
     static const Kern kernels[2][2][2] = {
         {{k_gemm_bf16x3<false, false, 2>, k_gemm_bf16x3<false, true, 2>}, {k_gemm_bf16x3<true, false, 2>, k_gemm_bf16x3<true, true, 2>}},
         {{k_gemm_bf16x3<false, false, 3>, k_gemm_bf16x3<false, true, 3>}, {k_gemm_bf16x3<true, false, 3>, k_gemm_bf16x3<true, true, 3>}}};
+    static const Kern qkernels[2][2] = {
+        {k_gemm_bf16x3<false, false, 3, true>, k_gemm_bf16x3<false, true, 3, true>},
+        {k_gemm_bf16x3<true, false, 3, true>, k_gemm_bf16x3<true, true, 3, true>}};
     static bool attr_done = false;
     if (!attr_done) {
         for (int i = 0; i < 8; ++i)
             if (cudaFuncSetAttribute(reinterpret_cast<const void *>(kernels[i >> 2][(i >> 1) & 1][i & 1]),
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
+                return record(QT_ERR_LAUNCH);
+        for (int i = 0; i < 4; ++i)
+            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(qkernels[i >> 1][i & 1]),
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
                 return record(QT_ERR_LAUNCH);
         attr_done = true;
@@ -626,12 +767,13 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
         g_gemm_sms = n;
     }
     const unsigned grid = (unsigned)(ctas < g_gemm_sms ? ctas : g_gemm_sms);     // persistent: one CTA per SM
-    kernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
+    if (qs) qkernels[a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
+    else kernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
     count_launch(1);
     return check_launch();
 }
 
-int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) { return launch_gemm_planes(a, nullptr, nullptr, s); }
+int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) { return launch_gemm_planes(a, nullptr, nullptr, s, nullptr); }
 
 // fp32 operands in, fp32 out: both operands are split into bf16 planes inside `scratch`
 // (global memory owned by the caller), then multiplied on the tensor cores.
@@ -766,7 +908,20 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
     if (!Amid || !Bmid) return record(QT_ERR_ARG);
     GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, M, N, K, batch, alpha, beta,
                C, ldc, strideC, D, ldd, strideD, nullptr, nullptr, 0, 0};
-    return launch_gemm_planes(a, Amid, Bmid, static_cast<cudaStream_t>(stream));
+    return launch_gemm_planes(a, Amid, Bmid, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int qt_gemm_bf16x6_q4(const void *Ahi, const void *Amid, const void *Alo, long long lda, long long strideA, int a_mn,
+                      const void *Bhi, const void *Bmid, const void *Blo, long long ldb, long long strideB, int b_mn,
+                      int n, int K, int batch, float alpha, float beta, const float *code,
+                      const unsigned char *q_in, const float *absmax_in, const float *diag_in,
+                      unsigned char *q_out, float *absmax_out, float *diag_out,
+                      long long stride_codes, long long stride_absmax, long long stride_diag, void *stream) {
+    if (!Amid || !Bmid) return record(QT_ERR_ARG);
+    GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, n, n, K, batch, alpha, beta,
+               nullptr, 0, 0, nullptr, 0, 0, nullptr, nullptr, 0, 0};
+    QuantStateArgs qs{code, q_in, absmax_in, diag_in, q_out, absmax_out, diag_out, stride_codes, stride_absmax, stride_diag};
+    return launch_gemm_planes(a, Amid, Bmid, static_cast<cudaStream_t>(stream), &qs);
 }
 
 unsigned long long qt_matmul_f32_scratch_bytes(int M, int N, int K, int batch, int trans_a, int trans_b) {

@@ -6,192 +6,25 @@
 //   packing) - and replace the CUDA kernels of cudaC_python/csrc/kernels.cu:57-457.
 //
 // Design (HBM-bound byte work, no tensor cores):
-//   * one launch covers a strided batch of same-order matrices (gridDim.y = matrix);
+//   * one launch covers a strided batch of same-order matrices (quantize: one resident wave
+//     of CTAs striding over the blocks of the whole batch; dequantize: gridDim.y = matrix);
 //   * a quantization block (64..256 elements of one row) is owned by a group of LPU
 //     lanes of one warp, EPL consecutive elements per lane, loaded as 128-bit vectors;
 //     the per-block absmax is a shuffle reduction inside the group;
 //   * the nearest-code rule |q-c_lo| > |c_hi-q| (fp32) is monotone in q, so it is
 //     replaced by 2^bits-1 exact fp32 thresholds found once per CTA by bisection over
 //     float bit patterns; the code index is the number of thresholds <= q.  For 16-entry
-//     codebooks a 1025-cell lookup table in shared memory gives (base index, threshold)
-//     per cell so that one LDS.64 and one compare resolve an element;
+//     codebooks a lookup table in shared memory (257 or 1025 cells of q, one 32-bit word each)
+//     gives (base index, threshold) per cell so that one LDS.32 and one compare resolve an element;
 //   * q = x / absmax is an IEEE-rounded fp32 division (the oracle divides);
 //   * codes are packed high-nibble-first and stored as 16/32-bit words.
 //   Orders that are not a multiple of 4, unaligned buffers and block sizes above 256
 //   take a generic two-kernel path (absmax pass, then one thread per output byte).
-#include "qt_common.cuh"
-#include <math_constants.h>
+#include "quant_device.cuh"
 
 namespace qt {
 
-static constexpr int kLutAlloc = 2048;        // cells allocated; the finest grid uses 2*512+1 of them
 static constexpr int kThreads = 256;
-
-// ------------------------------------------------------------------------------------
-// Codebook tables, built per CTA in shared memory.
-// ------------------------------------------------------------------------------------
-template <int NC>
-struct CodeTables {
-    float raw[NC];
-    float sorted[NC];
-    float thr[NC];            // thr[j], j < NC-1: smallest q that rounds up from sorted[j]; thr[NC-1] = +inf
-    unsigned char perm[NC];   // sorted position -> caller's code index
-    float cmin, cmax;
-    int perm_identity;
-    int need_clamp;
-    int lut_bad;
-    int tiny_thr;             // some decision threshold has |t| < 2^-50: quotients must be exact even when tiny
-    int thr_cell[NC];         // lookup-table cell of each threshold
-    float lut_scale;          // cells per unit of q: 128 when that separates the thresholds, else 512
-    // One 32-bit word per cell of q in [-1, 1]: bits 31..4 = the threshold inside the cell (or +inf)
-    // with its low four mantissa bits cleared, bits 3..0 = number of thresholds in lower cells.
-    // A 4-byte cell halves the shared-memory wavefronts of a warp's 32 scattered lookups compared
-    // with {float threshold, int base}; the 16-ulp bucket around the threshold that the cleared bits
-    // cannot resolve is decided against the exact threshold (rare).
-    unsigned lut[NC == 16 ? kLutAlloc : 1];
-};
-
-__device__ __forceinline__ long long float_key(float f) {
-    int i = __float_as_int(f);
-    return (long long)(i >= 0 ? i : (i ^ 0x7fffffff));
-}
-__device__ __forceinline__ float key_float(long long k) {
-    int i = (int)k;
-    return __int_as_float(i >= 0 ? i : (i ^ 0x7fffffff));
-}
-// Cell of q in [-1, 1] on a grid of `scale` cells per unit: round(q*scale + scale), taken from the
-// mantissa of the sum with 2^23 (no float-to-int conversion).  Monotone in q, which is all the table
-// needs.  The caller masks the result with kLutAlloc-1, which also removes the exponent bits.
-__device__ __forceinline__ int lut_cell_raw(float v, float scale) {
-    return __float_as_int(fmaf(v, scale, scale + 8388608.0f));
-}
-
-template <int NC>
-__device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) {
-    const int tid = threadIdx.x;
-    for (int i = tid; i < NC; i += blockDim.x) t.raw[i] = code[i];
-    if (tid == 0) { t.lut_bad = 0; t.tiny_thr = 0; }
-    __syncthreads();
-    // stable rank sort (the reference sorts only when the codebook is not ascending;
-    // sorting an ascending codebook is the identity, functional.py:561-565)
-    for (int i = tid; i < NC; i += blockDim.x) {
-        float v = t.raw[i];
-        int rank = 0;
-        for (int j = 0; j < NC; ++j) {
-            float w = t.raw[j];
-            rank += (w < v) || (w == v && j < i);
-        }
-        t.sorted[rank] = v;
-        t.perm[rank] = (unsigned char)i;
-    }
-    __syncthreads();
-    for (int j = tid; j < NC; j += blockDim.x) {
-        if (j == NC - 1) { t.thr[j] = CUDART_INF_F; continue; }
-        const float lo = t.sorted[j], hi = t.sorted[j + 1];
-        // predicate P(q) = |q - lo| > |hi - q| is false at lo and monotone in q
-        long long a = float_key(lo), b = float_key(hi);
-        if (!(fabsf(hi - lo) > 0.0f)) { t.thr[j] = hi; continue; }
-        for (int it = 0; it < 64 && b - a > 1; ++it) {
-            long long m = a + ((b - a) >> 1);
-            float q = key_float(m);
-            bool up = fabsf(q - lo) > fabsf(hi - q);
-            if (up) b = m; else a = m;
-        }
-        t.thr[j] = key_float(b);
-        if (fabsf(t.thr[j]) < 8.8817842e-16f) t.tiny_thr = 1;             // 2^-50
-    }
-    if (tid == 0) {
-        bool ident = true;
-        for (int j = 0; j < NC; ++j) ident = ident && (t.perm[j] == j);
-        t.perm_identity = ident;
-        t.cmin = t.sorted[0];
-        t.cmax = t.sorted[NC - 1];
-        t.need_clamp = !(t.sorted[0] <= -1.0f && t.sorted[NC - 1] >= 1.0f);
-    }
-    __syncthreads();
-    if (NC == 16) {
-        for (int attempt = 0; attempt < 2; ++attempt) {
-            const float scale = attempt ? 512.0f : 128.0f;
-            const int last = 2 * (int)scale;                 // highest cell a quotient can reach
-            if (tid == 0) { t.lut_bad = 0; t.lut_scale = scale; }
-            if (tid < NC - 1) {
-                const float th = t.thr[tid];
-                int c;
-                if (th > 1.0f) c = last + 1;                  // never reached
-                else if (!(th >= -1.0f)) c = -1;              // below every quotient
-                else c = lut_cell_raw(th, scale) - 0x4B000000;
-                t.thr_cell[tid] = c;
-            }
-            __syncthreads();
-            for (int k = tid; k <= last + 1; k += blockDim.x) {   // cells a finite quotient can index
-                int base = 0, inside = 0;
-                unsigned thb = 0x7f800000u;                   // +inf: no threshold in this cell
-                for (int j = 0; j < NC - 1; ++j) {
-                    const int cj = t.thr_cell[j];
-                    base += (cj < k);
-                    if (cj == k) { ++inside; thb = __float_as_uint(t.thr[j]); }
-                }
-                if (inside > 1 && k <= last) t.lut_bad = 1;
-                t.lut[k] = (thb & ~15u) | (unsigned)min(base, 15);
-            }
-            __syncthreads();
-            if (!t.lut_bad) break;                            // uniform: read after the barrier
-            __syncthreads();                                  // everyone has read lut_bad before it is reset
-        }
-    }
-}
-
-// Index of q (|q| <= 1, finite) in the sorted 16-entry codebook through the packed table.
-__device__ __forceinline__ int lut_index(const CodeTables<16> &t, const unsigned *lut, float scale, float q) {
-    const unsigned e = lut[lut_cell_raw(q, scale) & (kLutAlloc - 1)];
-    const int base = (int)(e & 15u);
-    int idx = base + (q >= __uint_as_float(e & ~15u) ? 1 : 0);
-    // q in the same 16-ulp bucket as the threshold: the cleared bits matter, use the exact value
-    if (((__float_as_uint(q) ^ e) & ~15u) == 0u) idx = base + (q >= t.thr[base] ? 1 : 0);
-    return idx;
-}
-
-// Number of thresholds <= q (== index into the sorted codebook).
-template <int NC>
-__device__ __forceinline__ int code_index_search(const CodeTables<NC> &t, float q) {
-    int lo = 0;
-#pragma unroll
-    for (int step = NC / 2; step > 0; step >>= 1)
-        if (t.thr[lo + step - 1] <= q) lo += step;
-    return lo;
-}
-
-// x / d rounded to nearest, given r = RN(1/d): one reciprocal multiply and two FMA
-// corrections (Markstein).  Exact whenever no intermediate underflows; callers guarantee
-// 2^-40 <= d <= 2^60 and treat |quotient| < 2^-60 as "sign only" (see k_quantize_vec).
-__device__ __forceinline__ float div_by_recip(float x, float d, float r) {
-    float q = x * r;
-    q = fmaf(fmaf(-q, d, x), r, q);
-    q = fmaf(fmaf(-q, d, x), r, q);
-    return q;
-}
-
-// Per-lane quantization of EPL elements for every case the lean path of k_quantize_vec does
-// not cover (any codebook, clamp, permutation, extreme scales).  Kept out of line on purpose.
-// Operands and results travel by value (registers): passing the caller's arrays by reference
-// would force them into local memory on the hot path as well.
-template <int EPL> struct LaneVals { float v[EPL]; };
-
-template <int NC, int EPL>
-__device__ __noinline__ unsigned long long quantize_lane_generic(const CodeTables<NC> &tab, LaneVals<EPL> x, float amax) {
-    unsigned long long packed = 0;                        // one byte per element
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-        int k = 0;
-        if (amax != 0.0f) {
-            float q = __fdiv_rn(x.v[j], amax);
-            if (tab.need_clamp) q = fminf(fmaxf(q, tab.cmin), tab.cmax);
-            k = tab.perm[code_index_search<NC>(tab, q)];
-        }
-        packed |= (unsigned long long)(unsigned)k << (8 * j);
-    }
-    return packed;
-}
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

@@ -103,3 +103,87 @@ def test_three_plane_product_reaches_fp32_accuracy(native_lib, trans_a, trans_b)
     P = _gemm.split3(A)
     back = P.hi.float() + P.mid.float() + P.lo.float()
     assert float((back.view(-1)[: A.numel()].view_as(A) - A).abs().max() / A.abs().max()) < 2.0 ** -22
+
+
+def _state(b, n, device, diagreal):
+    nb = (n + 63) // 64
+    row_bytes = ((n * n + 1) // 2 + 15) // 16 * 16
+    var = torch.zeros(b, row_bytes, dtype=torch.uint8, device=device)
+    absmax = torch.zeros(b, n * nb, device=device)
+    diag = torch.zeros(b, n, device=device) if diagreal else None
+    return var, absmax, diag
+
+
+def _quantize_batch(lib, X, code, st):
+    import ctypes as ct
+    b, n, _ = X.shape
+    var, absmax, diag = st
+    p = lambda t: None if t is None else ct.c_void_p(t.data_ptr())
+    rc = lib.qt_quantize_blockwise(p(X), 0, n * n, p(code), n, b, p(absmax), absmax.stride(0), p(diag), n,
+                                   p(var), var.stride(0), 64, 4, ct.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+
+
+def _dequantize_batch(lib, st, code, n):
+    import ctypes as ct
+    var, absmax, diag = st
+    b = var.shape[0]
+    out = torch.empty(b, n, n, device=var.device)
+    p = lambda t: None if t is None else ct.c_void_p(t.data_ptr())
+    rc = lib.qt_dequantize_blockwise(p(var), var.stride(0), p(code), n, b, p(absmax), absmax.stride(0), p(diag), n,
+                                     p(out), 0, n * n, 64, 4, ct.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    return out
+
+
+@pytest.mark.parametrize("n,k,axis,diagreal,with_old", [
+    (128, 64, 0, True, True), (512, 384, 1, True, True), (1200, 768, 0, True, True), (1200, 3072, 1, False, True),
+    (672, 768, 0, True, False), (1104, 200, 1, False, True), (2048, 2048, 0, True, True), (16, 40, 0, True, True),
+    (48, 48, 1, False, True)])
+def test_quantizing_epilogue_equals_unfused_sequence(native_lib, n, k, axis, diagreal, with_old):
+    """state <- quantize(w2 * G G^T + w1 * dequantize(state)) inside the GEMM epilogue: the code
+    bytes, block scales and diagonal must equal dequantize -> six-product GEMM -> quantize bit for
+    bit, and the dequantized result must be within 4-bit quantization error of the float64 value."""
+    import qtensor.functional as F
+    from optimizers import _gemm
+    dev = "cuda"
+    b = 3
+    gen = torch.Generator(device=dev).manual_seed(n * 31 + k)
+    code = F.create_linear_map(True, 4, 2).to(dev)
+    G = torch.randn((b, n, k) if axis == 0 else (b, k, n), device=dev, generator=gen) / n ** 0.5
+    # old state: SPD with a wide spectrum, one matrix left at zero (all-zero blocks)
+    Q = torch.linalg.qr(torch.randn(b, n, n, device=dev, generator=gen)).Q
+    lam = torch.exp(torch.rand(b, n, device=dev, generator=gen) * 13.8 - 13.8)
+    L0 = (Q * lam[:, None, :]) @ Q.transpose(1, 2)
+    L0 = 0.5 * (L0 + L0.transpose(1, 2))
+    L0[1].zero_()
+    old = _state(b, n, dev, diagreal)
+    _quantize_batch(native_lib, L0.contiguous(), code, old)
+    w1, w2 = 0.95, 0.05
+    P = _gemm.split3(G)
+    ta, tb = (False, True) if axis == 0 else (True, False)
+    # unfused sequence
+    Lold = _dequantize_batch(native_lib, old, code, n) if with_old else None
+    D, _ = _gemm.matmul(P, P, trans_a=ta, trans_b=tb, alpha=w2, beta=w1 if with_old else 0.0, C=Lold)
+    want = _state(b, n, dev, diagreal)
+    _quantize_batch(native_lib, D, code, want)
+    # fused, written to a fresh state and then in place
+    got = _state(b, n, dev, diagreal)
+    _gemm.matmul_q4(P, P, code, got, trans_a=ta, trans_b=tb, alpha=w2, beta=w1, old=old if with_old else None)
+    assert device_ok(native_lib)
+    nbytes = (n * n + 1) // 2
+    for w, g_, name in zip(want, got, ("codes", "absmax", "diag")):
+        if w is None:
+            continue
+        w, g_ = (w[:, :nbytes], g_[:, :nbytes]) if name == "codes" else (w, g_)
+        assert torch.equal(w.view(torch.uint8 if name == "codes" else torch.int32),
+                           g_.view(torch.uint8 if name == "codes" else torch.int32)), name
+    if with_old:
+        _gemm.matmul_q4(P, P, code, old, trans_a=ta, trans_b=tb, alpha=w2, beta=w1, old=old)
+        assert device_ok(native_lib)
+        assert torch.equal(old[0][:, :nbytes], want[0][:, :nbytes]) and torch.equal(old[1], want[1])
+    Gd = G.double()
+    ref = w2 * (Gd @ Gd.transpose(1, 2) if axis == 0 else Gd.transpose(1, 2) @ Gd)
+    if with_old:
+        ref = ref + w1 * Lold.double()
+    assert rel(D, ref) < TOL
