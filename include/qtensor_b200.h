@@ -188,12 +188,13 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
                    float *D, long long ldd, long long strideD, void *stream);
 
 /*
- * The same six-product GEMM with 4-bit blockwise state (block size 64, the byte format of
- * qt_quantize_blockwise) as its C operand and as its result, square n x n, n a multiple of 16:
+ * The three-product (qt_gemm_bf16x3_q4) and six-product (qt_gemm_bf16x6_q4) GEMMs with 4-bit
+ * blockwise state (block size 64, the byte format of qt_quantize_blockwise) as C operand and as
+ * result, square n x n, n a multiple of 16:
  *     state_out = quantize( alpha * op(A) * op(B) + beta * dequantize(state_in) )
  * The old state is dequantized and the new one quantized inside the epilogue, so no fp32 copy of
  * the state is written to or read from device memory; the bytes equal those of
- * qt_dequantize_blockwise -> qt_gemm_bf16x6 -> qt_quantize_blockwise.  This is the fused form of
+ * qt_dequantize_blockwise -> qt_gemm_bf16x3 / x6 -> qt_quantize_blockwise.  This is the fused form of
  * the statistics update L <- beta L + (1-beta) G G^T (optimizers/shampoo1.py:163-179: product,
  * dequantize, mul_/add_, quantize) and of storing a product as a low-bit preconditioner
  * (optimizers/shampoo2.py:231).
@@ -202,6 +203,12 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
  * Strides are per matrix: stride_codes in bytes (a multiple of 8), stride_absmax and stride_diag
  * in floats; code pointers must be 8-byte aligned.
  */
+int qt_gemm_bf16x3_q4(const void *Ahi, const void *Alo, long long lda, long long strideA, int a_mn,
+                      const void *Bhi, const void *Blo, long long ldb, long long strideB, int b_mn,
+                      int n, int K, int batch, float alpha, float beta, const float *code,
+                      const unsigned char *q_in, const float *absmax_in, const float *diag_in,
+                      unsigned char *q_out, float *absmax_out, float *diag_out,
+                      long long stride_codes, long long stride_absmax, long long stride_diag, void *stream);
 int qt_gemm_bf16x6_q4(const void *Ahi, const void *Amid, const void *Alo, long long lda, long long strideA, int a_mn,
                       const void *Bhi, const void *Bmid, const void *Blo, long long ldb, long long strideB, int b_mn,
                       int n, int K, int batch, float alpha, float beta, const float *code,

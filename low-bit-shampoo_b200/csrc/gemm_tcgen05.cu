@@ -139,19 +139,20 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
 struct GemmMaps { CUtensorMap a[3]; CUtensorMap b[3]; };
 
 // Epilogue of the kernels whose C operand and result are 4-bit blockwise state (block 64, packed
-// as the stand-alone quantizer packs them).  `sum` holds this thread's row of the 128-column tile,
-// i.e. two whole quantization blocks: the old state is dequantized in registers exactly as
+// as the stand-alone quantizer packs them).  `sum` holds LEN (64 or 128) consecutive accumulator
+// columns of this thread's row starting at column n0, i.e. whole quantization blocks: the old state is dequantized in registers exactly as
 // k_dequantize_vec does, combined as beta*old + alpha*sum, and quantized exactly as k_quantize_vec
 // does (diagonal side channel, block scale, exact division, threshold table).  The result equals
 // quantize(fp32 epilogue output) bit for bit and no fp32 copy of the state touches HBM.
 // In-place use (q_out == q_in) is safe: a block's bytes, scale and diagonal entry are read and
 // written by this thread only, reads first.
-__device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, const GemmParams &p, float (&sum)[BN],
+template <int LEN>
+__device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, const GemmParams &p, float (&sum)[LEN],
                                                     int b, int row, int n0) {
     const bool lean_launch = !tab.lut_bad && !tab.need_clamp && tab.perm_identity && !tab.tiny_thr;
     const float lut_scale = tab.lut_scale;
 #pragma unroll
-    for (int h = 0; h < BN / 64; ++h) {
+    for (int h = 0; h < LEN / 64; ++h) {
         const int c0 = n0 + h * 64;
         const int valid = p.N - c0;                            // a multiple of 16 (launcher)
         if (valid <= 0) continue;
@@ -236,7 +237,6 @@ __device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, c
 template <bool A_MN, bool B_MN, int NP, bool QOUT = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
-    static_assert(!QOUT || NP == 3, "the quantizing epilogue needs the whole row of the tile in registers");
     __shared__ QuantTablesHolder<QOUT> qtab;
     constexpr int STAGES = NP == 2 ? 3 : 2;
     constexpr int STAGE_BYTES = 2 * NP * PLANE_TILE_BYTES;
@@ -416,7 +416,7 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 }
                 if (!ok) break;
                 if constexpr (QOUT) {
-                    if (row_ok) quantizing_epilogue(qtab.t, p, sum, b, row, n0);
+                    if (row_ok) quantizing_epilogue<BN>(qtab.t, p, sum, b, row, n0);
                 } else
                 if (row_ok && p.D) {
                     const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
@@ -447,6 +447,29 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             const int acc = i & 1;
             const int row = m0 + warp * 32 + lane;
             const bool row_ok = row < p.M;
+            if constexpr (QOUT) {
+                // result (and C operand) are 4-bit state: one 64-column quantization block at a time
+                const bool okq = mbar_wait_warp(acc_full(acc), (i >> 1) & 1, abort_flag);
+                if (!okq) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
+#pragma unroll 1
+                for (int h = 0; h < BN / 64; ++h) {
+                    float v[64];
+                    {
+                        float t0[32], t1[32];
+                        tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(h * 64), t0);
+                        tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(h * 64 + 32), t1);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) { v[j] = t0[j]; v[32 + j] = t1[j]; }
+                    }
+                    if (row_ok) quantizing_epilogue<64>(qtab.t, p, v, b, row, n0 + h * 64);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
+                continue;
+            }
             const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
             float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + n0;
             __nv_bfloat16 *hrow = p.Dhi + (long long)b * p.strideP + (long long)row * p.ldp + n0;
@@ -697,7 +720,7 @@ struct QuantStateArgs {
 int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cudaStream_t s, const QuantStateArgs *qs) {
     const int np = (Amid && Bmid) ? 3 : 2;
     if (qs) {
-        if (np != 3 || a.M != a.N || a.N % 16 != 0) return record(QT_ERR_UNSUPPORTED);
+        if (a.M != a.N || a.N % 16 != 0) return record(QT_ERR_UNSUPPORTED);
         if (!qs->code || !qs->q_out || !qs->absmax_out) return record(QT_ERR_ARG);
         if (qs->q_in && !qs->absmax_in) return record(QT_ERR_ARG);
         // 8-byte code words per 16 elements
@@ -745,17 +768,19 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     static const Kern kernels[2][2][2] = {
         {{k_gemm_bf16x3<false, false, 2>, k_gemm_bf16x3<false, true, 2>}, {k_gemm_bf16x3<true, false, 2>, k_gemm_bf16x3<true, true, 2>}},
         {{k_gemm_bf16x3<false, false, 3>, k_gemm_bf16x3<false, true, 3>}, {k_gemm_bf16x3<true, false, 3>, k_gemm_bf16x3<true, true, 3>}}};
-    static const Kern qkernels[2][2] = {
-        {k_gemm_bf16x3<false, false, 3, true>, k_gemm_bf16x3<false, true, 3, true>},
-        {k_gemm_bf16x3<true, false, 3, true>, k_gemm_bf16x3<true, true, 3, true>}};
+    static const Kern qkernels[2][2][2] = {
+        {{k_gemm_bf16x3<false, false, 2, true>, k_gemm_bf16x3<false, true, 2, true>},
+         {k_gemm_bf16x3<true, false, 2, true>, k_gemm_bf16x3<true, true, 2, true>}},
+        {{k_gemm_bf16x3<false, false, 3, true>, k_gemm_bf16x3<false, true, 3, true>},
+         {k_gemm_bf16x3<true, false, 3, true>, k_gemm_bf16x3<true, true, 3, true>}}};
     static bool attr_done = false;
     if (!attr_done) {
         for (int i = 0; i < 8; ++i)
             if (cudaFuncSetAttribute(reinterpret_cast<const void *>(kernels[i >> 2][(i >> 1) & 1][i & 1]),
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
                 return record(QT_ERR_LAUNCH);
-        for (int i = 0; i < 4; ++i)
-            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(qkernels[i >> 1][i & 1]),
+        for (int i = 0; i < 8; ++i)
+            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(qkernels[i >> 2][(i >> 1) & 1][i & 1]),
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
                 return record(QT_ERR_LAUNCH);
         attr_done = true;
@@ -767,7 +792,7 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
         g_gemm_sms = n;
     }
     const unsigned grid = (unsigned)(ctas < g_gemm_sms ? ctas : g_gemm_sms);     // persistent: one CTA per SM
-    if (qs) qkernels[a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
+    if (qs) qkernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
     else kernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
     count_launch(1);
     return check_launch();
@@ -909,6 +934,18 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
     GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, M, N, K, batch, alpha, beta,
                C, ldc, strideC, D, ldd, strideD, nullptr, nullptr, 0, 0};
     return launch_gemm_planes(a, Amid, Bmid, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int qt_gemm_bf16x3_q4(const void *Ahi, const void *Alo, long long lda, long long strideA, int a_mn,
+                      const void *Bhi, const void *Blo, long long ldb, long long strideB, int b_mn,
+                      int n, int K, int batch, float alpha, float beta, const float *code,
+                      const unsigned char *q_in, const float *absmax_in, const float *diag_in,
+                      unsigned char *q_out, float *absmax_out, float *diag_out,
+                      long long stride_codes, long long stride_absmax, long long stride_diag, void *stream) {
+    GemmArgs a{Ahi, Alo, lda, strideA, a_mn, Bhi, Blo, ldb, strideB, b_mn, n, n, K, batch, alpha, beta,
+               nullptr, 0, 0, nullptr, 0, 0, nullptr, nullptr, 0, 0};
+    QuantStateArgs qs{code, q_in, absmax_in, diag_in, q_out, absmax_out, diag_out, stride_codes, stride_absmax, stride_diag};
+    return launch_gemm_planes(a, nullptr, nullptr, static_cast<cudaStream_t>(stream), &qs);
 }
 
 int qt_gemm_bf16x6_q4(const void *Ahi, const void *Amid, const void *Alo, long long lda, long long strideA, int a_mn,

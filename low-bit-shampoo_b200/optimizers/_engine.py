@@ -77,6 +77,16 @@ class QuantArena:
             st["diag"] = self.diag[i]
         return st
 
+    def fusable(self):
+        """True if a GEMM epilogue can read / write this arena's state directly
+        (qt_gemm_bf16x3_q4 / x6_q4: 4-bit, block 64, order a multiple of 16, CUDA)."""
+        return (self.lowbit and self.bits == 4 and self.blocksize == 64 and self.n % 16 == 0
+                and self.var.is_cuda and USE_TENSOR_CORES and FUSE_STATE_EPILOGUE and F.lib is not None)
+
+    def state(self, a, b):
+        """(codes, absmax, diag or None) views of matrices a..b-1, the operand form of _gemm.matmul_q4."""
+        return self.var[a:b], self.absmax[a:b], (self.diag[a:b] if self.diagreal else None)
+
     def dequantize(self, a, b):
         """fp32 (b-a, n, n) copy of matrices a..b-1."""
         if not self.lowbit:
@@ -150,6 +160,7 @@ class OrderClass:
 # state, used by the host-logic tests) the same operations are plain torch products.
 # ---------------------------------------------------------------------------------------
 USE_TENSOR_CORES = True
+FUSE_STATE_EPILOGUE = True     # products that end in 4-bit state quantize inside the GEMM epilogue
 # Set while an order class with plain 16/32-bit state, or a Schur-Newton inverse root, is
 # processed: those paths have no quantisation noise to hide the ~1e-5 relative error of the
 # split-bf16 products (and the Newton iteration amplifies it), so they stay on fp32 products.
@@ -291,6 +302,22 @@ def _index_tensor(ks, device):
     return t
 
 
+def _ema_update_fused(arena, a, grads_axes, w1, w2):
+    """state[a+k] <- quantize(w1 dequantize(state[a+k]) + w2 (G_k G_k^T | G_k^T G_k)) with the state read and
+    written by the product's epilogue (no fp32 copy of L).  Needs every group of equally shaped
+    blocks to occupy consecutive slots; returns False (nothing done) otherwise."""
+    groups = defaultdict(list)
+    for k, (g, axis) in enumerate(grads_axes):
+        groups[(tuple(g.shape), axis)].append(k)
+    if any(ks != list(range(ks[0], ks[0] + len(ks))) for ks in groups.values()):
+        return False
+    for (shape, axis), ks in groups.items():
+        P = _gemm.split3(torch.stack([grads_axes[k][0].float() for k in ks]))
+        st = arena.state(a + ks[0], a + ks[0] + len(ks))
+        _gemm.matmul_q4(P, P, arena.code, st, trans_a=(axis == 1), trans_b=(axis == 0), alpha=w2, beta=w1, old=st)
+    return True
+
+
 def _ema_update(L, grads_axes, w1, w2):
     """L[k] <- w1 L[k] + w2 * (G_k G_k^T | G_k^T G_k); blocks of equal shape are stacked."""
     groups = defaultdict(list)
@@ -357,6 +384,8 @@ def _class_statistics(cls, entries, w1, w2, eps, exact):
             if cls.flavour == "s1":
                 if REFERENCE_DIAGREAL_NONE and cls.stat.lowbit:
                     L = _eps_identity(cls, b - a, eps)
+                elif cls.stat.fusable() and not exact and _ema_update_fused(cls.stat, a, ga, w1, w2):
+                    continue
                 else:
                     L = cls.stat.dequantize(a, b)
                 cls.stat.quantize(a, b, _ema_update(L, ga, w1, w2))
@@ -419,6 +448,11 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent):
                         rows = op_bjorck(rows, want_planes=True)
                 rho = eps * cls.max_eig[a:b]
                 weights = 1 / (cls.S[a:b] + rho.unsqueeze(1)).pow(1 / exponent)
+                if cls.prec.fusable() and _tc(rows.f32 if rows.f32 is not None else rows._planes.hi):
+                    # rows^T diag(w) rows straight into the 4-bit preconditioner (quantized in the epilogue)
+                    scaled = Mat(weights.unsqueeze(2) * rows.f32)
+                    _gemm.matmul_q4(rows.planes, scaled.planes, cls.prec.code, cls.prec.state(a, b), trans_a=True)
+                    continue
                 P = op_scaled_gram(rows, weights).f32
             else:
                 Vt = Mat(cls.stat.dequantize(a, b))

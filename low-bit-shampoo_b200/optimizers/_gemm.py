@@ -136,7 +136,7 @@ def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=
 def matmul_q4(A, B, code, out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, old=None):
     """out <- quantize(alpha * op(A) @ op(B) + beta * dequantize(old)) on 4-bit block-64 state.
 
-    A, B: three-plane Planes of a square product (b, n, n), n a multiple of 16.  `out` and
+    A, B: Planes (both two-plane or both three-plane) of a square product (b, n, n), n a multiple of 16.  `out` and
     `old` are (codes uint8 (b, row_bytes), absmax fp32 (b, n*nb), diag fp32 (b, n) or None);
     `old=None` drops the C operand, `old is out` updates in place.  Same bytes as
     dequantize -> six-product GEMM -> quantize, without an fp32 copy of the state in HBM
@@ -146,7 +146,7 @@ def matmul_q4(A, B, code, out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0
     K = A.rows if trans_a else A.cols
     Kb = B.cols if trans_b else B.rows
     N = B.rows if trans_b else B.cols
-    assert K == Kb and A.batch == B.batch and M == N and A.mid is not None and B.mid is not None
+    assert K == Kb and A.batch == B.batch and M == N and (A.mid is None) == (B.mid is None)
     b = A.batch
     var, absmax, diag = out
     assert var.dtype == torch.uint8 and var.dim() == 2 and var.shape[0] == b and var.stride(1) == 1
@@ -156,13 +156,18 @@ def matmul_q4(A, B, code, out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0
         ovar, oabs, odiag = old
         assert ovar.stride(0) == var.stride(0) and oabs.stride(0) == absmax.stride(0)
         assert odiag is None or diag is None or odiag.stride(0) == diag.stride(0)
-    with torch.cuda.device(var.device):
-        rc = F.lib.qt_gemm_bf16x6_q4(
-            A.ptr_hi(), _ptr(A.mid), A.ptr_lo(), A.ld, A.stride, 1 if trans_a else 0,
-            B.ptr_hi(), _ptr(B.mid), B.ptr_lo(), B.ld, B.stride, 0 if trans_b else 1,
-            N, K, b, float(alpha), float(beta), _ptr(code),
+    tail = (N, K, b, float(alpha), float(beta), _ptr(code),
             _ptr(ovar), _ptr(oabs), _ptr(odiag), _ptr(var), _ptr(absmax), _ptr(diag),
             var.stride(0), absmax.stride(0),
             (diag if diag is not None else odiag).stride(0) if (diag is not None or odiag is not None) else 0,
             F._stream(var))
-    F._check(rc, "gemm_bf16x6_q4")
+    with torch.cuda.device(var.device):
+        if A.mid is not None:
+            rc = F.lib.qt_gemm_bf16x6_q4(
+                A.ptr_hi(), _ptr(A.mid), A.ptr_lo(), A.ld, A.stride, 1 if trans_a else 0,
+                B.ptr_hi(), _ptr(B.mid), B.ptr_lo(), B.ld, B.stride, 0 if trans_b else 1, *tail)
+        else:
+            rc = F.lib.qt_gemm_bf16x3_q4(
+                A.ptr_hi(), A.ptr_lo(), A.ld, A.stride, 1 if trans_a else 0,
+                B.ptr_hi(), B.ptr_lo(), B.ld, B.stride, 0 if trans_b else 1, *tail)
+    F._check(rc, "gemm_q4")
