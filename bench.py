@@ -221,6 +221,99 @@ def gemm_roofline(torch, device, iters=20):
             "flops_per_launch": flops, "case": f"{count} x ({n} x {n}) @ ({n} x {n})^T, bf16 hi/lo planes in, fp32 out"}
 
 
+def _time_cuda(torch, fn, warmup, iters):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def kernel_sweep(torch, device, orders=(128, 512, 1200, 2048, 4096, 8192), count=64):
+    """Kernel sweep of the fused statistics update L <- beta L + (1-beta) G G^T on 4-bit state
+    (dequantize and quantize inside the GEMM epilogue) and of the inverse 4th root, 64 matrices
+    per order.  G ~ N(0, 1/n) fp32; L = Q diag(lambda) Q^T with lambda log-uniform in [1e-6, 1],
+    stored 4-bit diagreal, block 64, beta = 0.95.  One JSON line per order; every working set
+    is far larger than L2.  Checks on the way: the fused bytes equal the unfused sequence's."""
+    import qtensor.functional as F
+    from optimizers import _gemm, matrix_functions as MF
+    from optimizers import _engine as E
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    code = F.create_linear_map(True, 4, 2).to(device)
+    gen = torch.Generator(device=device).manual_seed(0)
+    beta = 0.95
+    for n in orders:
+        torch.cuda.empty_cache()
+        nb = (n + 63) // 64
+        Q = torch.linalg.qr(torch.randn(n, n, device=device, generator=gen)).Q
+        arena = E.QuantArena(n, count, device, 4, 64, code, 4096, diagreal=True)
+        step = max(1, min(count, (1 << 28) // (n * n)))
+        for a in range(0, count, step):
+            lam = torch.exp(torch.rand(min(step, count - a), n, device=device, generator=gen) * 13.8155 - 13.8155)
+            L = (Q.unsqueeze(0) * lam.unsqueeze(1)) @ Q.t()
+            arena.quantize(a, a + L.shape[0], (0.5 * (L + L.transpose(1, 2))).contiguous())
+        del L, lam
+        G = torch.randn(count, n, n, device=device, generator=gen) / n ** 0.5
+        st = arena.state(0, count)
+        out = tuple(None if t is None else torch.empty_like(t) for t in st)
+        iters = 10 if n <= 1200 else 3
+        # fused: split G once per update (part of the operation), product + state in the epilogue
+        P = _gemm.split3(G)
+        t_split = _time_cuda(torch, lambda: _gemm.split3(G), 1, iters)
+        t_fused = _time_cuda(torch, lambda: _gemm.matmul_q4(P, P, code, out, trans_b=True, alpha=1 - beta, beta=beta, old=st),
+                             2, iters)
+        # unfused sequence with the same kernels: dequantize -> product (fp32 C and D) -> quantize
+        want = E.QuantArena(n, count, device, 4, 64, code, 4096, diagreal=True)
+
+        def unfused():
+            Lf = arena.dequantize(0, count)
+            D, _ = _gemm.matmul(P, P, trans_b=True, alpha=1 - beta, beta=beta, C=Lf, out=Lf)
+            want.quantize(0, count, D)
+        t_unfused = _time_cuda(torch, unfused, 1, iters)
+        same = all(torch.equal(a_, b_) for a_, b_ in zip(out, want.state(0, count)))
+        del want
+        # inverse 4th root, factor form (functional.py:749-762): rows = kept half of a 4-bit
+        # orthogonal factor, 4 Bjorck steps, rows^T diag((S + rho)^-1/4) rows quantized in the epilogue
+        fac = E.QuantArena(n, count, device, 4, 64, code, 4096, diagreal=False)
+        for a in range(0, count, step):
+            fac.quantize(a, min(count, a + step), Q.t().contiguous().unsqueeze(0).expand(min(step, count - a), n, n).contiguous())
+        S = torch.exp(torch.rand(count, n // 2, device=device, generator=gen) * 13.8155 - 13.8155)
+        prec = E.QuantArena(n, count, device, 4, 64, code, 4096, diagreal=True)
+
+        def factor_root():
+            rows = E.Mat(fac.dequantize(0, count)[:, : n // 2, :])
+            for _ in range(4):
+                rows = E.op_bjorck(rows, want_planes=True)
+            w = 1 / (S + 1e-6).pow(0.25)
+            scaled = E.Mat(w.unsqueeze(2) * rows.f32)
+            _gemm.matmul_q4(rows.planes, scaled.planes, code, prec.state(0, count), trans_a=True)
+        t_root = _time_cuda(torch, factor_root, 1, iters)
+        del fac, prec
+        t_newton = None
+        if n <= 2048:                                        # Schur-Newton (matrix_functions.py:80-141), fp32 library products
+            Lf = arena.dequantize(0, count)
+            t_newton = _time_cuda(torch, lambda: MF.ComputePower(Lf.clone(), 4, ridge_epsilon=1e-6), 1, 2)
+            del Lf
+        state_bytes = (n * n) // 2 + 4 * n * nb + 4 * n
+        algo_bytes = count * (4 * n * n + 2 * state_bytes)               # read G, read + write the 4-bit state
+        flops = 2.0 * count * n ** 3
+        line = {"case": "fused statistics update on 4-bit state", "n": n, "matrices": count, "beta": beta,
+                "fused_us": t_fused * 1e3, "split_us": t_split * 1e3, "unfused_us": t_unfused * 1e3,
+                "fused_equals_unfused_bytes": bool(same),
+                "algorithmic_bytes": algo_bytes, "gbs": algo_bytes / (t_fused + t_split) / 1e6,
+                "gbs_frac_of_measured_copy": algo_bytes / (t_fused + t_split) / 1e6 / hbm_peak,
+                "tflops_algorithmic": flops / t_fused / 1e9, "tflops_executed": 6 * flops / t_fused / 1e9,
+                "tensor_frac_of_measured_sustained": 6 * flops / t_fused / 1e9 / tensor_peak,
+                "peaks": peak_kind, "factor_root_us": t_root * 1e3, "newton_root_us": None if t_newton is None else t_newton * 1e3}
+        print(json.dumps(line), flush=True)
+        del G, P, arena, out, st
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -365,9 +458,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of as a captured CUDA graph")
+    ap.add_argument("--sweep", action="store_true",
+                    help="kernel sweep of the fused 4-bit statistics update and the inverse 4th root over orders 128..8192")
+    ap.add_argument("--sweep-orders", default="128,512,1200,2048,4096,8192")
     ap.add_argument("--profile-case", default=None, choices=["quant", "gemm"],
                     help="run only one small kernel case (for an ncu capture) and print its rates")
     args = ap.parse_args()
+    if args.sweep:
+        import torch
+        from qtensor.cextension import get_lib
+        get_lib()
+        kernel_sweep(torch, torch.device("cuda", 0), orders=tuple(int(x) for x in args.sweep_orders.split(",")))
+        return
     if args.profile_case == "quant":
         import torch
         from qtensor.cextension import get_lib

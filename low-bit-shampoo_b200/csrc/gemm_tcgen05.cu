@@ -52,6 +52,23 @@ struct GemmParams {
     const float *q_code; int q_nb;
 };
 
+// Tile number -> (row band, column band, matrix).  Within a matrix the tiles are walked in groups
+// of RASTER_M row bands, column by column, so that the ~148 tiles in flight at any moment form a
+// roughly square patch: both operands' k-panels are then shared by a dozen CTAs through L2
+// instead of one operand by all and the other by two (matters once a matrix exceeds L2).
+static constexpr int RASTER_M = 12;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int &tm, int &tn, int &b) {
+    const int per_matrix = tiles_m * tiles_n;
+    b = tile / per_matrix;
+    const int t = tile - b * per_matrix;
+    const int group = t / (RASTER_M * tiles_n);
+    const int first_m = group * RASTER_M;
+    const int gsize = min(tiles_m - first_m, RASTER_M);
+    const int r = t - group * RASTER_M * tiles_n;
+    tn = r / gsize;
+    tm = first_m + (r - tn * gsize);
+}
+
 template <bool Q> struct QuantTablesHolder { CodeTables<16> t; };
 template <> struct QuantTablesHolder<false> { int unused; };
 
@@ -286,7 +303,8 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             unsigned it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int tn = tile % p.tiles_n, tm = (tile / p.tiles_n) % p.tiles_m, b = tile / (p.tiles_n * p.tiles_m);
+                int tm, tn, b;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
                 const int m0 = tm * BM, n0 = tn * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -388,7 +406,8 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             // chunked accumulation: partial sums of KC k-blocks are added in registers
             int j = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                const int tn = tile % p.tiles_n, tm = (tile / p.tiles_n) % p.tiles_m, b = tile / (p.tiles_n * p.tiles_m);
+                int tm, tn, b;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
                 const int m0 = tm * BM, n0 = tn * BN;
                 const int row = m0 + warp * 32 + lane;
                 const bool row_ok = row < p.M;
@@ -442,7 +461,8 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         } else {
         int i = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
-            const int tn = tile % p.tiles_n, tm = (tile / p.tiles_n) % p.tiles_m, b = tile / (p.tiles_n * p.tiles_m);
+            int tm, tn, b;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
             const int m0 = tm * BM, n0 = tn * BN;
             const int acc = i & 1;
             const int row = m0 + warp * 32 + lane;
