@@ -117,6 +117,21 @@ int qt_dequantize_blockwise(const unsigned char *A, long long strideA,
                             int blocksize, int bits, void *stream);
 
 /*
+ * Dequantize into the operand format of the tcgen05 products (two bf16 planes hi, lo with
+ * x = hi + lo to 16 bits, row pitch ldp elements, strideP elements between matrices; see
+ * qt_split_bf16).  Output matrix j is read from state slot slots[j] (device int32 array), or
+ * from slot j when slots is NULL; A, absmax and diag point at slot 0.  The values equal
+ * qt_dequantize_blockwise followed by qt_split_bf16; the fp32 matrix, the gather of scattered
+ * slots and the split pass never touch device memory.  This is the dequantize side of
+ * preconditioned_grad (optimizers/shampoo2.py:258-268), where the dequantized preconditioners
+ * are only ever product operands.  order must be a multiple of 8.
+ */
+int qt_dequantize_planes(const unsigned char *A, long long strideA, const float *code, int order, int count,
+                         const float *absmax, long long stride_absmax, const float *diag, long long stride_diag,
+                         const int *slots, void *hi, void *lo, long long ldp, long long strideP,
+                         int blocksize, int bits, void *stream);
+
+/*
  * Self-test of the quantizer's division: the kernels replace x / absmax by an exact
  * reciprocal plus two fused corrections; this entry point compares that sequence with the
  * IEEE division on `pairs` pseudo-random operand pairs (seeded) and ADDS the number of

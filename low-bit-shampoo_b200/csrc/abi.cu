@@ -94,6 +94,15 @@ int qt_dequantize_blockwise(const unsigned char *A, long long strideA, const flo
     return launch_dequantize(a, static_cast<cudaStream_t>(stream));
 }
 
+int qt_dequantize_planes(const unsigned char *A, long long strideA, const float *code, int order, int count,
+                         const float *absmax, long long stride_absmax, const float *diag, long long stride_diag,
+                         const int *slots, void *hi, void *lo, long long ldp, long long strideP,
+                         int blocksize, int bits, void *stream) {
+    DequantArgs a{A, strideA, code, order, count, blocksize, bits, absmax, stride_absmax,
+                  diag, stride_diag, nullptr, QT_BF16, 0};
+    return launch_dequantize_planes(a, slots, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
+}
+
 int qt_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches, void *stream) {
     return launch_selftest_division(seed, pairs, mismatches, static_cast<cudaStream_t>(stream));
 }

@@ -39,6 +39,9 @@ struct DequantArgs {
 
 int launch_quantize(const QuantArgs &a, cudaStream_t stream);
 int launch_dequantize(const DequantArgs &a, cudaStream_t stream);
+// a.out / a.out_dtype / a.stride_out are ignored: output goes to the bf16 planes hi, lo
+int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, void *lo, long long ldp, long long strideP,
+                             cudaStream_t stream);
 int launch_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches_dev,
                              cudaStream_t stream);
 int launch_householder_panel(const float *A, long long strideA, int n, int count, int j0, int w,

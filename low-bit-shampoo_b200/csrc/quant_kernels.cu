@@ -360,6 +360,84 @@ k_dequantize_vec(const unsigned char *__restrict__ in_base, long long stride_in,
     }
 }
 
+// ------------------------------------------------------------------------------------
+// Dequantize straight into the operand format of the tcgen05 products: two bf16 planes
+// (hi = bf16(x), lo = bf16(x - hi)) with row pitch ldp.  Output matrix j is taken from state
+// slot slots[j] (or j when slots == nullptr), so a product's batch can be assembled from
+// scattered slots of an arena without an fp32 copy, a stack and a split pass in between.
+// Eight elements per thread: one 32/64-bit code load, two 128-bit stores.
+// ------------------------------------------------------------------------------------
+template <int BITS>
+__global__ void __launch_bounds__(kThreads)
+k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_in, const float *__restrict__ code,
+                    int n, int nb, int bs_shift, const float *__restrict__ absmax_base, long long stride_absmax,
+                    const float *__restrict__ diag_base, long long stride_diag, const int *__restrict__ slots,
+                    __nv_bfloat16 *__restrict__ hi_base, __nv_bfloat16 *__restrict__ lo_base, long long ldp, long long strideP) {
+    constexpr int NC = 1 << BITS, EPL = 8;
+    __shared__ float2 pair_lut[BITS == 4 ? 256 : 1];
+    __shared__ float code_s[BITS == 8 ? 256 : 16];
+    for (int i = threadIdx.x; i < NC; i += blockDim.x) code_s[i] = code[i];
+    __syncthreads();
+    if (BITS == 4)
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) pair_lut[i] = make_float2(code_s[i >> 4], code_s[i & 15]);
+    __syncthreads();
+
+    const int m = blockIdx.y;
+    const long long src = slots ? (long long)slots[m] : (long long)m;
+    const unsigned char *in = in_base + src * stride_in;
+    const float *absmax = absmax_base + src * stride_absmax;
+    const float *diag = diag_base ? diag_base + src * stride_diag : nullptr;
+    __nv_bfloat16 *hi = hi_base + (long long)m * strideP, *lo = lo_base + (long long)m * strideP;
+
+    const int chunks_per_row = n / EPL;
+    const int chunks = n * chunks_per_row;
+    const int S = gridDim.x * kThreads;
+    int t = blockIdx.x * kThreads + threadIdx.x;
+    int r = t / chunks_per_row, cc = t - r * chunks_per_row;
+    const int dr = S / chunks_per_row, dc = S - dr * chunks_per_row;
+#pragma unroll 2
+    for (; t < chunks; t += S) {
+        const int c = cc * EPL;
+        const long long e = (long long)r * n + c;
+        const float amax = __ldg(absmax + (long long)r * nb + (c >> bs_shift));
+        const float z = (amax == 0.0f) ? 0.0f : -0.0f;        // exact +0.0 for all-zero blocks
+        float v[EPL];
+        if constexpr (BITS == 4) {
+            const unsigned w = __ldg(reinterpret_cast<const unsigned *>(in + (e >> 1)));
+#pragma unroll
+            for (int j = 0; j < EPL / 2; ++j) {
+                const float2 pr = pair_lut[(w >> (8 * j)) & 255u];
+                v[2 * j] = fmaf(pr.x, amax, z);
+                v[2 * j + 1] = fmaf(pr.y, amax, z);
+            }
+        } else {
+            const uint2 ww = __ldg(reinterpret_cast<const uint2 *>(in + e));
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) v[j] = fmaf(code_s[((j < 4 ? ww.x : ww.y) >> (8 * (j & 3))) & 255u], amax, z);
+        }
+        if (diag && (unsigned)(r - c) < (unsigned)EPL) {
+            const float d = diag[r];
+#pragma unroll
+            for (int j = 0; j < EPL; ++j)
+                if (c + j == r) v[j] = d;
+        }
+        unsigned h[4], l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * j]), h1 = __float2bfloat16_rn(v[2 * j + 1]);
+            const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * j] - __bfloat162float(h0));
+            const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * j + 1] - __bfloat162float(h1));
+            h[j] = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
+            l[j] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
+        }
+        const long long o = (long long)r * ldp + c;
+        *reinterpret_cast<uint4 *>(hi + o) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4 *>(lo + o) = make_uint4(l[0], l[1], l[2], l[3]);
+        r += dr; cc += dc;
+        if (cc >= chunks_per_row) { cc -= chunks_per_row; r += 1; }
+    }
+}
+
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
@@ -595,6 +673,32 @@ int launch_dequantize(const DequantArgs &a, cudaStream_t s) {
     } else {
         if (a.bits == 4) launch_dequantize_typed<__nv_bfloat16, 4>(a, s); else launch_dequantize_typed<__nv_bfloat16, 8>(a, s);
     }
+    return check_launch();
+}
+
+int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, void *lo, long long ldp, long long strideP,
+                             cudaStream_t s) {
+    if (a.bits != 4 && a.bits != 8) return record(QT_ERR_BITS);
+    if (!valid_blocksize(a.bs)) return record(QT_ERR_BLOCKSIZE);
+    if (a.n < 0 || a.count < 0 || a.n > 46340 || a.count > 65535) return record(QT_ERR_ARG);
+    if (a.n == 0 || a.count == 0) return record(QT_OK);
+    if (!a.A || !a.code || !a.absmax || !hi || !lo) return record(QT_ERR_ARG);
+    // eight elements per thread: 16-byte plane stores, 4/8-byte code loads
+    if (a.n % 8 || ldp % 8 || strideP % 8 || !aligned(hi, 16) || !aligned(lo, 16) || ldp < a.n) return record(QT_ERR_UNSUPPORTED);
+    const int in_bytes = a.bits == 4 ? 4 : 8;
+    if (!aligned(a.A, in_bytes) || a.strideA % in_bytes) return record(QT_ERR_UNSUPPORTED);
+    if (!aligned(a.absmax, 4) || !aligned(a.code, 4) || (a.diag && !aligned(a.diag, 4))) return record(QT_ERR_ARG);
+    const int n = a.n, nb = (n + a.bs - 1) / a.bs;
+    int bs_shift = 0;
+    while ((1 << bs_shift) < a.bs) ++bs_shift;
+    dim3 grid(grid_x_for((long long)n * (n / 8), a.count, 4), a.count);
+    if (a.bits == 4)
+        k_dequantize_planes<4><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax, a.stride_absmax,
+            a.diag, a.stride_diag, slots, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    else
+        k_dequantize_planes<8><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax, a.stride_absmax,
+            a.diag, a.stride_diag, slots, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    count_launch(1);
     return check_launch();
 }
 

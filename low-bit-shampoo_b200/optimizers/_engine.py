@@ -87,6 +87,20 @@ class QuantArena:
         """(codes, absmax, diag or None) views of matrices a..b-1, the operand form of _gemm.matmul_q4."""
         return self.var[a:b], self.absmax[a:b], (self.diag[a:b] if self.diagreal else None)
 
+    def dequantize_planes(self, slots):
+        """Matrices `slots` (any order, repeats allowed) as bf16 hi/lo Planes, written by the
+        dequantize kernel itself: no fp32 copy, no gather, no split pass (qt_dequantize_planes)."""
+        n, m = self.n, len(slots)
+        P = _gemm.Planes(m, n, n, self.device)
+        idx = _index_tensor(list(slots), self.device, torch.int32)
+        with torch.cuda.device(self.device):
+            rc = F.lib.qt_dequantize_planes(
+                _ptr(self.var), self.row_bytes, _ptr(self.code), n, m, _ptr(self.absmax), n * self.nb,
+                _ptr(self.diag) if self.diagreal else None, n, _ptr(idx),
+                P.ptr_hi(), P.ptr_lo(), P.ld, P.stride, self.blocksize, self.bits, F._stream(self.var))
+        F._check(rc, "dequantize to planes")
+        return P
+
     def dequantize(self, a, b):
         """fp32 (b-a, n, n) copy of matrices a..b-1."""
         if not self.lowbit:
@@ -161,6 +175,7 @@ class OrderClass:
 # ---------------------------------------------------------------------------------------
 USE_TENSOR_CORES = True
 FUSE_STATE_EPILOGUE = True     # products that end in 4-bit state quantize inside the GEMM epilogue
+DEQUANTIZE_TO_PLANES = True    # preconditioners are dequantized straight into bf16 operand planes
 # Set while an order class with plain 16/32-bit state, or a Schur-Newton inverse root, is
 # processed: those paths have no quantisation noise to hide the ~1e-5 relative error of the
 # split-bf16 products (and the Newton iteration amplifies it), so they stay on fp32 products.
@@ -292,13 +307,13 @@ def _gather_rows(Vt, idx):
 _INDEX_CACHE = {}
 
 
-def _index_tensor(ks, device):
+def _index_tensor(ks, device, dtype=torch.int64):
     """Device copy of a small index list, cached: the same lists recur every step, and a
     host-to-device copy is not allowed while a CUDA graph is being captured."""
-    key = (str(device), tuple(ks))
+    key = (str(device), tuple(ks), dtype)
     t = _INDEX_CACHE.get(key)
     if t is None:
-        t = _INDEX_CACHE[key] = torch.tensor(ks, device=device)
+        t = _INDEX_CACHE[key] = torch.tensor(ks, device=device, dtype=dtype)
     return t
 
 
@@ -464,8 +479,44 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent):
             cls.prec.quantize(a, b, P)
 
 
+def _planes_direct(cls, dtype):
+    """True if this class's preconditioners can be dequantized straight into product operands."""
+    a = cls.prec
+    return (a.lowbit and a.n % 8 == 0 and dtype == torch.float32 and a.var.is_cuda and USE_TENSOR_CORES
+            and DEQUANTIZE_TO_PLANES and F.lib is not None and not _EXACT and not REFERENCE_DIAGREAL_NONE)
+
+
 def preconditioned_blocks(items):
     """items: list of (cls0, slot0, cls1, slot1, grad_block).  Returns [P0 G P1 for each]."""
+    out = [None] * len(items)
+    # Fast path: 4-bit preconditioners are only ever product operands here, so they are dequantized
+    # straight into bf16 planes, already stacked in the order of the blocks that use them.
+    rest = []
+    direct = defaultdict(list)
+    for k, (c0, s0, c1, s1, g) in enumerate(items):
+        if _planes_direct(c0, g.dtype) and _planes_direct(c1, g.dtype):
+            direct[(c0, c1, tuple(g.shape))].append(k)
+        else:
+            rest.append(k)
+    for (c0, c1, shape), ks in direct.items():
+        cap = max(1, _TEMP_ELEMS // max(shape[0] * shape[0], shape[1] * shape[1], 1))
+        for s in range(0, len(ks), cap):
+            part = ks[s: s + cap]
+            G = torch.stack([items[k][4] for k in part])
+            P0 = Mat(planes=c0.prec.dequantize_planes([items[k][1] for k in part]))
+            P1 = Mat(planes=c1.prec.dequantize_planes([items[k][3] for k in part]))
+            T = mm(P0, Mat(G), want_float=False, want_planes=True)
+            R = mm(T, P1).f32
+            for j, k in enumerate(part):
+                out[k] = R[j]
+    if not rest:
+        return out
+    for k, r in zip(rest, _preconditioned_blocks_general([items[k] for k in rest])):
+        out[k] = r
+    return out
+
+
+def _preconditioned_blocks_general(items):
     needed = defaultdict(set)
     for c0, s0, c1, s1, _ in items:
         needed[c0].add(s0)

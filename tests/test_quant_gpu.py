@@ -264,3 +264,31 @@ def test_fast_division_is_bit_identical_to_ieee_division(native_lib):
         assert rc == 0
     torch.cuda.synchronize()
     assert int(counter.item()) == 0
+
+
+@pytest.mark.parametrize("n,bits,diagreal", [(768, 4, True), (1200, 4, True), (72, 4, False), (256, 8, True), (1000, 4, True)])
+def test_dequantize_to_planes_equals_dequantize_then_split(native_lib, n, bits, diagreal):
+    """qt_dequantize_planes (with a slot gather) writes exactly the bf16 hi/lo planes that
+    dequantize -> split produce, for scattered and repeated slots."""
+    import ctypes as ct
+    import qtensor.functional as F
+    from optimizers import _engine as E, _gemm
+    dev = "cuda"
+    code = F.create_linear_map(True, bits, 2).to(dev)
+    count = 7
+    arena = E.QuantArena(n, count, dev, bits, 64, code, 4096, diagreal=diagreal)
+    g = torch.Generator(device=dev).manual_seed(n + bits)
+    X = torch.randn(count, n, n, device=dev, generator=g) * torch.logspace(-4, 2, count, device=dev)[:, None, None]
+    X[2].zero_()
+    arena.quantize(0, count, X)
+    slots = [5, 0, 2, 2, 6]
+    P = arena.dequantize_planes(slots)
+    full = arena.dequantize(0, count)
+    want = _gemm.split(full[slots].contiguous())
+    torch.cuda.synchronize()
+    assert native_lib.qt_last_error() == 0
+    k = (n - 1) * P.ld + n
+    hi, lo = P.hi.view(len(slots), n, P.ld)[:, :, :n], P.lo.view(len(slots), n, P.ld)[:, :, :n]
+    whi, wlo = want.hi.view(len(slots), n, want.ld)[:, :, :n], want.lo.view(len(slots), n, want.ld)[:, :, :n]
+    assert torch.equal(hi.view(torch.int16), whi.view(torch.int16))
+    assert torch.equal(lo.view(torch.int16), wlo.view(torch.int16))
