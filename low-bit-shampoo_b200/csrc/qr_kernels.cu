@@ -25,21 +25,25 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// Register-resident panel: warp c owns column c, lane l holds rows l, l+32, ... of it (RPL
-// values) for the whole factorisation.  Per column step the pivot warp builds its Householder
-// vector from registers and publishes it once through a double-buffered shared-memory vector;
-// the warps to its right apply the reflector to their own registers, the warps to its left
-// (already final) take the dot product v_i . v_c needed for the triangular factor T.  Shared
-// memory traffic per step is one vector write and one read per warp, one barrier per step.
-template <int RPL>
+// Register-resident panel: warp c owns column c, lane l holds rows l, l+32, ... of it for the
+// whole factorisation: the first RPL of them in registers, RS more (tall panels only) in the
+// column's slots of the shared staging buffer, so that the register budget of a 1024-thread CTA
+// (64 per thread) is never exceeded.  Per column step the pivot warp builds its Householder
+// vector and publishes it once through a double-buffered shared-memory vector; the warps to
+// its right apply the reflector to their own column, the warps to its left (already final)
+// take the dot product v_i . v_c needed for the triangular factor T, and warp 0 fills in
+// column c-1 of T meanwhile (slarft recurrence), off the critical path.  One barrier per step;
+// every reduction chain is split over four accumulators.
+template <int RPL, int RS>
 __global__ void __launch_bounds__(kQrThreads, 1)
 k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, int j0, int w,
                     float *__restrict__ Vbase, long long strideV, float *__restrict__ Tbase, long long strideT) {
+    constexpr int RT = RPL + RS;
     extern __shared__ float sm[];
     const int m = n - j0;
     float *P = sm;                                         // [m][33] staging for coalesced global access
-    float *vb = P + ((m * 33 + 31) & ~31);                 // [2][RPL * 32] published Householder vector
-    float *G = vb + 2 * RPL * 32;                          // [32][33]  v_i . v_j, i < j
+    float *vb = P + ((m * 33 + 31) & ~31);                 // [2][RT * 32] published Householder vector
+    float *G = vb + 2 * RT * 32;                           // [32][33]  v_i . v_j, i < j
     float *Ts = G + kPanel * (kPanel + 1);                 // [32][33]
     float *tau = Ts + kPanel * (kPanel + 1);               // [32]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -54,14 +58,43 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
         const int r = lane + 32 * k;
         col[k] = (r < m) ? P[r * 33 + warp] : 0.0f;
     }
+    // element k of this lane's part of the column (k is a compile-time constant after unrolling)
+    auto get = [&](int k) -> float {
+        if (k < RPL) return col[k < RPL ? k : 0];
+        const int r = lane + 32 * k;
+        return r < m ? P[r * 33 + warp] : 0.0f;
+    };
+    auto put = [&](int k, float v) {
+        if (k < RPL) { col[k < RPL ? k : 0] = v; return; }
+        const int r = lane + 32 * k;
+        if (r < m) P[r * 33 + warp] = v;
+    };
+    auto t_column = [&](int i) {                            // LAPACK slarft, forward / columnwise; whole warp
+        const float ti = tau[i];
+        if (lane == i) Ts[i * (kPanel + 1) + i] = ti;
+        if (lane < i) {
+            float a0 = 0.0f, a1 = 0.0f;
+            int l = lane;
+            for (; l + 1 < i; l += 2) {
+                a0 = fmaf(Ts[lane * (kPanel + 1) + l], G[l * (kPanel + 1) + i], a0);
+                a1 = fmaf(Ts[lane * (kPanel + 1) + l + 1], G[(l + 1) * (kPanel + 1) + i], a1);
+            }
+            if (l < i) a0 = fmaf(Ts[lane * (kPanel + 1) + l], G[l * (kPanel + 1) + i], a0);
+            Ts[lane * (kPanel + 1) + i] = -ti * (a0 + a1);
+        }
+        __syncwarp();
+    };
 
     for (int c = 0; c < w; ++c) {
-        float *vbuf = vb + (c & 1) * (RPL * 32);
+        float *vbuf = vb + (c & 1) * (RT * 32);
         if (warp == c) {
-            float s = 0.0f;
+            float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int k = 0; k < RPL; ++k) s = (lane + 32 * k > c) ? fmaf(col[k], col[k], s) : s;
-            const float sigma = warp_sum(s);
+            for (int k = 0; k < RT; ++k) {
+                const float x = get(k);
+                s4[k & 3] = (lane + 32 * k > c) ? fmaf(x, x, s4[k & 3]) : s4[k & 3];
+            }
+            const float sigma = warp_sum((s4[0] + s4[1]) + (s4[2] + s4[3]));
             const float alpha = __shfl_sync(0xffffffffu, col[0], c);      // row c lives in lane c, slot 0
             float tc = 0.0f, scale = 0.0f;
             if (sigma != 0.0f) {
@@ -70,42 +103,33 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
                 scale = 1.0f / (alpha - beta);
             }
 #pragma unroll
-            for (int k = 0; k < RPL; ++k) {
+            for (int k = 0; k < RT; ++k) {
                 const int r = lane + 32 * k;
-                const float v = (r > c) ? col[k] * scale : (r == c ? 1.0f : 0.0f);
-                col[k] = v;                                 // the column now holds v_c (zeros above, one on the diagonal)
+                const float v = (r > c) ? get(k) * scale : (r == c ? 1.0f : 0.0f);
+                put(k, v);                                  // the column now holds v_c (zeros above, one on the diagonal)
                 vbuf[k * 32 + lane] = v;
             }
             if (lane == 0) tau[c] = tc;
         }
         __syncthreads();
         if (warp != c && warp < w) {
-            float d = 0.0f;
+            float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int k = 0; k < RPL; ++k) d = fmaf(vbuf[k * 32 + lane], col[k], d);
-            d = warp_sum(d);
+            for (int k = 0; k < RT; ++k) d4[k & 3] = fmaf(vbuf[k * 32 + lane], get(k), d4[k & 3]);
+            const float d = warp_sum((d4[0] + d4[1]) + (d4[2] + d4[3]));
             if (warp > c) {                                 // apply H_c = I - tau v v^T to this column
                 const float f = tau[c] * d;
 #pragma unroll
-                for (int k = 0; k < RPL; ++k) col[k] = fmaf(-f, vbuf[k * 32 + lane], col[k]);
+                for (int k = 0; k < RT; ++k) put(k, fmaf(-f, vbuf[k * 32 + lane], get(k)));
             } else if (lane == 0) {
                 G[warp * (kPanel + 1) + c] = d;             // v_warp . v_c
             }
         }
+        // column c-1 of T: its dot products were completed before this step's barrier
+        if (warp == 0 && c >= 1) t_column(c - 1);
     }
     __syncthreads();
-    if (warp == 0) {                                        // LAPACK slarft, forward / columnwise
-        for (int i = 0; i < w; ++i) {
-            const float ti = tau[i];
-            if (lane == i) Ts[i * (kPanel + 1) + i] = ti;
-            if (lane < i) {
-                float acc = 0.0f;
-                for (int l = lane; l < i; ++l) acc = fmaf(Ts[lane * (kPanel + 1) + l], G[l * (kPanel + 1) + i], acc);
-                Ts[lane * (kPanel + 1) + i] = -ti * acc;
-            }
-            __syncwarp();
-        }
-    }
+    if (warp == 0) t_column(w - 1);
 #pragma unroll
     for (int k = 0; k < RPL; ++k) {
         const int r = lane + 32 * k;
@@ -119,19 +143,19 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
     for (int i = tid; i < kPanel * kPanel; i += kQrThreads) T[i] = Ts[(i / kPanel) * (kPanel + 1) + (i % kPanel)];
 }
 
-template <int RPL>
+template <int RPL, int RS>
 static int launch_panel_rpl(const float *A, long long strideA, int n, int count, int j0, int w,
                             float *V, long long strideV, float *T, long long strideT, cudaStream_t s) {
     const int m = n - j0;
-    const size_t smem = sizeof(float) * ((size_t)((m * 33 + 31) & ~31) + 2 * RPL * 32 + 2 * kPanel * (kPanel + 1) + kPanel);
+    const size_t smem = sizeof(float) * ((size_t)((m * 33 + 31) & ~31) + 2 * (RPL + RS) * 32 + 2 * kPanel * (kPanel + 1) + kPanel);
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(k_householder_panel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_householder_panel<RPL, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
             return record(QT_ERR_LAUNCH);
         attr_set = true;
     }
     if (smem > 227 * 1024) return record(QT_ERR_UNSUPPORTED);
-    k_householder_panel<RPL><<<count, kQrThreads, smem, s>>>(A, strideA, n, j0, w, V, strideV, T, strideT);
+    k_householder_panel<RPL, RS><<<count, kQrThreads, smem, s>>>(A, strideA, n, j0, w, V, strideV, T, strideT);
     count_launch(1);
     return check_launch();
 }
@@ -143,12 +167,12 @@ int launch_householder_panel(const float *A, long long strideA, int n, int count
     if (count == 0) return record(QT_OK);
     const int rows_per_lane = (n - j0 + 31) / 32;
     if (rows_per_lane > kMaxRowsPerLane) return record(QT_ERR_UNSUPPORTED);
-#define QT_PANEL(R) return launch_panel_rpl<R>(A, strideA, n, count, j0, w, V, strideV, T, strideT, s)
-    if (rows_per_lane <= 6) QT_PANEL(6);
-    if (rows_per_lane <= 12) QT_PANEL(12);
-    if (rows_per_lane <= 20) QT_PANEL(20);
-    if (rows_per_lane <= 28) QT_PANEL(28);
-    QT_PANEL(38);
+#define QT_PANEL(R, S) return launch_panel_rpl<R, S>(A, strideA, n, count, j0, w, V, strideV, T, strideT, s)
+    if (rows_per_lane <= 6) QT_PANEL(6, 0);
+    if (rows_per_lane <= 12) QT_PANEL(12, 0);
+    if (rows_per_lane <= 20) QT_PANEL(20, 0);
+    if (rows_per_lane <= 28) QT_PANEL(24, 4);
+    QT_PANEL(24, 14);
 #undef QT_PANEL
 }
 
