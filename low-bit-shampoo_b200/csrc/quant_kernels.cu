@@ -63,7 +63,7 @@ __device__ __forceinline__ void load_vec(const T *p, float (&x)[EPL]) {
 // Quantize, vector path.  Requires n % EPL == 0 and vector-aligned buffers.
 // ------------------------------------------------------------------------------------
 template <typename T, int BITS, int EPL, int LPU>
-__global__ void __launch_bounds__(kThreads, (EPL == 16 ? 3 : 4))
+__global__ void __launch_bounds__(kThreads, 4)
 k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__restrict__ code,
                int n, int nb, int count, float *__restrict__ absmax_base, long long stride_absmax,
                float *__restrict__ diag_base, long long stride_diag,
@@ -130,25 +130,61 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
         const bool scale_ok = (amax >= 9.094947e-13f && amax <= 1.1529215e18f) || amax == 0.0f;
         const bool lean = lean_launch && __all_sync(0xffffffffu, scale_ok);
         if (lane_ok) {
-            int idx[EPL];
-            if (lean) {
-                const float d = (amax == 0.0f) ? 1.0f : amax;
-                const float rcp = __frcp_rn(d);
+            const long long e = (long long)r * n + c;         // flat element index, multiple of EPL
+            unsigned char *out = out_base + (long long)m * stride_out;
+            if constexpr (BITS == 4) {
+                // codes are collected most-significant-nibble first (wq = wq << 4 | code), eight per
+                // word, and the bytes of each word are reversed once at the end: element 2j ends up
+                // in the high nibble of byte j (functional.py:733-734)
+                constexpr int NW = EPL >= 8 ? EPL / 8 : 1;
+                unsigned wq[NW];
 #pragma unroll
-                for (int j = 0; j < EPL; ++j) {
-                    const float q = div_by_recip(x[j], d, rcp);
-                    if constexpr (NC == 16) idx[j] = lut_index(tab, lut16, lut_scale, q);
-                    else idx[j] = 0;                          // lean_launch is false for other codebook sizes
+                for (int i = 0; i < NW; ++i) wq[i] = 0;
+                bool generic = !lean;
+                if (lean) {
+                    const float d = (amax == 0.0f) ? 1.0f : amax;
+                    const float rcp = __frcp_rn(d);
+                    unsigned nearest = 0xffffffffu;
+#pragma unroll
+                    for (int j = 0; j < EPL; ++j) {
+                        const float q = div_by_recip(x[j], d, rcp);
+                        const unsigned cellw = lut16[lut_cell_raw(q, lut_scale) & (kLutAlloc - 1)];
+                        // the cell word read as a float is the threshold to within 16 ulp (its low bits
+                        // hold the base index): the compare is exact unless q lies in that 16-ulp bucket
+                        nearest = min(nearest, (__float_as_uint(q) ^ cellw) & ~15u);
+                        const unsigned t = cellw + (q >= __uint_as_float(cellw) ? 1u : 0u);
+                        wq[j / 8] = (wq[j / 8] << 4) | (t & 15u);
+                    }
+                    if (amax == 0.0f) {                       // functional.py:600-602
+#pragma unroll
+                        for (int i = 0; i < NW; ++i) wq[i] = 0;
+                    }
+                    generic = (nearest == 0u);                // rare: decide those against the exact thresholds
                 }
-                if (amax == 0.0f) {                           // functional.py:600-602
-                    if constexpr (BITS == 4 && EPL == 16) {
-                        // every quotient is +-0 here and lands on one index: clear the words below instead
-                    } else {
+                if (generic) {
+                    constexpr int PART = EPL > 8 ? 8 : EPL;
 #pragma unroll
-                        for (int j = 0; j < EPL; ++j) idx[j] = 0;
+                    for (int h = 0; h < EPL / PART; ++h) {
+                        LaneVals<PART> xv;
+#pragma unroll
+                        for (int j = 0; j < PART; ++j) xv.v[j] = x[h * PART + j];
+                        const unsigned long long pk = quantize_lane_generic<NC, PART>(tab, xv, amax);
+                        unsigned w = 0;
+#pragma unroll
+                        for (int j = 0; j < PART; ++j) w = (w << 4) | (unsigned)((pk >> (8 * j)) & 15u);
+                        wq[h] = w;
                     }
                 }
+                if constexpr (EPL == 16) {
+                    *reinterpret_cast<uint2 *>(out + (e >> 1)) = make_uint2(__byte_perm(wq[0], 0, 0x0123), __byte_perm(wq[1], 0, 0x0123));
+                } else if constexpr (EPL == 8) {
+                    *reinterpret_cast<unsigned *>(out + (e >> 1)) = __byte_perm(wq[0], 0, 0x0123);
+                } else {
+                    *reinterpret_cast<unsigned short *>(out + (e >> 1)) = (unsigned short)(((wq[0] >> 8) & 0xffu) | ((wq[0] & 0xffu) << 8));
+                }
             } else {
+                // 8-bit codes: always the out-of-line routine (binary search over 255 thresholds)
+                int idx[EPL];
                 constexpr int PART = EPL > 8 ? 8 : EPL;
 #pragma unroll
                 for (int h = 0; h < EPL / PART; ++h) {
@@ -159,26 +195,6 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
 #pragma unroll
                     for (int j = 0; j < PART; ++j) idx[h * PART + j] = (int)((pk >> (8 * j)) & 255u);
                 }
-            }
-            const long long e = (long long)r * n + c;         // flat element index, multiple of EPL
-            unsigned char *out = out_base + (long long)m * stride_out;
-            if constexpr (BITS == 4 && EPL == 16) {
-                unsigned w0 = 0, w1 = 0;
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    w0 |= (unsigned)((idx[j] << 4) | idx[j + 1]) << (4 * j);
-                    w1 |= (unsigned)((idx[8 + j] << 4) | idx[8 + j + 1]) << (4 * j);
-                }
-                if (lean && amax == 0.0f) { w0 = 0; w1 = 0; }
-                *reinterpret_cast<uint2 *>(out + (e >> 1)) = make_uint2(w0, w1);
-            } else if constexpr (BITS == 4) {
-                unsigned w = 0;
-#pragma unroll
-                for (int j = 0; j < EPL; j += 2)
-                    w |= (unsigned)((idx[j] << 4) | idx[j + 1]) << (4 * j);
-                if constexpr (EPL == 8) *reinterpret_cast<unsigned *>(out + (e >> 1)) = w;
-                else *reinterpret_cast<unsigned short *>(out + (e >> 1)) = (unsigned short)w;
-            } else {
                 unsigned w0 = 0, w1 = 0;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) w0 |= (unsigned)idx[j] << (8 * j);
@@ -575,7 +591,7 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
             launch_quantize_typed<T, BITS>(hi, s);
             return;
         }
-        const int resident = (epl == 16) ? 3 : 4;            // the kernels' launch bounds
+        const int resident = 4;                              // the kernels' launch bounds
         long long ctas = (long long)sm_count() * resident;
         const long long needed = (units * a.count * lpu + kThreads - 1) / kThreads;
         if (ctas > needed) ctas = needed;
