@@ -425,10 +425,15 @@ class _ShampooBase(optim.Optimizer):
                 lib = F.lib
                 before = lib.qt_launch_count() if lib is not None else 0
                 graph = torch.cuda.CUDAGraph()
+                split_before = E.SPLIT_CLASSES
                 try:
+                    # launches are free on replay: cut dominant order classes into more concurrent units
+                    E.SPLIT_CLASSES = True
                     with torch.cuda.graph(graph):
                         self._apply_update(group, params, scalars=gs["scalars"])
+                    E.SPLIT_CLASSES = split_before
                 except Exception:
+                    E.SPLIT_CLASSES = split_before
                     for p, (st, act) in zip(params, book):      # capture failed: undo bookkeeping, go eager
                         self.state[p]['step'] = st
                         self.state[p]['preconditioner']._active = act

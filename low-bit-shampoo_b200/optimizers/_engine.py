@@ -350,6 +350,7 @@ def _ema_update(L, grads_axes, w1, w2):
 
 PARALLEL_CLASSES = True        # order classes are independent: run them on separate CUDA streams
 _STREAMS = {}
+_NUM_STREAMS = 8
 
 
 def _over_classes(by_class, payload=None):
@@ -366,7 +367,7 @@ def _over_classes(by_class, payload=None):
         return
     pool = _STREAMS.get(str(dev))
     if pool is None:
-        pool = _STREAMS[str(dev)] = [torch.cuda.Stream(device=dev) for _ in range(6)]
+        pool = _STREAMS[str(dev)] = [torch.cuda.Stream(device=dev) for _ in range(_NUM_STREAMS)]
     main = torch.cuda.current_stream(dev)
     used = pool[: min(len(pool), len(classes))]
     for s in used:
@@ -376,6 +377,62 @@ def _over_classes(by_class, payload=None):
             yield cls, item
     for s in used:
         main.wait_stream(s)
+
+
+SPLIT_CLASSES = False          # cut a class that dominates the step into slot ranges on separate streams
+                               # (more, smaller launches: switched on while a CUDA graph is captured)
+_UNIT_TARGET = 6               # aim for about this many equally expensive units per refresh
+
+
+def _split_units(merged):
+    """{cls: (stat entries, root slots)} -> list of (cost, cls, (entries, slots)) work units.
+
+    The step's critical path is the largest class: its chain of latency-bound launches (a QR of
+    62 order-1200 matrices is ~40 panel launches that each occupy 62 SMs) runs on one stream while
+    the small classes finish early.  Cutting such a class into contiguous slot ranges lets those
+    chains run side by side; a slot's statistics and inverse root stay in the same unit."""
+    cost = {cls: float(cls.n) ** 3 * len(set([e[0] for e in v[0]] + list(v[1]))) for cls, v in merged.items()}
+    total = sum(cost.values())
+    units = []
+    for cls, (entries, slots) in merged.items():
+        parts = 1
+        if SPLIT_CLASSES and total > 0 and torch.device(cls.device).type == "cuda":
+            parts = max(1, min(4, int(round(cost[cls] / (total / _UNIT_TARGET)))))
+        ids = sorted(set([e[0] for e in entries] + list(slots)))
+        parts = min(parts, max(1, len(ids) // 8))          # keep at least 8 matrices per unit
+        if parts == 1:
+            units.append((cost[cls], cls, (entries, slots)))
+            continue
+        step = (len(ids) + parts - 1) // parts
+        for k in range(parts):
+            chunk = set(ids[k * step: (k + 1) * step])
+            if chunk:
+                units.append((cost[cls] * len(chunk) / len(ids), cls,
+                              ([e for e in entries if e[0] in chunk], [x for x in slots if x in chunk])))
+    return units
+
+
+def _over_units(units):
+    """Yields (cls, item) for every (cost, cls, item) unit, most expensive first, each on one of a
+    few side streams on CUDA; joined back before returning."""
+    units = sorted(units, key=lambda u: -u[0])
+    dev = units[0][1].device if units else None
+    if not PARALLEL_CLASSES or len(units) < 2 or dev is None or torch.device(dev).type != "cuda":
+        for _, cls, item in units:
+            yield cls, item
+        return
+    pool = _STREAMS.get(str(dev))
+    if pool is None:
+        pool = _STREAMS[str(dev)] = [torch.cuda.Stream(device=dev) for _ in range(_NUM_STREAMS)]
+    main = torch.cuda.current_stream(dev)
+    used = pool[: min(len(pool), len(units))]
+    for st in used:
+        st.wait_stream(main)
+    for i, (_, cls, item) in enumerate(units):
+        with torch.cuda.stream(used[i % len(used)]):
+            yield cls, item
+    for st in used:
+        main.wait_stream(st)
 
 
 def add_statistics(items, w1, w2, eps=1e-6, exact=False):
@@ -438,8 +495,7 @@ def refresh(stat_items, root_items, w1, w2, eps, inv_root_mode, exact=False, exp
     for cls, slot in root_items:
         roots[cls].append(slot)
     merged = {cls: (stats.get(cls, []), roots.get(cls, [])) for cls in list(stats) + [c for c in roots if c not in stats]}
-    weight = {cls: (len(v[0]) + len(v[1])) for cls, v in merged.items()}
-    for cls, (entries, slots) in _over_classes({cls: [None] * weight[cls] for cls in merged}, payload=merged):
+    for cls, (entries, slots) in _over_units(_split_units(merged)):
         if entries:
             _class_statistics(cls, entries, w1, w2, eps, exact)
         if slots:
