@@ -102,7 +102,14 @@ __device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) 
                 int c;
                 if (th > 1.0f) c = last + 1;                  // never reached
                 else if (!(th >= -1.0f)) c = -1;              // below every quotient
-                else c = lut_cell_raw(th, scale) - 0x4B000000;
+                else {
+                    c = lut_cell_raw(th, scale) - 0x4B000000;
+                    // the quantizer looks cells up with a quotient that may be 3 ulp off: a threshold
+                    // closer than 8 ulp to a cell border would make the neighbouring cell wrong
+                    const long long k = float_key(th);
+                    if (lut_cell_raw(key_float(k - 8), scale) - 0x4B000000 != c ||
+                        lut_cell_raw(key_float(k + 8), scale) - 0x4B000000 != c) t.lut_bad = 1;
+                }
                 t.thr_cell[tid] = c;
             }
             __syncthreads();

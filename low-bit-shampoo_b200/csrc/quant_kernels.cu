@@ -72,41 +72,43 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
     constexpr int BS = EPL * LPU;
     __shared__ CodeTables<NC> tab;
 
-    // Units (one block of one row) are numbered across the whole batch, matrix-major, and the
-    // grid is one resident wave striding over them: the tables are built once per resident CTA
-    // and no second wave of CTAs trails behind.  (m, r, b) = matrix, row, block of a unit.
-    const int units = n * nb;                               // per matrix
-    const int total = units * count;                        // launcher keeps this below 2^31
-    const int groups_per_cta = kThreads / LPU;
-    const int G = gridDim.x * groups_per_cta;               // groups striding over the batch
-    const int lane_u = threadIdx.x % LPU;
-    int u = blockIdx.x * groups_per_cta + threadIdx.x / LPU;
-    // first unit of this thread's warp: uniform loop bound so shuffles see full warps
-    int u_warp = blockIdx.x * groups_per_cta + (threadIdx.x / 32) * (32 / LPU);
-    int m = u / units;
-    int r = (u - m * units) / nb, b = u - m * units - r * nb;
-    const int dm = G / units, dr = (G - dm * units) / nb, db = G - dm * units - dr * nb;
+    // A warp works on one block column of GW consecutive rows (a "warp unit": GW quantization
+    // blocks, LPU lanes each), so the diagonal crosses only one warp unit in nb and the diagonal
+    // side channel costs nothing elsewhere.  Warp units are numbered across the whole batch
+    // (matrix, row band, block) and the grid is one resident wave striding over them: the tables
+    // are built once per resident CTA and no second wave of CTAs trails behind.
+    constexpr int GW = 32 / LPU;
+    const int bands = (n + GW - 1) / GW;
+    const int wunits = bands * nb;                          // per matrix
+    const int total = wunits * count;                       // launcher keeps this below 2^31
+    const int SW = gridDim.x * (kThreads / 32);             // warps striding over the batch
+    const int lane_u = threadIdx.x % LPU, row_in_band = (threadIdx.x & 31) / LPU;
+    int gw = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    int m = gw / wunits;
+    int band = (gw - m * wunits) / nb, b = gw - m * wunits - band * nb;
+    const int dm = SW / wunits, dband = (SW - dm * wunits) / nb, db = SW - dm * wunits - dband * nb;
 
     // issue the first loads before the table build so its latency is hidden
     float x[EPL];
     bool have = false;
     {
-        const int c = b * BS + lane_u * EPL;
-        if (u < total && c < n) { load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x); have = true; }
+        const int r = band * GW + row_in_band, c = b * BS + lane_u * EPL;
+        if (gw < total && r < n && c < n) { load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x); have = true; }
     }
     build_tables<NC>(tab, code);
     const bool lean_launch = (NC == 16) && !tab.lut_bad && !tab.need_clamp && tab.perm_identity && !tab.tiny_thr;
     const unsigned *lut16 = tab.lut;
     const float lut_scale = tab.lut_scale;
 
-    for (; u_warp < total; u_warp += G) {
-        const int c = b * BS + lane_u * EPL;
-        const bool unit_ok = u < total;
+    for (; gw < total; gw += SW) {
+        const int r = band * GW + row_in_band, c = b * BS + lane_u * EPL;
+        const bool unit_ok = r < n;
         const bool lane_ok = unit_ok && c < n;
-        if (!have) {
+        if (lane_ok) {
+            if (!have) load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x);
+        } else {
 #pragma unroll
             for (int j = 0; j < EPL; ++j) x[j] = 0.0f;
-            if (lane_ok) load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x);
         }
         have = false;
         if (diag_base && lane_ok && (unsigned)(r - c) < (unsigned)EPL) {   // functional.py:574-578
@@ -147,11 +149,15 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
                     unsigned nearest = 0xffffffffu;
 #pragma unroll
                     for (int j = 0; j < EPL; ++j) {
-                        const float q = div_by_recip(x[j], d, rcp);
+                        // q0 = x * RN(1/d) is within 3 ulp of the IEEE quotient the reference forms
+                        // (functional.py:604).  The cell word read as a float is the decision threshold to
+                        // within 16 ulp (its low four bits hold the base index).  Unless q0 falls within
+                        // 8 ulp of that 16-ulp bucket, q0 and the exact quotient lie on the same side of
+                        // the threshold (and build_tables keeps thresholds 8 ulp away from cell
+                        // borders, so a neighbouring cell gives the same answer): the code is exact.
+                        const float q = x[j] * rcp;
                         const unsigned cellw = lut16[lut_cell_raw(q, lut_scale) & (kLutAlloc - 1)];
-                        // the cell word read as a float is the threshold to within 16 ulp (its low bits
-                        // hold the base index): the compare is exact unless q lies in that 16-ulp bucket
-                        nearest = min(nearest, (__float_as_uint(q) ^ cellw) & ~15u);
+                        nearest = min(nearest, __float_as_uint(q) - (cellw & ~15u) + 8u);
                         const unsigned t = cellw + (q >= __uint_as_float(cellw) ? 1u : 0u);
                         wq[j / 8] = (wq[j / 8] << 4) | (t & 15u);
                     }
@@ -159,7 +165,7 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
 #pragma unroll
                         for (int i = 0; i < NW; ++i) wq[i] = 0;
                     }
-                    generic = (nearest == 0u);                // rare: decide those against the exact thresholds
+                    generic = (nearest < 32u);                // rare: redo this lane with the exact division
                 }
                 if (generic) {
                     constexpr int PART = EPL > 8 ? 8 : EPL;
@@ -207,9 +213,9 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
                 }
             }
         }
-        u += G; b += db; r += dr; m += dm;
-        if (b >= nb) { b -= nb; r += 1; }
-        if (r >= n) { r -= n; m += 1; }
+        b += db; band += dband; m += dm;
+        if (b >= nb) { b -= nb; band += 1; }
+        if (band >= bands) { band -= bands; m += 1; }
     }
 }
 
@@ -578,7 +584,8 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
         const long long units = (long long)n * nb;
         // every CTA builds the code tables once: exactly one resident wave (or fewer CTAs when the
         // batch is small), striding over the units of the whole batch
-        if (units * a.count >= (1ll << 31) - (1ll << 24) && a.count > 1) {   // unit numbers are 32-bit in the kernel
+        const long long wunits = (long long)((n + 32 / lpu - 1) / (32 / lpu)) * nb;   // warp units per matrix
+        if (wunits * a.count >= (1ll << 31) - (1ll << 24) && a.count > 1) {   // warp-unit numbers are 32-bit in the kernel
             const int half = a.count / 2;
             QuantArgs lo = a, hi = a;
             lo.count = half;
@@ -593,7 +600,7 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
         }
         const int resident = 4;                              // the kernels' launch bounds
         long long ctas = (long long)sm_count() * resident;
-        const long long needed = (units * a.count * lpu + kThreads - 1) / kThreads;
+        const long long needed = (wunits * a.count + kThreads / 32 - 1) / (kThreads / 32);
         if (ctas > needed) ctas = needed;
         if (ctas < 1) ctas = 1;
         dim3 grid((unsigned)ctas);
