@@ -581,7 +581,6 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
         epl = 16;
     if (epl) {
         const int lpu = a.bs / epl;
-        const long long units = (long long)n * nb;
         // every CTA builds the code tables once: exactly one resident wave (or fewer CTAs when the
         // batch is small), striding over the units of the whole batch
         const long long wunits = (long long)((n + 32 / lpu - 1) / (32 / lpu)) * nb;   // warp units per matrix
