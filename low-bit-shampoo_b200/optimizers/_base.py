@@ -7,6 +7,7 @@ reference's optimizers/shampoo2.py (BlockPartitioner :35-99, Preconditioner :102
 ShampooSGD :278-367, ShampooAdamW :370-468) and optimizers/shampoo1.py.
 """
 import itertools
+import warnings
 import math
 from collections import defaultdict
 
@@ -361,6 +362,16 @@ class _ShampooBase(optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
+        # launches are free on graph replay: cut dominant order classes into more concurrent units
+        # (from the first, eager step on, so that every cached index list exists before capture)
+        split_before = E.SPLIT_CLASSES
+        E.SPLIT_CLASSES = split_before or self._use_graph
+        try:
+            self._step_groups()
+        finally:
+            E.SPLIT_CLASSES = split_before
+
+    def _step_groups(self):
         for group in self.param_groups:
             params = [p for p in group['params'] if p.grad is not None]
             for p in params:
@@ -425,15 +436,11 @@ class _ShampooBase(optim.Optimizer):
                 lib = F.lib
                 before = lib.qt_launch_count() if lib is not None else 0
                 graph = torch.cuda.CUDAGraph()
-                split_before = E.SPLIT_CLASSES
                 try:
-                    # launches are free on replay: cut dominant order classes into more concurrent units
-                    E.SPLIT_CLASSES = True
                     with torch.cuda.graph(graph):
                         self._apply_update(group, params, scalars=gs["scalars"])
-                    E.SPLIT_CLASSES = split_before
-                except Exception:
-                    E.SPLIT_CLASSES = split_before
+                except Exception as exc:
+                    warnings.warn(f"CUDA-graph capture of the optimizer step failed ({exc!r}); running eagerly")
                     for p, (st, act) in zip(params, book):      # capture failed: undo bookkeeping, go eager
                         self.state[p]['step'] = st
                         self.state[p]['preconditioner']._active = act

@@ -79,4 +79,4 @@ def synthetic_gradients(model, batch, img, classes, device, autocast_bf16=True, 
     with torch.autocast(device_type=torch.device(device).type, dtype=torch.bfloat16, enabled=autocast_bf16):
         loss = F.cross_entropy(model(x).float(), y)
     loss.backward()
-    return float(loss)
+    return float(loss.detach())
