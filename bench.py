@@ -422,12 +422,17 @@ def run_ours(args):
             "achieved": gres["tflops_algorithmic"], "peak": tf_peak, "unit": "TFLOP/s",
             "frac": gres["tflops_algorithmic"] / tf_peak, "peak_kind": f"of {peak_kind} (sustained bf16)",
             "executed": gres["tflops_executed"], "frac_executed": gres["tflops_executed"] / tf_peak,
-            "emulation_factor": 3, "traffic": None, "flops_per_launch": gres["flops_per_launch"], "case": gres["case"],
+            "emulation_factor": 3, "traffic": 542.5e6,
+            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case under ncu "
+                              "(profiles/gemm_bf16x3_768x125.md); algorithmic operand + result bytes: 590e6",
+            "flops_per_launch": gres["flops_per_launch"], "case": gres["case"],
             "us_per_launch": gres["us_per_launch"],
             "quantize": {"bound": "hbm", "achieved": qres["quantize"]["gbs"], "peak": hbm_peak, "unit": "GB/s",
-                         "frac": qres["quantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc},
+                         "frac": qres["quantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc,
+                         "traffic": 331.0e6},
             "dequantize": {"bound": "hbm", "achieved": qres["dequantize"]["gbs"], "peak": hbm_peak, "unit": "GB/s",
-                           "frac": qres["dequantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc}}
+                           "frac": qres["dequantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc,
+                           "traffic": 279.2e6}}
     line = {"metric": METRIC, "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 arithmetic on 4-bit state", "data": "synthetic",
@@ -461,7 +466,7 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="kernel sweep of the fused 4-bit statistics update and the inverse 4th root over orders 128..8192")
     ap.add_argument("--sweep-orders", default="128,512,1200,2048,4096,8192")
-    ap.add_argument("--profile-case", default=None, choices=["quant", "gemm"],
+    ap.add_argument("--profile-case", default=None, choices=["quant", "gemm", "step"],
                     help="run only one small kernel case (for an ncu capture) and print its rates")
     args = ap.parse_args()
     if args.sweep:
@@ -475,6 +480,29 @@ def main():
         from qtensor.cextension import get_lib
         res, nbytes, desc = quantizer_roofline(torch, get_lib(), torch.device("cuda", 0), iters=3)
         print(json.dumps({"case": desc, "bytes_per_launch": nbytes, **res}))
+        return
+    if args.profile_case == "step":
+        # one eager optimizer step between cudaProfilerStart/Stop, for a launch list:
+        #   ncu --profile-from-start off --metrics gpu__time_duration.sum --clock-control none --csv ...
+        import torch
+        import workloads
+        from optimizers.shampoo2 import ShampooAdamW
+        device = torch.device("cuda", 0)
+        torch.manual_seed(0)
+        model = workloads.vit_base_patch32_224().to(device)
+        opt = ShampooAdamW(list(model.parameters()), **HYPER)
+        workloads.synthetic_gradients(model, 256, 224, 1000, device, autocast_bf16=True, seed=0)
+        for _ in range(3):
+            opt.step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.profiler.start()
+        e0.record()
+        opt.step()
+        e1.record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"case": "one eager ShampooAdamW.step(), ViT-B/32, T1=T2=1", "ms": e0.elapsed_time(e1)}))
         return
     if args.profile_case == "gemm":
         import torch
