@@ -141,6 +141,20 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// 256-bit global accesses (sm_100); addresses must be 32-byte aligned.
+__device__ __forceinline__ void ldg256f(const float *p, float *v) {
+    asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(p));
+}
+__device__ __forceinline__ void stg256f(float *p, const float *v) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
+__device__ __forceinline__ void stg256u(void *p, const unsigned *v) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
 __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
     unsigned long long d = 0;
     d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
@@ -402,6 +416,11 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                             ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 15) == 0 &&
                             ((p.ldp | p.strideP) & 7) == 0 &&
                             ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dlo)) & 15) == 0;
+        // 256-bit accesses: every 32-column chunk of a row starts on a 32-byte boundary
+        const bool wide_ok = vec_ok && ((p.ldc | p.ldd | p.strideC | p.strideD) & 7) == 0 &&
+                             ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 31) == 0 &&
+                             ((p.ldp | p.strideP) & 15) == 0 &&
+                             ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dlo)) & 31) == 0;
         if constexpr (KC > 0) {
             // chunked accumulation: partial sums of KC k-blocks are added in registers
             int j = 0;
@@ -441,6 +460,16 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                     const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
                     float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + n0;
                     const int valid = min(BN, p.N - n0);
+                    if (wide_ok && valid == BN) {
+#pragma unroll
+                        for (int q = 0; q < BN; q += 8) {
+                            float cv8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, o[8];
+                            if (has_c) ldg256f(crow + q, cv8);
+#pragma unroll
+                            for (int t = 0; t < 8; ++t) o[t] = fmaf(p.beta, cv8[t], p.alpha * sum[q + t]);
+                            stg256f(drow + q, o);
+                        }
+                    } else
 #pragma unroll
                     for (int q = 0; q < BN; q += 4) {
                         if (vec_ok && q + 4 <= valid) {
@@ -498,7 +527,10 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             auto fetch_c = [&](int c, float (&dst)[32]) {
                 const int valid = p.N - (n0 + c * 32);
                 if (has_c && row_ok && valid > 0) {
-                    if (vec_ok && valid >= 32) {
+                    if (wide_ok && valid >= 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) ldg256f(crow + c * 32 + j, &dst[j]);
+                    } else if (vec_ok && valid >= 32) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
                             const float4 t = __ldg(reinterpret_cast<const float4 *>(crow + c * 32 + j));
@@ -527,7 +559,28 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 if (c + 1 < BN / 32) fetch_c(c + 1, cv);
                 const int valid = p.N - (n0 + c * 32);
                 if (row_ok && valid > 0) {
-                    if (vec_ok && valid >= 32) {
+                    if (wide_ok && valid >= 32) {
+                        if (p.D) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) stg256f(drow + c * 32 + j, &v[j]);
+                        }
+                        if (p.Dhi) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 16) {
+                                unsigned h[8], l[8];
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) {
+                                    const __nv_bfloat16 h0 = __float2bfloat16_rn(v[j + 2 * q]), h1 = __float2bfloat16_rn(v[j + 2 * q + 1]);
+                                    const __nv_bfloat16 l0 = __float2bfloat16_rn(v[j + 2 * q] - __bfloat162float(h0));
+                                    const __nv_bfloat16 l1 = __float2bfloat16_rn(v[j + 2 * q + 1] - __bfloat162float(h1));
+                                    h[q] = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
+                                    l[q] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
+                                }
+                                stg256u(hrow + c * 32 + j, h);
+                                stg256u(lrow + c * 32 + j, l);
+                            }
+                        }
+                    } else if (vec_ok && valid >= 32) {
                         if (p.D) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)

@@ -9,6 +9,7 @@
 namespace qt {
 
 static constexpr int kLutAlloc = 2048;        // cells allocated; the finest grid uses 2*512+1 of them
+static constexpr float kLutCoarseScale = 127.0f;   // coarse grid: cells 0..254, so an 8-bit mask is a safe index
 
 // ------------------------------------------------------------------------------------
 // Codebook tables, built per CTA in shared memory.
@@ -25,7 +26,7 @@ struct CodeTables {
     int lut_bad;
     int tiny_thr;             // some decision threshold has |t| < 2^-50: quotients must be exact even when tiny
     int thr_cell[NC];         // lookup-table cell of each threshold
-    float lut_scale;          // cells per unit of q: 128 when that separates the thresholds, else 512
+    float lut_scale;          // cells per unit of q: 127 (255 cells) when that separates the thresholds, else 512
     // One 32-bit word per cell of q in [-1, 1]: bits 31..4 = the threshold inside the cell (or +inf)
     // with its low four mantissa bits cleared, bits 3..0 = number of thresholds in lower cells.
     // A 4-byte cell halves the shared-memory wavefronts of a warp's 32 scattered lookups compared
@@ -94,7 +95,7 @@ __device__ void build_tables(CodeTables<NC> &t, const float *__restrict__ code) 
     __syncthreads();
     if (NC == 16) {
         for (int attempt = 0; attempt < 2; ++attempt) {
-            const float scale = attempt ? 512.0f : 128.0f;
+            const float scale = attempt ? 512.0f : kLutCoarseScale;
             const int last = 2 * (int)scale;                 // highest cell a quotient can reach
             if (tid == 0) { t.lut_bad = 0; t.lut_scale = scale; }
             if (tid < NC - 1) {

@@ -30,6 +30,38 @@ template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// 256-bit global accesses (sm_100): one request per lane for 32 bytes, half the L1 wavefronts of
+// two 128-bit ones.  The address must be 32-byte aligned.
+__device__ __forceinline__ void ldg256(const void *p, unsigned (&w)[8]) {
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(p));
+}
+__device__ __forceinline__ void stg256(void *p, const float (&v)[8]) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
+// 16 consecutive elements (64 bytes of fp32, 32 bytes of bf16) with 256-bit loads.
+template <typename T>
+__device__ __forceinline__ void load16_wide(const T *p, float (&x)[16]) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            unsigned w[8];
+            ldg256(p + 8 * h, w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[8 * h + j] = __uint_as_float(w[j]);
+        }
+    } else {
+        unsigned w[8];
+        ldg256(p, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            x[2 * j] = __uint_as_float(w[j] << 16);
+            x[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    }
+}
+
 // Load EPL consecutive elements (EPL*sizeof(T) is 8, 16 or 32 bytes, pointer aligned to it or 16).
 template <typename T, int EPL>
 __device__ __forceinline__ void load_vec(const T *p, float (&x)[EPL]) {
@@ -67,9 +99,16 @@ __global__ void __launch_bounds__(kThreads, 4)
 k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__restrict__ code,
                int n, int nb, int count, float *__restrict__ absmax_base, long long stride_absmax,
                float *__restrict__ diag_base, long long stride_diag,
-               unsigned char *__restrict__ out_base, long long stride_out) {
+               unsigned char *__restrict__ out_base, long long stride_out, int wide) {
     constexpr int NC = 1 << BITS;
     constexpr int BS = EPL * LPU;
+    // `wide` (EPL == 16 only): every lane's 16 elements start on a 32-byte boundary
+    auto load_lane = [&](const T *p, float (&dst)[EPL]) {
+        if constexpr (EPL == 16) {
+            if (wide) { load16_wide<T>(p, dst); return; }
+        }
+        load_vec<T, EPL>(p, dst);
+    };
     __shared__ CodeTables<NC> tab;
 
     // A warp works on one block column of GW consecutive rows (a "warp unit": GW quantization
@@ -93,7 +132,7 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
     bool have = false;
     {
         const int r = band * GW + row_in_band, c = b * BS + lane_u * EPL;
-        if (gw < total && r < n && c < n) { load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x); have = true; }
+        if (gw < total && r < n && c < n) { load_lane(Abase + (long long)m * strideA + (long long)r * n + c, x); have = true; }
     }
     build_tables<NC>(tab, code);
     const bool lean_launch = (NC == 16) && !tab.lut_bad && !tab.need_clamp && tab.perm_identity && !tab.tiny_thr;
@@ -105,7 +144,7 @@ k_quantize_vec(const T *__restrict__ Abase, long long strideA, const float *__re
         const bool unit_ok = r < n;
         const bool lane_ok = unit_ok && c < n;
         if (lane_ok) {
-            if (!have) load_vec<T, EPL>(Abase + (long long)m * strideA + (long long)r * n + c, x);
+            if (!have) load_lane(Abase + (long long)m * strideA + (long long)r * n + c, x);
         } else {
 #pragma unroll
             for (int j = 0; j < EPL; ++j) x[j] = 0.0f;
@@ -296,8 +335,7 @@ template <> __device__ __forceinline__ void store_vec<float, 4>(float *p, const 
     *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
 }
 template <> __device__ __forceinline__ void store_vec<float, 8>(float *p, const float (&v)[8]) {
-    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    stg256(p, v);                                             // launcher guarantees 32-byte alignment
 }
 __device__ __forceinline__ unsigned pack_bf16x2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);           // .x = a (low half), .y = b
@@ -598,6 +636,9 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
             return;
         }
         const int resident = 4;                              // the kernels' launch bounds
+        // 256-bit loads need every lane's 16 elements on a 32-byte boundary
+        const int wide = (epl == 16 && aligned(A, 32) && ((long long)n * (long long)esz) % 32 == 0 &&
+                          (!many || (a.strideA * (long long)esz) % 32 == 0)) ? 1 : 0;
         long long ctas = (long long)sm_count() * resident;
         const long long needed = (wunits * a.count + kThreads / 32 - 1) / (kThreads / 32);
         if (ctas > needed) ctas = needed;
@@ -605,7 +646,7 @@ static void launch_quantize_typed(const QuantArgs &a, cudaStream_t s) {
         dim3 grid((unsigned)ctas);
 #define QT_LAUNCH_Q(E, L)                                                                          \
         k_quantize_vec<T, BITS, E, L><<<grid, kThreads, 0, s>>>(A, a.strideA, a.code, n, nb, a.count, a.absmax, \
-            a.stride_absmax, a.diag, a.stride_diag, a.out, a.stride_out)
+            a.stride_absmax, a.diag, a.stride_diag, a.out, a.stride_out, wide)
         if constexpr (BITS == 4) { if (epl == 16) { QT_LAUNCH_Q(16, 4); count_launch(1); return; } }
         if (epl == 8 && lpu == 8) QT_LAUNCH_Q(8, 8);
         else if (epl == 8 && lpu == 16) QT_LAUNCH_Q(8, 16);
@@ -652,17 +693,16 @@ static void launch_dequantize_typed(const DequantArgs &a, cudaStream_t s) {
     while ((1 << bs_shift) < a.bs) ++bs_shift;
     const bool many = a.count > 1;
     auto ok = [&](int epl) {
-        const size_t in_bytes = (size_t)epl * BITS / 8, out_bytes = (size_t)(epl * esz > 16 ? 16 : epl * esz);
+        // fp32 x 8 is one 256-bit store (32-byte aligned); everything else is at most 128 bits
+        const size_t in_bytes = (size_t)epl * BITS / 8, out_bytes = (size_t)(epl * esz > 16 ? (esz == 4 ? 32 : 16) : epl * esz);
         if (n % epl) return false;
         if (!aligned(a.A, in_bytes) || !aligned(out, out_bytes)) return false;
         if (many && (a.strideA % (long long)in_bytes || (a.stride_out * (long long)esz) % (long long)out_bytes)) return false;
         return true;
     };
-    // fp32 output: 4 elements per thread keeps every 128-bit store fully coalesced;
-    // bf16 output: 8 elements per thread make one 128-bit store.
-    int epl = 0;
-    if (esz == 2) epl = ok(8) ? 8 : (ok(4) ? 4 : 0);
-    else epl = ok(4) ? 4 : 0;
+    // 8 elements per thread make one store: 256 bits of fp32 or 128 bits of bf16; otherwise 4
+    // elements (one 128-bit fp32 store).
+    int epl = ok(8) ? 8 : (ok(4) ? 4 : 0);
     if (epl) {
         const long long chunks = (long long)n * (n / epl);
         dim3 grid(grid_x_for(chunks, a.count, 4), a.count);

@@ -25,29 +25,37 @@ OUTER = 128                 # columns per outer block (four panels): trailing up
 USE_TENSOR_CORES = True     # rank-128 far updates on the tcgen05 kernel (panel-local rank-32 ones stay fp32)
 
 
-def _reflect(Vk, Tk, target, target_planes, transpose_t):
+def _reflect(Vk, Tk, target, target_planes, transpose_t, Pv=None):
     """target <- (I - Vk T Vk^T) target (or with T^T), fp32 in place; when `target_planes` (the
     bf16 planes of `target`) is given the two large products run on the tensor cores and the
-    planes are kept in step with the fp32 values."""
+    planes are kept in step with the fp32 values.  `Pv`: planes of Vk if the caller has them."""
     from optimizers import _gemm
     if target_planes is None:
         W = torch.bmm(Vk.transpose(1, 2), target)
         W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
         target.baddbmm_(Vk, W, alpha=-1.0)
         return
-    Pv = _gemm.split(Vk)
+    if Pv is None:
+        Pv = _gemm.split(Vk)
     W, _ = _gemm.matmul(Pv, target_planes, trans_a=True)                   # Vk^T target, (w x t)
     W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
     _gemm.matmul(Pv, _gemm.split(W), alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
 
 
-def _merge_t(Vo, Tp, widths):
+def _merge_t(Vo, Tp, widths, Pv=None):
     """Triangular factor of a block of panels: H_1 .. H_p = I - Vo T Vo^T from the panels' own
-    factors Tp[k] (LAPACK larft recurrence on blocks): T[:c, c:c+w] = -T[:c, :c] (Vo[:, :c]^T Vo[:, c:c+w]) Tk."""
+    factors Tp[k] (LAPACK larft recurrence on blocks): T[:c, c:c+w] = -T[:c, :c] (Vo[:, :c]^T Vo[:, c:c+w]) Tk.
+    With `Pv` (planes of Vo) the Gram matrix Vo^T Vo is a tensor-core product."""
     B = Vo.shape[0]
     wo = sum(widths)
     T = torch.zeros(B, wo, wo, dtype=torch.float32, device=Vo.device)
-    G = torch.bmm(Vo.transpose(1, 2), Vo) if len(widths) > 1 else None
+    G = None
+    if len(widths) > 1:
+        if Pv is not None:
+            from optimizers import _gemm
+            G, _ = _gemm.matmul(Pv, Pv, trans_a=True)
+        else:
+            G = torch.bmm(Vo.transpose(1, 2), Vo)
     c = 0
     for k, w in enumerate(widths):
         Tk = Tp[:, k, :w, :w]
@@ -89,14 +97,15 @@ def householder_q(X, tensor_cores=True):
                 if j0 + w < J0 + wo:                      # rest of this outer block: rank-32 update in fp32
                     _reflect(V[:, j0:, j0:j0 + w], T[:, k, :w, :w], X[:, j0:, j0 + w:J0 + wo], None, True)
             Vo = V[:, J0:, J0:J0 + wo]
-            Tb = _merge_t(Vo, T[:, J0 // PANEL:], widths)
-            blocks.append((J0, wo, Tb))
+            Pv = _gemm.split(Vo) if tc else None          # shared by the merge, the far update and the accumulation of Q
+            Tb = _merge_t(Vo, T[:, J0 // PANEL:], widths, Pv)
+            blocks.append((J0, wo, Tb, Pv))
             if J0 + wo < n:
                 m, t = n - J0, n - J0 - wo
-                _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True)
+                _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True, Pv)
         Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
         Qp = _gemm.split(Q) if tc else None
-        for J0, wo, Tb in reversed(blocks):
+        for J0, wo, Tb, Pv in reversed(blocks):
             m = n - J0
-            _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False)
+            _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False, Pv)
     return Q
