@@ -166,6 +166,17 @@ int qt_split_bf16(const float *X, long long ldx, long long strideX, int rows, in
                   void *hi, void *lo, long long ldp, long long strideP, void *stream);
 
 /*
+ * qt_split_bf16 with a row gather and / or a row scale: plane row i of matrix b holds
+ * scale[b*stride_scale + i] * X[b][ index[b*stride_index + i] ][:] (index: int64 row numbers;
+ * either pointer may be NULL).  Folds the selection of the kept eigenvector rows
+ * (qtensor/utils.py:202, qtensor/functional.py:752) and the diag(.) factor of V^T diag(.) V
+ * (qtensor/utils.py:203, qtensor/functional.py:762) into the operand preparation of the product.
+ */
+int qt_split_bf16_rows(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                       const long long *index, long long stride_index, const float *scale, long long stride_scale,
+                       void *hi, void *lo, long long ldp, long long strideP, void *stream);
+
+/*
  * Batched D = alpha * A * B^T-or-B + beta * C on the tcgen05 tensor cores with fp32
  * accumulation, operands as bf16 hi/lo planes (three MMAs per k-slice: hi*hi + hi*lo +
  * lo*hi, about 1e-5 relative accuracy).  Replaces the torch.matmul / @ products of the

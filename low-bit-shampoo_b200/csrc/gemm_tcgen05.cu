@@ -661,6 +661,69 @@ k_split_bf16_vec(const float *__restrict__ X, long long ldx, long long strideX, 
     }
 }
 
+// 16 elements per thread with 256-bit accesses (two loads, one store per plane); needs 32-byte
+// aligned rows in the source and in both planes.
+__global__ void __launch_bounds__(256)
+k_split_bf16_wide(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols16,
+                  __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, long long ldp, long long strideP) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    __nv_bfloat16 *h = hi + (long long)b * strideP, *l = lo + (long long)b * strideP;
+    const long long total = (long long)rows * cols16;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / cols16), c = (int)(e - (long long)r * cols16) * 16;
+        float v[16];
+        ldg256f(x + (long long)r * ldx + c, v);
+        ldg256f(x + (long long)r * ldx + c + 8, v + 8);
+        unsigned H[8], L[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) split2(v[2 * j], v[2 * j + 1], H[j], L[j]);
+        stg256u(h + (long long)r * ldp + c, H);
+        stg256u(l + (long long)r * ldp + c, L);
+    }
+}
+
+// Split with a row gather and / or a row scale: output row i of matrix b is
+// scale[b][i] * X[b][index[b][i]][:] (either may be absent).  This folds the row selection of the kept
+// eigenvectors and the diag(w) factor of rows^T diag(w) rows into the operand preparation.
+// WIDE: 16 elements per thread with 256-bit accesses; otherwise one element per thread.
+template <bool WIDE>
+__global__ void __launch_bounds__(256)
+k_split_bf16_rows(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
+                  const long long *__restrict__ index, long long stride_index,
+                  const float *__restrict__ scale, long long stride_scale,
+                  __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, long long ldp, long long strideP) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    __nv_bfloat16 *h = hi + (long long)b * strideP, *l = lo + (long long)b * strideP;
+    const long long *idx = index ? index + (long long)b * stride_index : nullptr;
+    const float *sc = scale ? scale + (long long)b * stride_scale : nullptr;
+    constexpr int E = WIDE ? 16 : 1;
+    const int per_row = cols / E;
+    const long long total = (long long)rows * per_row;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / per_row), c = (int)(e - (long long)r * per_row) * E;
+        const long long src = idx ? idx[r] : (long long)r;
+        const float f = sc ? sc[r] : 1.0f;
+        if constexpr (WIDE) {
+            float v[16];
+            ldg256f(x + src * ldx + c, v);
+            ldg256f(x + src * ldx + c + 8, v + 8);
+            unsigned H[8], L[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) split2(sc ? f * v[2 * j] : v[2 * j], sc ? f * v[2 * j + 1] : v[2 * j + 1], H[j], L[j]);
+            stg256u(h + (long long)r * ldp + c, H);
+            stg256u(l + (long long)r * ldp + c, L);
+        } else {
+            float v = x[src * ldx + c];
+            if (sc) v *= f;
+            const __nv_bfloat16 vh = __float2bfloat16_rn(v);
+            h[(long long)r * ldp + c] = vh;
+            l[(long long)r * ldp + c] = __float2bfloat16_rn(v - __bfloat162float(vh));
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256)
 k_split_bf16(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
              __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, long long ldp, long long strideP) {
@@ -718,13 +781,19 @@ int launch_split_bf16(const float *X, long long ldx, long long strideX, int rows
     const bool vec = cols % 8 == 0 && ldx % 4 == 0 && strideX % 4 == 0 && ldp % 8 == 0 && strideP % 8 == 0 &&
                      (reinterpret_cast<uintptr_t>(X) & 15) == 0 && (reinterpret_cast<uintptr_t>(hi) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(lo) & 15) == 0;
-    const long long total = vec ? (long long)rows * (cols / 8) : (long long)rows * cols;
+    const bool wide = vec && cols % 16 == 0 && ldx % 8 == 0 && strideX % 8 == 0 && ldp % 16 == 0 && strideP % 16 == 0 &&
+                      (reinterpret_cast<uintptr_t>(X) & 31) == 0 && (reinterpret_cast<uintptr_t>(hi) & 31) == 0 &&
+                      (reinterpret_cast<uintptr_t>(lo) & 31) == 0;
+    const long long total = wide ? (long long)rows * (cols / 16) : vec ? (long long)rows * (cols / 8) : (long long)rows * cols;
     long long ctas = (total + 256 * 4 - 1) / (256 * 4);
     const long long cap = (148LL * 32 + batch - 1) / batch;
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;
     dim3 grid((unsigned)ctas, batch);
-    if (vec)
+    if (wide)
+        k_split_bf16_wide<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols / 16, static_cast<__nv_bfloat16 *>(hi),
+                                                static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    else if (vec)
         k_split_bf16_vec<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols / 8, static_cast<__nv_bfloat16 *>(hi),
                                                static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
     else
@@ -735,6 +804,45 @@ int launch_split_bf16(const float *X, long long ldx, long long strideX, int rows
 }
 
 // fp32 -> three bf16 planes (hi, mid, lo): x = hi + mid + lo to 24 bits.
+// Three planes, 16 elements per thread with 256-bit accesses (32-byte aligned rows everywhere).
+__global__ void __launch_bounds__(256)
+k_split_bf16_3_wide(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols16,
+                    __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ mid, __nv_bfloat16 *__restrict__ lo,
+                    long long ldp, long long strideP) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    const long long po = (long long)b * strideP;
+    const long long total = (long long)rows * cols16;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / cols16), c = (int)(e - (long long)r * cols16) * 16;
+        float v[16];
+        ldg256f(x + (long long)r * ldx + c, v);
+        ldg256f(x + (long long)r * ldx + c + 8, v + 8);
+        unsigned H[8], M[8], L[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            unsigned short hh[2], mm[2], ll[2];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const float a = v[2 * j + t];
+                const __nv_bfloat16 h = __float2bfloat16_rn(a);
+                const float r1 = a - __bfloat162float(h);
+                const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+                hh[t] = __bfloat16_as_ushort(h);
+                mm[t] = __bfloat16_as_ushort(m);
+                ll[t] = __bfloat16_as_ushort(__float2bfloat16_rn(r1 - __bfloat162float(m)));
+            }
+            H[j] = (unsigned)hh[0] | ((unsigned)hh[1] << 16);
+            M[j] = (unsigned)mm[0] | ((unsigned)mm[1] << 16);
+            L[j] = (unsigned)ll[0] | ((unsigned)ll[1] << 16);
+        }
+        const long long o = po + (long long)r * ldp + c;
+        stg256u(hi + o, H);
+        stg256u(mid + o, M);
+        stg256u(lo + o, L);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 k_split_bf16_3(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
                __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ mid, __nv_bfloat16 *__restrict__ lo,
@@ -754,15 +862,48 @@ k_split_bf16_3(const float *__restrict__ X, long long ldx, long long strideX, in
     }
 }
 
+int launch_split_bf16_rows(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                           const long long *index, long long stride_index, const float *scale, long long stride_scale,
+                           void *hi, void *lo, long long ldp, long long strideP, cudaStream_t s) {
+    if (rows < 0 || cols < 0 || batch < 0 || batch > 65535) return record(QT_ERR_ARG);
+    if (rows == 0 || cols == 0 || batch == 0) return record(QT_OK);
+    if (!X || !hi || !lo || ldx < cols || ldp < cols) return record(QT_ERR_ARG);
+    const bool wide = cols % 16 == 0 && ldx % 8 == 0 && strideX % 8 == 0 && ldp % 16 == 0 && strideP % 16 == 0 &&
+                      ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 31) == 0;
+    const long long total = (long long)rows * (wide ? cols / 16 : cols);
+    long long ctas = (total + 256 * 4 - 1) / (256 * 4);
+    const long long cap = (148LL * 32 + batch - 1) / batch;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    dim3 grid((unsigned)ctas, batch);
+    if (wide)
+        k_split_bf16_rows<true><<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, index, stride_index, scale, stride_scale,
+                                                      static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    else
+        k_split_bf16_rows<false><<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, index, stride_index, scale, stride_scale,
+                                                       static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    count_launch(1);
+    return check_launch();
+}
+
 int launch_split_bf16_3(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
                         void *hi, void *mid, void *lo, long long ldp, long long strideP, cudaStream_t s) {
     if (rows < 0 || cols < 0 || batch < 0 || batch > 65535) return record(QT_ERR_ARG);
     if (rows == 0 || cols == 0 || batch == 0) return record(QT_OK);
     if (!X || !hi || !mid || !lo || ldx < cols || ldp < cols) return record(QT_ERR_ARG);
-    long long ctas = ((long long)rows * cols + 1023) / 1024;
+    const bool wide = cols % 16 == 0 && ldx % 8 == 0 && strideX % 8 == 0 && ldp % 16 == 0 && strideP % 16 == 0 &&
+                      ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(mid) |
+                        reinterpret_cast<uintptr_t>(lo)) & 31) == 0;
+    long long ctas = ((long long)rows * (wide ? cols / 16 : cols) + 1023) / 1024;
     const long long cap = (148LL * 32 + batch - 1) / batch;
     if (ctas > cap) ctas = cap;
     dim3 grid((unsigned)(ctas < 1 ? 1 : ctas), batch);
+    if (wide) {
+        k_split_bf16_3_wide<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols / 16, static_cast<__nv_bfloat16 *>(hi),
+                                                  static_cast<__nv_bfloat16 *>(mid), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+        count_launch(1);
+        return check_launch();
+    }
     k_split_bf16_3<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, static_cast<__nv_bfloat16 *>(hi),
                                          static_cast<__nv_bfloat16 *>(mid), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
     count_launch(1);
@@ -980,6 +1121,13 @@ extern "C" {
 int qt_split_bf16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
                   void *hi, void *lo, long long ldp, long long strideP, void *stream) {
     return launch_split_bf16(X, ldx, strideX, rows, cols, batch, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
+}
+
+int qt_split_bf16_rows(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                       const long long *index, long long stride_index, const float *scale, long long stride_scale,
+                       void *hi, void *lo, long long ldp, long long strideP, void *stream) {
+    return launch_split_bf16_rows(X, ldx, strideX, rows, cols, batch, index, stride_index, scale, stride_scale,
+                                  hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
 }
 
 int qt_gemm_bf16x3(const void *Ahi, const void *Alo, long long lda, long long strideA, int a_mn,

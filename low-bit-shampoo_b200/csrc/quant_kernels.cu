@@ -425,15 +425,21 @@ k_dequantize_vec(const unsigned char *__restrict__ in_base, long long stride_in,
 // (hi = bf16(x), lo = bf16(x - hi)) with row pitch ldp.  Output matrix j is taken from state
 // slot slots[j] (or j when slots == nullptr), so a product's batch can be assembled from
 // scattered slots of an arena without an fp32 copy, a stack and a split pass in between.
-// Eight elements per thread: one 32/64-bit code load, two 128-bit stores.
+// EPL = 8 elements per thread (one 32/64-bit code load, one 128-bit store per plane) or, with
+// 32-byte aligned rows, 16 (one 256-bit store per plane).
 // ------------------------------------------------------------------------------------
-template <int BITS>
+__device__ __forceinline__ void stg256u(void *p, const unsigned (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
+template <int BITS, int EPL>
 __global__ void __launch_bounds__(kThreads)
 k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_in, const float *__restrict__ code,
                     int n, int nb, int bs_shift, const float *__restrict__ absmax_base, long long stride_absmax,
                     const float *__restrict__ diag_base, long long stride_diag, const int *__restrict__ slots,
                     __nv_bfloat16 *__restrict__ hi_base, __nv_bfloat16 *__restrict__ lo_base, long long ldp, long long strideP) {
-    constexpr int NC = 1 << BITS, EPL = 8;
+    constexpr int NC = 1 << BITS;
     __shared__ float2 pair_lut[BITS == 4 ? 256 : 1];
     __shared__ float code_s[BITS == 8 ? 256 : 16];
     for (int i = threadIdx.x; i < NC; i += blockDim.x) code_s[i] = code[i];
@@ -463,17 +469,30 @@ k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_
         const float z = (amax == 0.0f) ? 0.0f : -0.0f;        // exact +0.0 for all-zero blocks
         float v[EPL];
         if constexpr (BITS == 4) {
-            const unsigned w = __ldg(reinterpret_cast<const unsigned *>(in + (e >> 1)));
+            unsigned w[EPL / 8];
+            if constexpr (EPL == 16) {
+                const uint2 ww = __ldg(reinterpret_cast<const uint2 *>(in + (e >> 1)));
+                w[0] = ww.x; w[1] = ww.y;
+            } else {
+                w[0] = __ldg(reinterpret_cast<const unsigned *>(in + (e >> 1)));
+            }
 #pragma unroll
             for (int j = 0; j < EPL / 2; ++j) {
-                const float2 pr = pair_lut[(w >> (8 * j)) & 255u];
+                const float2 pr = pair_lut[(w[j / 4] >> (8 * (j & 3))) & 255u];
                 v[2 * j] = fmaf(pr.x, amax, z);
                 v[2 * j + 1] = fmaf(pr.y, amax, z);
             }
         } else {
-            const uint2 ww = __ldg(reinterpret_cast<const uint2 *>(in + e));
+            unsigned w[EPL / 4];
+            if constexpr (EPL == 16) {
+                const uint4 ww = __ldg(reinterpret_cast<const uint4 *>(in + e));
+                w[0] = ww.x; w[1] = ww.y; w[2] = ww.z; w[3] = ww.w;
+            } else {
+                const uint2 ww = __ldg(reinterpret_cast<const uint2 *>(in + e));
+                w[0] = ww.x; w[1] = ww.y;
+            }
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) v[j] = fmaf(code_s[((j < 4 ? ww.x : ww.y) >> (8 * (j & 3))) & 255u], amax, z);
+            for (int j = 0; j < EPL; ++j) v[j] = fmaf(code_s[(w[j / 4] >> (8 * (j & 3))) & 255u], amax, z);
         }
         if (diag && (unsigned)(r - c) < (unsigned)EPL) {
             const float d = diag[r];
@@ -481,9 +500,9 @@ k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_
             for (int j = 0; j < EPL; ++j)
                 if (c + j == r) v[j] = d;
         }
-        unsigned h[4], l[4];
+        unsigned h[EPL / 2], l[EPL / 2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < EPL / 2; ++j) {
             const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * j]), h1 = __float2bfloat16_rn(v[2 * j + 1]);
             const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * j] - __bfloat162float(h0));
             const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * j + 1] - __bfloat162float(h1));
@@ -491,8 +510,13 @@ k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_
             l[j] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
         }
         const long long o = (long long)r * ldp + c;
-        *reinterpret_cast<uint4 *>(hi + o) = make_uint4(h[0], h[1], h[2], h[3]);
-        *reinterpret_cast<uint4 *>(lo + o) = make_uint4(l[0], l[1], l[2], l[3]);
+        if constexpr (EPL == 16) {
+            stg256u(hi + o, h);
+            stg256u(lo + o, l);
+        } else {
+            *reinterpret_cast<uint4 *>(hi + o) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4 *>(lo + o) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
         r += dr; cc += dc;
         if (cc >= chunks_per_row) { cc -= chunks_per_row; r += 1; }
     }
@@ -753,13 +777,17 @@ int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, v
     const int n = a.n, nb = (n + a.bs - 1) / a.bs;
     int bs_shift = 0;
     while ((1 << bs_shift) < a.bs) ++bs_shift;
-    dim3 grid(grid_x_for((long long)n * (n / 8), a.count, 4), a.count);
-    if (a.bits == 4)
-        k_dequantize_planes<4><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax, a.stride_absmax,
-            a.diag, a.stride_diag, slots, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
-    else
-        k_dequantize_planes<8><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax, a.stride_absmax,
-            a.diag, a.stride_diag, slots, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP);
+    // 16 elements per thread: 256-bit plane stores (32-byte rows) and 8/16-byte code loads
+    const int in16 = a.bits == 4 ? 8 : 16;
+    const bool wide = n % 16 == 0 && ldp % 16 == 0 && strideP % 16 == 0 && aligned(hi, 32) && aligned(lo, 32) &&
+                      aligned(a.A, in16) && a.strideA % in16 == 0 && a.bs >= 16;
+    dim3 grid(grid_x_for((long long)n * (n / (wide ? 16 : 8)), a.count, 4), a.count);
+#define QT_DQP(B, E)                                                                                                    \
+    k_dequantize_planes<B, E><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax, a.stride_absmax, \
+        a.diag, a.stride_diag, slots, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP)
+    if (a.bits == 4) { if (wide) QT_DQP(4, 16); else QT_DQP(4, 8); }
+    else { if (wide) QT_DQP(8, 16); else QT_DQP(8, 8); }
+#undef QT_DQP
     count_launch(1);
     return check_launch();
 }

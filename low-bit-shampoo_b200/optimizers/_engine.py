@@ -253,6 +253,18 @@ def op_scaled_gram(rows, weights, want_planes=False):
     return mm(rows, scaled, trans_a=True, want_planes=want_planes and _tc(rows.f32))
 
 
+def op_scaled_gram_gathered(Vt, idx, weights):
+    """rows^T diag(weights) rows with rows = Vt[idx] (utils.py:202-203); Vt fp32 (b, n, n), idx int64
+    (b, k), weights fp32 (b, k).  On the tensor-core path the gather and the scaling happen while
+    the operands are split into planes, so neither rows nor the scaled copy is materialised."""
+    if _tc(Vt) and Vt.stride(2) == 1:
+        A = _gemm.split_rows(Vt, idx)
+        B = _gemm.split_rows(Vt, idx, weights.contiguous())
+        D, _ = _gemm.matmul(A, B, trans_a=True)
+        return Mat(D)
+    return op_scaled_gram(Mat(_gather_rows(Vt, idx)), weights)
+
+
 def op_ema_gram(L, G, axis, w1, w2):
     """w1 L + w2 G G^T (axis 0) or w1 L + w2 G^T G (axis 1) (shampoo2.py:185-199); L fp32 tensor.
 
@@ -466,8 +478,7 @@ def _class_statistics(cls, entries, w1, w2, eps, exact):
             if cls.stat.lowbit:
                 for _ in range(cls.rect_t1):
                     Vt = op_bjorck(Vt, want_planes=True)
-            rows = Mat(_gather_rows(Vt.f32, cls.keep_idx[a:b]))
-            L = op_scaled_gram(rows, cls.S[a:b]).f32
+            L = op_scaled_gram_gathered(Vt.f32, cls.keep_idx[a:b], cls.S[a:b]).f32
             L = _ema_update(L, ga, w1, w2)
             V, eigs = op_subspace_step(Mat(L), Vt)
             vals, idx = torch.sort(eigs, dim=1)
@@ -521,8 +532,8 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent):
                 weights = 1 / (cls.S[a:b] + rho.unsqueeze(1)).pow(1 / exponent)
                 if cls.prec.fusable() and _tc(rows.f32 if rows.f32 is not None else rows._planes.hi):
                     # rows^T diag(w) rows straight into the 4-bit preconditioner (quantized in the epilogue)
-                    scaled = Mat(weights.unsqueeze(2) * rows.f32)
-                    _gemm.matmul_q4(rows.planes, scaled.planes, cls.prec.code, cls.prec.state(a, b), trans_a=True)
+                    scaled = _gemm.split_rows(rows.f32, None, weights.contiguous())
+                    _gemm.matmul_q4(rows.planes, scaled, cls.prec.code, cls.prec.state(a, b), trans_a=True)
                     continue
                 P = op_scaled_gram(rows, weights).f32
             else:

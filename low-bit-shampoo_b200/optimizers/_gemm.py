@@ -1,7 +1,7 @@
 """Host wrappers of the tcgen05 matrix-product kernels (qt_split_bf16, qt_gemm_bf16x3).
 
 A `Planes` object is an fp32 matrix batch carried as two bf16 planes (hi, lo) with a row
-pitch that is a multiple of 8 elements, the operand format of the kernel.  `matmul`
+pitch that is a multiple of 16 elements, the operand format of the kernel.  `matmul`
 multiplies two such batches with any combination of transposes without moving data: a
 transposed operand is presented to the kernel as an MN-major tile.
 """
@@ -17,7 +17,7 @@ def _ptr(t):
 
 
 def _pitch(cols):
-    return (cols + 7) // 8 * 8
+    return (cols + 15) // 16 * 16       # 32-byte rows: TMA needs 16, the 256-bit epilogue stores 32
 
 
 class Planes:
@@ -80,6 +80,26 @@ def split(X):
         rc = F.lib.qt_split_bf16(_ptr(X), X.stride(1), X.stride(0), r, c, b, P.ptr_hi(), P.ptr_lo(), P.ld, P.stride,
                                  F._stream(X))
     F._check(rc, "split_bf16")
+    return P
+
+
+def split_rows(X, index=None, scale=None):
+    """Planes of the matrices whose row i is scale[b, i] * X[b, index[b, i], :] (qt_split_bf16_rows).
+    X: fp32 (batch, R, cols); index: int64 (batch, rows) or None; scale: fp32 (batch, rows) or None."""
+    assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
+    b, R, c = X.shape
+    rows = index.shape[1] if index is not None else R
+    if index is not None:
+        assert index.dtype == torch.int64 and index.shape[0] == b and index.stride(1) == 1
+    if scale is not None:
+        assert scale.dtype == torch.float32 and scale.shape == (b, rows) and scale.stride(1) == 1
+    P = Planes(b, rows, c, X.device)
+    with torch.cuda.device(X.device):
+        rc = F.lib.qt_split_bf16_rows(_ptr(X), X.stride(1), X.stride(0), rows, c, b,
+                                      _ptr(index), index.stride(0) if index is not None else 0,
+                                      _ptr(scale), scale.stride(0) if scale is not None else 0,
+                                      P.ptr_hi(), P.ptr_lo(), P.ld, P.stride, F._stream(X))
+    F._check(rc, "split_bf16_rows")
     return P
 
 

@@ -101,8 +101,8 @@ def test_three_plane_product_reaches_fp32_accuracy(native_lib, trans_a, trans_b)
     assert rel(D, ref) < 2e-6, rel(D, ref)               # measured 8e-7, independent of K
     assert rel(D, ref) < 4 * rel(fp32, ref) + 1e-6
     P = _gemm.split3(A)
-    back = P.hi.float() + P.mid.float() + P.lo.float()
-    assert float((back.view(-1)[: A.numel()].view_as(A) - A).abs().max() / A.abs().max()) < 2.0 ** -22
+    back = (P.hi.float() + P.mid.float() + P.lo.float()).view(b, A.shape[1], P.ld)[:, :, : A.shape[2]]   # rows are padded to the pitch
+    assert float((back - A).abs().max() / A.abs().max()) < 2.0 ** -22
 
 
 def _state(b, n, device, diagreal):
@@ -187,3 +187,21 @@ def test_quantizing_epilogue_equals_unfused_sequence(native_lib, n, k, axis, dia
     if with_old:
         ref = ref + w1 * Lold.double()
     assert rel(D, ref) < TOL
+
+
+def test_split_rows_gathers_and_scales(native_lib):
+    """qt_split_bf16_rows == split(scale[:, :, None] * X[gathered rows]) bit for bit, wide and scalar variants."""
+    from optimizers import _gemm
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for cols in (768, 100):
+        X = torch.randn(3, 40, cols, device="cuda", generator=g)
+        idx = torch.stack([torch.randperm(40, device="cuda", generator=g)[:17] for _ in range(3)])
+        w = torch.rand(3, 17, device="cuda", generator=g) + 0.5
+        for index, scale in ((idx, w), (idx, None), (None, torch.rand(3, 40, device="cuda", generator=g))):
+            P = _gemm.split_rows(X, index, scale)
+            ref = X if index is None else torch.gather(X, 1, index.unsqueeze(2).expand(-1, -1, cols))
+            if scale is not None:
+                ref = scale.unsqueeze(2) * ref
+            W = _gemm.split(ref.contiguous())
+            assert device_ok(native_lib)
+            assert torch.equal(P.to_float(), W.to_float())
