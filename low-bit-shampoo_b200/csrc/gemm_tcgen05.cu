@@ -366,6 +366,12 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             bool ok = true;
             int j = 0;                                      // accumulator hand-offs so far
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                // a ragged last column band needs only its own columns (N is any multiple of 16):
+                // the tensor core's time per MMA scales with N
+                int tm_, tn_, b_;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm_, tn_, b_);
+                const int ncur = min(BN, (p.N - tn_ * BN + 15) & ~15);
+                const unsigned idesc_tile = (idesc & ~(0x3Fu << 17)) | ((unsigned)(ncur >> 3) << 17);
                 const int nchunks = KC ? (num_kb + KC - 1) / KC : 1;
                 int kb = 0;
                 for (int ch = 0; ch < nchunks && ok; ++ch, ++j) {
@@ -393,7 +399,7 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                             for (int sum = NP - 1; sum >= 0; --sum) {
 #pragma unroll
                                 for (int ia = 0; ia <= sum; ++ia) {
-                                    umma_bf16(tmem_acc, dA[ia] + ao, dB[sum - ia] + bo, idesc, first ? 0u : 1u);
+                                    umma_bf16(tmem_acc, dA[ia] + ao, dB[sum - ia] + bo, idesc_tile, first ? 0u : 1u);
                                     first = false;
                                 }
                             }
