@@ -156,6 +156,17 @@ int qt_householder_panel(const float *A, long long strideA, int order, int count
                          float *V, long long strideV, float *T, long long strideT, void *stream);
 
 /*
+ * Triangular factor T (width x width, width <= 128) of a block of up to four consecutive panels,
+ * H_1 .. H_width = I - Vo T Vo^T, from the panels' factors (Tp + m*strideTp: consecutive 32 x 32
+ * row-major factors as written by qt_householder_panel) and the Gram matrix G = Vo^T Vo
+ * (G + m*strideG, ldg floats between rows): LAPACK's larft recurrence on blocks.  T + m*strideT
+ * is written whole, row-major, pitch `width`.  Part of the same replacement of
+ * torch.linalg.qr (qtensor/utils.py:157).
+ */
+int qt_merge_t(const float *G, long long ldg, long long strideG, const float *Tp, long long strideTp, int width, int count,
+               float *T, long long strideT, void *stream);
+
+/*
  * fp32 matrix -> two bf16 planes, hi = bf16(x), lo = bf16(x - hi): the operand format of
  * qt_gemm_bf16x3.  X is rows x cols with ldx floats between rows, `batch` matrices strideX
  * floats apart; the planes have ldp elements between rows (a multiple of 8) and strideP

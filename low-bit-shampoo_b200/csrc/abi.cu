@@ -107,6 +107,11 @@ int qt_selftest_division(unsigned long long seed, unsigned long long pairs, unsi
     return launch_selftest_division(seed, pairs, mismatches, static_cast<cudaStream_t>(stream));
 }
 
+int qt_merge_t(const float *G, long long ldg, long long strideG, const float *Tp, long long strideTp, int width, int count,
+               float *T, long long strideT, void *stream) {
+    return launch_merge_t(G, ldg, strideG, Tp, strideTp, width, count, T, strideT, static_cast<cudaStream_t>(stream));
+}
+
 int qt_householder_panel(const float *A, long long strideA, int order, int count, int j0, int width,
                          float *V, long long strideV, float *T, long long strideT, void *stream) {
     return launch_householder_panel(A, strideA, order, count, j0, width, V, strideV, T, strideT,

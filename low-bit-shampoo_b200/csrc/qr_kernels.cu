@@ -176,4 +176,70 @@ int launch_householder_panel(const float *A, long long strideA, int n, int count
 #undef QT_PANEL
 }
 
+// Triangular factor of an outer block of up to four panels from the panels' own factors and
+// the Gram matrix G = Vo^T Vo of the block's Householder vectors (LAPACK larft recurrence on
+// blocks): with c columns done and the next panel k of width w,
+//     T[:c, c:c+w] = -T[:c, :c] * G[:c, c:c+w] * T_k,   T[c:c+w, c:c+w] = T_k.
+// One CTA per matrix; T (<= 128 x 128) is assembled in shared memory and written out whole
+// (zeros below the diagonal blocks).  Replaces ~17 small library launches per outer block.
+static constexpr int kMergeMax = 128;
+__global__ void __launch_bounds__(256)
+k_merge_t(const float *__restrict__ Gbase, long long ldg, long long strideG,
+          const float *__restrict__ Tp_base, long long strideTp, int wo,
+          float *__restrict__ Tbase, long long strideT) {
+    extern __shared__ float merge_sm[];
+    float (*Ts)[kMergeMax + 1] = reinterpret_cast<float (*)[kMergeMax + 1]>(merge_sm);
+    float (*M1)[kPanel + 1] = reinterpret_cast<float (*)[kPanel + 1]>(merge_sm + kMergeMax * (kMergeMax + 1));
+    float (*Tk)[kPanel + 1] = reinterpret_cast<float (*)[kPanel + 1]>(merge_sm + kMergeMax * (kMergeMax + 1) + 96 * (kPanel + 1));
+    const float *G = Gbase + (long long)blockIdx.x * strideG;
+    const float *Tp = Tp_base + (long long)blockIdx.x * strideTp;
+    float *T = Tbase + (long long)blockIdx.x * strideT;
+    const int tid = threadIdx.x;
+    for (int i = tid; i < wo * wo; i += blockDim.x) Ts[i / wo][i % wo] = 0.0f;
+    __syncthreads();
+    for (int c = 0, k = 0; c < wo; c += kPanel, ++k) {
+        const int w = min(kPanel, wo - c);
+        for (int i = tid; i < kPanel * kPanel; i += blockDim.x) {
+            const int a = i / kPanel, b = i % kPanel;
+            Tk[a][b] = (a < w && b < w) ? Tp[(long long)k * kPanel * kPanel + i] : 0.0f;
+        }
+        __syncthreads();
+        for (int i = tid; i < w * w; i += blockDim.x) Ts[c + i / w][c + i % w] = Tk[i / w][i % w];
+        if (c > 0) {
+            for (int e = tid; e < c * w; e += blockDim.x) {                 // M1 = T[:c, :c] G[:c, c:c+w]
+                const int i = e / w, j = e % w;
+                float acc = 0.0f;
+                for (int l = i; l < c; ++l) acc = fmaf(Ts[i][l], G[(long long)l * ldg + c + j], acc);   // T is upper triangular
+                M1[i][j] = acc;
+            }
+            __syncthreads();
+            for (int e = tid; e < c * w; e += blockDim.x) {                 // T[:c, c:c+w] = -M1 T_k
+                const int i = e / w, j = e % w;
+                float acc = 0.0f;
+                for (int l = 0; l <= j; ++l) acc = fmaf(M1[i][l], Tk[l][j], acc);                      // T_k is upper triangular
+                Ts[i][c + j] = -acc;
+            }
+        }
+        __syncthreads();
+    }
+    for (int i = tid; i < wo * wo; i += blockDim.x) T[i] = Ts[i / wo][i % wo];
+}
+
+int launch_merge_t(const float *G, long long ldg, long long strideG, const float *Tp, long long strideTp, int wo, int count,
+                   float *T, long long strideT, cudaStream_t s) {
+    if (wo <= 0 || wo > kMergeMax || count < 0 || ldg < wo) return record(QT_ERR_ARG);
+    if (!G || !Tp || !T) return record(QT_ERR_ARG);
+    if (count == 0) return record(QT_OK);
+    constexpr size_t smem = sizeof(float) * (kMergeMax * (kMergeMax + 1) + 96 * (kPanel + 1) + kPanel * (kPanel + 1));
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_merge_t, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return record(QT_ERR_LAUNCH);
+        attr_set = true;
+    }
+    k_merge_t<<<count, 256, smem, s>>>(G, ldg, strideG, Tp, strideTp, wo, T, strideT);
+    count_launch(1);
+    return check_launch();
+}
+
 }  // namespace qt

@@ -37,6 +37,8 @@ struct DequantArgs {
     void *out; int out_dtype; long long stride_out;         // elements
 };
 
+int launch_merge_t(const float *G, long long ldg, long long strideG, const float *Tp, long long strideTp, int wo, int count,
+                   float *T, long long strideT, cudaStream_t stream);
 int launch_quantize(const QuantArgs &a, cudaStream_t stream);
 int launch_dequantize(const DequantArgs &a, cudaStream_t stream);
 // a.out / a.out_dtype / a.stride_out are ignored: output goes to the bf16 planes hi, lo

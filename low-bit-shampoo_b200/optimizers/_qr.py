@@ -48,6 +48,16 @@ def _merge_t(Vo, Tp, widths, Pv=None):
     With `Pv` (planes of Vo) the Gram matrix Vo^T Vo is a tensor-core product."""
     B = Vo.shape[0]
     wo = sum(widths)
+    if Pv is not None and len(widths) > 1 and wo <= 128 and Tp.stride(3) == 1 and Tp.stride(2) == PANEL and Tp.stride(1) == PANEL * PANEL:
+        # one launch: Gram matrix on the tensor cores, recurrence in the library's merge kernel
+        from optimizers import _gemm
+        G, _ = _gemm.matmul(Pv, Pv, trans_a=True)
+        T = torch.empty(B, wo, wo, dtype=torch.float32, device=Vo.device)
+        with torch.cuda.device(Vo.device):
+            rc = F.lib.qt_merge_t(_ptr(G), G.stride(1), G.stride(0), _ptr(Tp), Tp.stride(0), wo, B,
+                                  _ptr(T), wo * wo, F._stream(Vo))
+        F._check(rc, "merge_t")
+        return T
     T = torch.zeros(B, wo, wo, dtype=torch.float32, device=Vo.device)
     G = None
     if len(widths) > 1:
