@@ -297,6 +297,23 @@ int qt_matmul_f32_static(const float *A, long long lda, long long strideA, int t
                          const float *C, long long ldc, long long strideC,
                          float *D, long long ldd, long long strideD, void *stream);
 
+/*
+ * Fused AdamW tail of the Shampoo step over a list of fp32 tensors, one launch
+ * (optimizers/shampoo2.py:441 and :457-466: decoupled weight decay, both moments, bias-corrected
+ * update), d being the preconditioned and grafted direction:
+ *     p <- p * scalars[2];  m <- beta1 m + (1-beta1) d;  v <- beta2 v + (1-beta2) d d;
+ *     p <- p + scalars[1] * m / (sqrt(v) * scalars[0] + eps)
+ * with scalars = { 1/sqrt(1-beta2^t), -lr/(1-beta1^t), 1 - lr*weight_decay } in DEVICE memory.
+ * one_minus_beta{1,2} are passed separately because the reference forms 1 - beta in double
+ * precision before rounding (1 - 0.999 differs from 1.0f - 0.999f by 1.3e-5 relative).
+ * All tables are device arrays: per tensor the four addresses (as 64-bit integers) and the
+ * element count; per CTA a (tensor, chunk) pair; a chunk is chunk_elems elements (a multiple of 4).
+ */
+int qt_adamw_tail(const long long *p_ptrs, const long long *d_ptrs, const long long *m_ptrs, const long long *v_ptrs,
+                  const long long *numels, const int *chunk_tensor, const int *chunk_index, int num_chunks,
+                  int chunk_elems, const float *scalars, float beta1, float beta2, float one_minus_beta1,
+                  float one_minus_beta2, float eps, void *stream);
+
 /* Sticky device-side error word (QT_OK or QT_ERR_TIMEOUT); synchronises the device.
  * clear != 0 resets it.  Additive; the reference has no device-side waits. */
 int qt_device_error(int clear);

@@ -6,6 +6,7 @@ grafting, the AdamW / SGD tails - is common.  Class and argument names follow th
 reference's optimizers/shampoo2.py (BlockPartitioner :35-99, Preconditioner :102-275,
 ShampooSGD :278-367, ShampooAdamW :370-468) and optimizers/shampoo1.py.
 """
+import ctypes as ct
 import itertools
 import warnings
 import math
@@ -17,6 +18,8 @@ import torch.optim as optim
 import qtensor.functional as F
 from qtensor.utils import QTensorDiagReal, QTensorSVDFast
 from optimizers import _engine as E
+
+FUSED_TAIL = True              # AdamW tail as one multi-tensor launch of the library (CUDA fp32 parameters)
 
 CODE = 'linear-2'
 
@@ -415,16 +418,14 @@ class _ShampooBase(optim.Optimizer):
             gs = self._graph_state = {
                 "ids": ids, "graphs": {},
                 "grads": [torch.empty_like(p.grad) for p in params],
-                "scalars": torch.zeros(2, device=params[0].device),
-                "host": torch.zeros(2).pin_memory(),
+                "scalars": torch.zeros(3, device=params[0].device),
             }
         step = self.state[params[0]]['step'] + 1
         fires_stat = step % group['stat_compute_steps'] == 0
         fires_root = step % group['prec_compute_steps'] == 0
         active = tuple(self.state[p]['preconditioner'].is_active() for p in params)
         key = (fires_stat, fires_root, all(active), any(active), step >= group['start_prec_step'])
-        self._graph_scalars(group, step, gs["host"])
-        gs["scalars"].copy_(gs["host"], non_blocking=True)
+        self._stage_scalars(group, step, gs["scalars"])
         torch._foreach_copy_(gs["grads"], [p.grad for p in params])
         user_grads = [p.grad for p in params]
         for p, g in zip(params, gs["grads"]):
@@ -515,15 +516,97 @@ class ShampooAdamWBase(_ShampooBase):
 
     def _graph_scalars(self, group, step, out):
         """Step-dependent scalars of the tail, written where a captured graph reads them:
-        out[0] = 1 / sqrt(1 - beta2^t), out[1] = -lr / (1 - beta1^t)."""
+        out[0] = 1 / sqrt(1 - beta2^t), out[1] = -lr / (1 - beta1^t), out[2] = 1 - lr * weight_decay."""
         beta1, beta2 = group['betas']
         out[0] = 1.0 / math.sqrt(1 - beta2 ** step)
         out[1] = -(group['lr'] / (1 - beta1 ** step))
+        out[2] = 1 - group['lr'] * group['weight_decay']
+
+    def _stage_scalars(self, group, step, dst):
+        """Asynchronous copy of this step's factors to the device through a ring of pinned buffers:
+        the host may run several steps ahead of the device, so a buffer is reused only after the
+        copy that read it has completed (its event), never by overwriting one still in flight."""
+        ring = self.__dict__.setdefault("_scalar_ring", {"next": 0, "slots": []})
+        if not ring["slots"]:
+            ring["slots"] = [[torch.zeros(3).pin_memory(), None] for _ in range(8)]
+        slot = ring["slots"][ring["next"]]
+        ring["next"] = (ring["next"] + 1) % len(ring["slots"])
+        if slot[1] is not None:
+            slot[1].synchronize()
+        self._graph_scalars(group, step, slot[0])
+        dst.copy_(slot[0], non_blocking=True)
+        slot[1] = torch.cuda.Event()
+        slot[1].record(torch.cuda.current_stream(dst.device))
+
+    # ---- fused tail: one launch of the library's multi-tensor kernel ----------------------
+    _TAIL_CHUNK = 8192
+
+    def _fused_tail_ok(self, params, directions):
+        if F.lib is None or not FUSED_TAIL or not params:
+            return False
+        dev = params[0].device
+        if dev.type != "cuda" or len({self.state[p]['step'] for p in params}) != 1:
+            return False
+        for p, d in zip(params, directions):
+            st = self.state[p]
+            if not (p.device == dev and p.dtype == torch.float32 and p.is_contiguous() and d.dtype == torch.float32
+                    and d.is_contiguous() and d.numel() == p.numel() and d.device == dev
+                    and st['exp_avg'].is_contiguous() and st['exp_avg_sq'].is_contiguous()
+                    and st['exp_avg'].dtype == torch.float32 and st['exp_avg_sq'].dtype == torch.float32):
+                return False
+        return True
+
+    def _fused_tail(self, group, params, directions, scalars):
+        """Decay, both moments and the update for every parameter in one launch (qt_adamw_tail).
+        `scalars`: device tensor of the three step-dependent factors."""
+        dev = params[0].device
+        cache = self.__dict__.setdefault("_tail_cache", {})
+        key = tuple(p.data_ptr() for p in params) + tuple(self.state[p]['exp_avg'].data_ptr() for p in params)
+        tab = cache.get(("static", key))
+        if tab is None:
+            numels = [p.numel() for p in params]
+            ct_, ci_ = [], []
+            for t, n in enumerate(numels):
+                for c in range((n + self._TAIL_CHUNK - 1) // self._TAIL_CHUNK):
+                    ct_.append(t)
+                    ci_.append(c)
+            i64 = lambda xs: torch.tensor(xs, dtype=torch.int64, device=dev)
+            # directions are gathered into one persistent buffer (their own tensors move from step to
+            # step), so every table is built once - nothing is uploaded while a graph is captured
+            flat = torch.empty(sum((n + 3) // 4 * 4 for n in numels), dtype=torch.float32, device=dev)
+            views, off = [], 0
+            for p_, n in zip(params, numels):
+                views.append(flat[off: off + n].view(p_.shape))
+                off += (n + 3) // 4 * 4
+            tab = cache[("static", key)] = dict(
+                p=i64([p.data_ptr() for p in params]), m=i64([self.state[p]['exp_avg'].data_ptr() for p in params]),
+                v=i64([self.state[p]['exp_avg_sq'].data_ptr() for p in params]), n=i64(numels),
+                d=i64([v_.data_ptr() for v_ in views]), dviews=views, dflat=flat,
+                ct=torch.tensor(ct_, dtype=torch.int32, device=dev), ci=torch.tensor(ci_, dtype=torch.int32, device=dev))
+        torch._foreach_copy_(tab["dviews"], list(directions))
+        beta1, beta2 = group['betas']
+        vp = lambda t: ct.c_void_p(t.data_ptr())
+        with torch.cuda.device(dev):
+            rc = F.lib.qt_adamw_tail(vp(tab["p"]), vp(tab["d"]), vp(tab["m"]), vp(tab["v"]), vp(tab["n"]), vp(tab["ct"]), vp(tab["ci"]),
+                                     tab["ct"].numel(), self._TAIL_CHUNK, vp(scalars), float(beta1), float(beta2),
+                                     1.0 - float(beta1), 1.0 - float(beta2), float(group['eps']), F._stream(params[0]))
+        F._check(rc, "adamw tail")
 
     def _apply_update(self, group, params, scalars=None):
-        # decoupled weight decay first, as in the reference (shampoo2.py:441)
-        torch._foreach_mul_(params, 1 - group['lr'] * group['weight_decay'])
         directions = self._precondition(group, params)
+        if self._fused_tail_ok(params, directions):
+            if scalars is None:                               # eager: stage this step's factors on the device
+                scalars = self.__dict__.get("_tail_scalars")
+                if scalars is None or scalars.device != params[0].device:
+                    scalars = self._tail_scalars = torch.zeros(3, device=params[0].device)
+                self._stage_scalars(group, self.state[params[0]]['step'], scalars)
+            self._fused_tail(group, params, directions, scalars)
+            return
+        # decoupled weight decay (shampoo2.py:441; it commutes with the preconditioning, which reads gradients only)
+        if scalars is None:
+            torch._foreach_mul_(params, 1 - group['lr'] * group['weight_decay'])
+        else:
+            torch._foreach_mul_(params, scalars[2])
         beta1, beta2 = group['betas']
         by_step = defaultdict(list)
         for k, p in enumerate(params):

@@ -174,3 +174,41 @@ def test_sharded_step_on_two_gpus_equals_single_gpu(native_lib):
         assert p.exitcode == 0
     for rank, err in results:
         assert err < 1e-5, (rank, err)
+
+
+def test_fused_adamw_tail_matches_foreach_tail(native_lib):
+    """qt_adamw_tail (one multi-tensor launch) against the tensor-wide torch operations of the same
+    tail, over several steps with a changing learning rate: parameters and both moments agree to
+    fp32 rounding (the fused kernel contracts some multiply-adds)."""
+    import copy
+    from optimizers import _base
+    from optimizers.shampoo2 import ShampooAdamW
+    torch.manual_seed(3)
+    shapes = [(96, 160), (160,), (64, 96), (7,), (130, 70)]
+    ref_params = [torch.randn(s, device="cuda").requires_grad_() for s in shapes]
+    new_params = [p.detach().clone().requires_grad_() for p in ref_params]
+    kw = dict(lr=1e-2, weight_decay=0.1, prec_bits=4, stat_compute_steps=1, prec_compute_steps=1, start_prec_step=1,
+              min_lowbit_size=4096)
+    opts = []
+    for fused, ps in ((False, ref_params), (True, new_params)):
+        _base.FUSED_TAIL = fused
+        opts.append(ShampooAdamW(ps, **kw))
+    try:
+        for step in range(4):
+            grads = [torch.randn_like(p) for p in ref_params]
+            for fused, opt, ps in ((False, opts[0], ref_params), (True, opts[1], new_params)):
+                _base.FUSED_TAIL = fused
+                for g in opt.param_groups:
+                    g['lr'] = 1e-2 / (step + 1)
+                for p, g in zip(ps, grads):
+                    p.grad = g.clone()
+                opt.step()
+    finally:
+        _base.FUSED_TAIL = True
+    torch.cuda.synchronize()
+    assert native_lib.qt_last_error() == 0
+    for a, b, oa, ob in zip(ref_params, new_params, opts[0].param_groups[0]['params'], opts[1].param_groups[0]['params']):
+        assert float((a.detach() - b.detach()).norm() / a.detach().norm()) < 2e-6
+        for k in ('exp_avg', 'exp_avg_sq'):
+            x, y = opts[0].state[oa][k], opts[1].state[ob][k]
+            assert float((x - y).norm() / x.norm().clamp_min(1e-30)) < 2e-6
