@@ -291,9 +291,12 @@ class _ShampooBase(optim.Optimizer):
                 inv_root_mode=group.get('inv_root_mode', 0), classes=classes.get(p.device))
             self._init_moments(p, state)
 
-    def _precondition(self, group, params):
+    def _precondition(self, group, params, split_exchange=False):
         """Runs the statistics / inverse-root / apply phases for `params` (all with grads) and
-        returns the list of update directions (grafted to the gradient norm where active)."""
+        returns the list of update directions (grafted to the gradient norm where active).
+        With `split_exchange` the sharded exchange stops after the pack: the caller then calls
+        _exchange_collective() and _exchange_unpack() itself."""
+        self._pending_exchange = None
         t1, t2 = group['stat_compute_steps'], group['prec_compute_steps']
         start = group['start_prec_step']
         stat_items, root_items, apply_list = [], [], []
@@ -342,23 +345,43 @@ class _ShampooBase(optim.Optimizer):
                 torch._foreach_div_(gn, dn)
                 torch._foreach_mul_(dirs, gn)
             if self._world > 1:
-                self._exchange(params, directions, apply_list)
+                self._pending_exchange = self._exchange_pack(params, directions, apply_list)
+        if not split_exchange:
+            self._exchange_collective()
+            self._exchange_unpack(params, directions)
         return directions
 
-    def _exchange(self, params, directions, apply_list):
-        """All-gather of the owners' preconditioned, grafted directions (one collective)."""
+    # The one exchange step of the sharded optimizer, in three parts so that a captured CUDA graph
+    # can end after the pack and the next one start at the unpack, with the collective issued
+    # eagerly in between (NCCL inside a captured graph did not return on this stack).
+    def _exchange_pack(self, params, directions, apply_list):
         from optimizers._sharding import GatherPlan
         shipped = [(k, p) for k, p, pre in apply_list if self.state[p]['owner'] >= 0]
         if not shipped:
-            return
+            return None
         sig = tuple(k for k, _ in shipped)
         plan = self._plans.get((id(params[0]), sig))
         if plan is None:
             plan = GatherPlan([(k, p.numel(), self.state[p]['owner']) for k, p in shipped], self._world)
             self._plans[(id(params[0]), sig)] = plan
         local = {k: directions[k] for k, p in shipped if self.state[p]['owner'] == self._rank}
-        ref = params[shipped[0][0]]
-        got = plan.exchange(local, self._rank, self._pg, ref.device, torch.float32)
+        dev = params[shipped[0][0]].device
+        plan.pack(local, self._rank, dev, torch.float32)
+        return plan, shipped, dev
+
+    def _exchange_collective(self):
+        ctx = getattr(self, "_pending_exchange", None)
+        if ctx is not None:
+            plan, _, dev = ctx
+            plan.collective(self._pg, dev, torch.float32)
+
+    def _exchange_unpack(self, params, directions):
+        ctx = getattr(self, "_pending_exchange", None)
+        self._pending_exchange = None
+        if ctx is None:
+            return
+        plan, shipped, dev = ctx
+        got = plan.views(dev, torch.float32)
         for k, p in shipped:
             if self.state[p]['owner'] != self._rank:
                 directions[k] = got[k].view(p.shape).to(p.grad.dtype)
@@ -402,8 +425,6 @@ class _ShampooBase(optim.Optimizer):
     def _graph_eligible(self, group, params):
         if len(self.param_groups) != 1 or not hasattr(self, "_graph_scalars"):
             return False
-        if self._world > 1:
-            return False                                  # the all-gather is not captured: sharded steps run eagerly
         if self.preconditioner_cls.flavour != "s2" or group.get('inv_root_mode', 0) != 0:
             return False                                  # the Schur-Newton loop synchronises with the host
         dev = params[0].device
@@ -437,11 +458,34 @@ class _ShampooBase(optim.Optimizer):
                 lib = F.lib
                 before = lib.qt_launch_count() if lib is not None else 0
                 graph = torch.cuda.CUDAGraph()
+                tail_graph = None
+                first_half_ran = False
                 try:
-                    with torch.cuda.graph(graph):
-                        self._apply_update(group, params, scalars=gs["scalars"])
+                    if self._world == 1:
+                        with torch.cuda.graph(graph):
+                            self._apply_update(group, params, scalars=gs["scalars"])
+                    else:
+                        # sharded: graph 1 ends with this rank's directions packed into the send buffer,
+                        # the all-gather runs eagerly, graph 2 unpacks and applies the tail
+                        with torch.cuda.graph(graph):
+                            directions = self._precondition(group, params, split_exchange=True)
+                        graph.replay()
+                        pending = self._pending_exchange
+                        self._exchange_collective()
+                        first_half_ran = True
+                        tail_graph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(tail_graph, pool=graph.pool()):
+                            self._exchange_unpack(params, directions)
+                            self._apply_tail(group, params, directions, scalars=gs["scalars"])
                 except Exception as exc:
                     warnings.warn(f"CUDA-graph capture of the optimizer step failed ({exc!r}); running eagerly")
+                    if first_half_ran:                          # statistics, roots and the exchange are done: finish the step
+                        self._use_graph = False
+                        self._graph_state = None
+                        self._pending_exchange = pending
+                        self._exchange_unpack(params, directions)
+                        self._apply_tail(group, params, directions)
+                        return
                     for p, (st, act) in zip(params, book):      # capture failed: undo bookkeeping, go eager
                         self.state[p]['step'] = st
                         self.state[p]['preconditioner']._active = act
@@ -450,16 +494,25 @@ class _ShampooBase(optim.Optimizer):
                     self._apply_update(group, params)
                     return
                 launches = (lib.qt_launch_count() - before) if lib is not None else 0
-                gs["graphs"][key] = (graph, launches)
-                graph.replay()
+                if tail_graph is None:
+                    gs["graphs"][key] = (graph, launches, None, None)
+                    graph.replay()
+                else:
+                    gs["graphs"][key] = (graph, launches, tail_graph, pending)
+                    tail_graph.replay()                       # graph 1 and the collective already ran above
             else:
-                graph, launches = entry
+                graph, launches, tail_graph, pending = entry
                 for p in params:                                # host-side bookkeeping of the captured step
                     st = self.state[p]
                     st['step'] += 1
                     if fires_root:
                         st['preconditioner']._active = True
                 graph.replay()
+                if tail_graph is not None:
+                    self._pending_exchange = pending
+                    self._exchange_collective()
+                    self._pending_exchange = None
+                    tail_graph.replay()
                 if F.lib is not None and launches:
                     F.lib.qt_note_graph_replay(launches)
         finally:
@@ -594,6 +647,9 @@ class ShampooAdamWBase(_ShampooBase):
 
     def _apply_update(self, group, params, scalars=None):
         directions = self._precondition(group, params)
+        self._apply_tail(group, params, directions, scalars)
+
+    def _apply_tail(self, group, params, directions, scalars=None):
         if self._fused_tail_ok(params, directions):
             if scalars is None:                               # eager: stage this step's factors on the device
                 scalars = self.__dict__.get("_tail_scalars")

@@ -54,15 +54,41 @@ class GatherPlan:
         self.slot = max(1, max(fill))
         self.fill = fill
 
-    def exchange(self, local, rank, group, device, dtype):
-        """local: {key: tensor} for the keys this rank owns.  Returns {key: flat view} for all keys."""
+    def buffers(self, device, dtype):
+        """Persistent send / receive buffers (allocated once, so that captured CUDA graphs and the
+        eager collective between them always see the same addresses)."""
+        buf = getattr(self, "_buffers", None)
+        if buf is None or buf[0].device != torch.device(device) or buf[0].dtype != dtype:
+            buf = self._buffers = (torch.zeros(self.slot, dtype=dtype, device=device),
+                                   torch.empty(self.world * self.slot, dtype=dtype, device=device))
+        return buf
+
+    def pack(self, local, rank, device, dtype):
+        """Copies this rank's directions ({key: tensor}) into its slot of the send buffer."""
+        send, _ = self.buffers(device, dtype)
+        keys = list(local)
+        if keys:
+            dst = []
+            for key in keys:
+                owner, off, numel = self.offset[key]
+                assert owner == rank
+                dst.append(send[off: off + numel].view(local[key].shape))
+            torch._foreach_copy_(dst, [local[k] for k in keys])
+
+    def collective(self, group, device, dtype):
+        """The one exchange step of the sharded optimizer: an all-gather of every rank's slot."""
         import torch.distributed as dist
-        send = torch.zeros(self.slot, dtype=dtype, device=device)
-        for key, t in local.items():
-            owner, off, numel = self.offset[key]
-            assert owner == rank
-            send[off: off + numel].copy_(t.reshape(-1))
-        recv = torch.empty(self.world * self.slot, dtype=dtype, device=device)
+        send, recv = self.buffers(device, dtype)
         dist.all_gather_into_tensor(recv, send, group=group)
+
+    def views(self, device, dtype):
+        """{key: flat view into the receive buffer} for all keys."""
+        _, recv = self.buffers(device, dtype)
         recv = recv.view(self.world, self.slot)
         return {key: recv[owner, off: off + numel] for key, (owner, off, numel) in self.offset.items()}
+
+    def exchange(self, local, rank, group, device, dtype):
+        """local: {key: tensor} for the keys this rank owns.  Returns {key: flat view} for all keys."""
+        self.pack(local, rank, device, dtype)
+        self.collective(group, device, dtype)
+        return self.views(device, dtype)

@@ -135,19 +135,21 @@ def _sharded_worker(rank, world, port, out):
         shapes = [(256, 192), (192,), (128, 320), (64, 64), (96, 96)]
         hyper = dict(lr=1e-2, weight_decay=0.05, prec_bits=4, stat_compute_steps=1, prec_compute_steps=1)
 
-        def run(group):
+        def run(group, graph=False):
             g = torch.Generator().manual_seed(9)
             ps = [torch.nn.Parameter((torch.randn(s, generator=g) * 0.3).cuda()) for s in shapes]
-            opt = ShampooAdamW(ps, process_group=group, **hyper)
-            for _ in range(3):
+            opt = ShampooAdamW(ps, process_group=group, cuda_graph=graph, **hyper)
+            for _ in range(5):
                 for p in ps:
                     p.grad = (torch.randn(p.shape, generator=g) * 0.1).cuda()
                 opt.step()
             torch.cuda.synchronize()
+            assert opt._use_graph == graph                  # a failed capture would have switched it off
             return [p.detach().cpu() for p in ps]
 
-        sharded, single = run(dist.group.WORLD), run(None)
-        err = max(float((a - b).norm() / b.norm()) for a, b in zip(sharded, single))
+        # eager sharded, sharded with two captured graphs around the eager all-gather, single GPU
+        sharded, graphed, single = run(dist.group.WORLD), run(dist.group.WORLD, graph=True), run(None)
+        err = max(max(float((a - b).norm() / b.norm()) for a, b in zip(x, single)) for x in (sharded, graphed))
         out.put((rank, err))
     finally:
         dist.destroy_process_group()
