@@ -183,7 +183,7 @@ int launch_householder_panel(const float *A, long long strideA, int n, int count
 // One CTA per matrix; T (<= 128 x 128) is assembled in shared memory and written out whole
 // (zeros below the diagonal blocks).  Replaces ~17 small library launches per outer block.
 static constexpr int kMergeMax = 128;
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 k_merge_t(const float *__restrict__ Gbase, long long ldg, long long strideG,
           const float *__restrict__ Tp_base, long long strideTp, int wo,
           float *__restrict__ Tbase, long long strideT) {
@@ -194,35 +194,33 @@ k_merge_t(const float *__restrict__ Gbase, long long ldg, long long strideG,
     const float *G = Gbase + (long long)blockIdx.x * strideG;
     const float *Tp = Tp_base + (long long)blockIdx.x * strideTp;
     float *T = Tbase + (long long)blockIdx.x * strideT;
-    const int tid = threadIdx.x;
-    for (int i = tid; i < wo * wo; i += blockDim.x) Ts[i / wo][i % wo] = 0.0f;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // warp ty works on rows ty, ty+32, ..; lane = column
+    for (int i = ty; i < wo; i += 32)
+        for (int j = tx; j < wo; j += 32) Ts[i][j] = 0.0f;
     __syncthreads();
     for (int c = 0, k = 0; c < wo; c += kPanel, ++k) {
         const int w = min(kPanel, wo - c);
-        for (int i = tid; i < kPanel * kPanel; i += blockDim.x) {
-            const int a = i / kPanel, b = i % kPanel;
-            Tk[a][b] = (a < w && b < w) ? Tp[(long long)k * kPanel * kPanel + i] : 0.0f;
-        }
+        Tk[ty][tx] = (ty < w && tx < w) ? Tp[(long long)k * kPanel * kPanel + ty * kPanel + tx] : 0.0f;
         __syncthreads();
-        for (int i = tid; i < w * w; i += blockDim.x) Ts[c + i / w][c + i % w] = Tk[i / w][i % w];
+        if (ty < w && tx < w) Ts[c + ty][c + tx] = Tk[ty][tx];
         if (c > 0) {
-            for (int e = tid; e < c * w; e += blockDim.x) {                 // M1 = T[:c, :c] G[:c, c:c+w]
-                const int i = e / w, j = e % w;
+            for (int i = ty; i < c; i += 32) {                   // M1 = T[:c, :c] G[:c, c:c+w]; T is upper triangular
                 float acc = 0.0f;
-                for (int l = i; l < c; ++l) acc = fmaf(Ts[i][l], G[(long long)l * ldg + c + j], acc);   // T is upper triangular
-                M1[i][j] = acc;
+                if (tx < w)
+                    for (int l = i; l < c; ++l) acc = fmaf(Ts[i][l], __ldg(G + (long long)l * ldg + c + tx), acc);
+                M1[i][tx] = acc;
             }
             __syncthreads();
-            for (int e = tid; e < c * w; e += blockDim.x) {                 // T[:c, c:c+w] = -M1 T_k
-                const int i = e / w, j = e % w;
+            for (int i = ty; i < c; i += 32) {                   // T[:c, c:c+w] = -M1 T_k; T_k is upper triangular
                 float acc = 0.0f;
-                for (int l = 0; l <= j; ++l) acc = fmaf(M1[i][l], Tk[l][j], acc);                      // T_k is upper triangular
-                Ts[i][c + j] = -acc;
+                for (int l = 0; l <= tx; ++l) acc = fmaf(M1[i][l], Tk[l][tx], acc);
+                if (tx < w) Ts[i][c + tx] = -acc;
             }
         }
         __syncthreads();
     }
-    for (int i = tid; i < wo * wo; i += blockDim.x) T[i] = Ts[i / wo][i % wo];
+    for (int i = ty; i < wo; i += 32)
+        for (int j = tx; j < wo; j += 32) T[(long long)i * wo + j] = Ts[i][j];
 }
 
 int launch_merge_t(const float *G, long long ldg, long long strideG, const float *Tp, long long strideTp, int wo, int count,
@@ -237,7 +235,7 @@ int launch_merge_t(const float *G, long long ldg, long long strideG, const float
             return record(QT_ERR_LAUNCH);
         attr_set = true;
     }
-    k_merge_t<<<count, 256, smem, s>>>(G, ldg, strideG, Tp, strideTp, wo, T, strideT);
+    k_merge_t<<<count, 1024, smem, s>>>(G, ldg, strideG, Tp, strideTp, wo, T, strideT);
     count_launch(1);
     return check_launch();
 }
