@@ -98,11 +98,9 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
             const float alpha = __shfl_sync(0xffffffffu, col[0], c);      // row c lives in lane c, slot 0
             float tc = 0.0f, scale = 0.0f;
             if (sigma != 0.0f) {
-                // correctly rounded square root and two independent reciprocals instead of two IEEE
-                // division sequences (measured neutral: a column step is bound by shared-memory reads of v)
-                const float beta = -copysignf(__fsqrt_rn(fmaf(alpha, alpha, sigma)), alpha);
-                tc = (beta - alpha) * __frcp_rn(beta);
-                scale = __frcp_rn(alpha - beta);
+                const float beta = -copysignf(sqrtf(fmaf(alpha, alpha, sigma)), alpha);
+                tc = (beta - alpha) / beta;
+                scale = 1.0f / (alpha - beta);
             }
 #pragma unroll
             for (int k = 0; k < RT; ++k) {
