@@ -220,3 +220,46 @@ def test_fused_adamw_tail_matches_foreach_tail(native_lib):
         for k in ('exp_avg', 'exp_avg_sq'):
             x, y = opts[0].state[oa][k], opts[1].state[ob][k]
             assert float((x - y).norm() / x.norm().clamp_min(1e-30)) < 2e-6
+
+
+def test_adamw_tail_entry_point_handles_unaligned_and_ragged_tensors(native_lib):
+    """qt_adamw_tail through the C ABI on tensors that are not 16-byte aligned and whose sizes are
+    not multiples of the chunk or of four, against the same arithmetic in torch."""
+    import ctypes as ct
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(21)
+    sizes = [8192 * 2 + 5, 3, 8192, 4099]
+    store = [torch.randn(4, n + 1, device=dev, generator=g) for n in sizes]
+    # tensors 0 and 3 start one float into their storage: 4-byte aligned only
+    views = [[s[k, (1 if i in (0, 3) else 0):][:n] for k in range(4)] for i, (s, n) in enumerate(zip(store, sizes))]
+    for p, d, m, v in views:
+        v.abs_()
+    beta1, beta2, eps, lr, wd, step = 0.9, 0.999, 1e-8, 1e-2, 0.1, 3
+    c0, c1, c2 = 1 / (1 - beta2 ** step) ** 0.5, -lr / (1 - beta1 ** step), 1 - lr * wd
+    want = []
+    for p, d, m, v in views:
+        m2 = m * beta1 + (1 - beta1) * d
+        v2 = v * beta2 + (1 - beta2) * d * d
+        want.append((p * c2 + c1 * (m2 / (v2.sqrt() * c0 + eps)), m2, v2))
+    chunk = 8192
+    ct_, ci_ = [], []
+    for t, n in enumerate(sizes):
+        for c in range((n + chunk - 1) // chunk):
+            ct_.append(t)
+            ci_.append(c)
+    i64 = lambda xs: torch.tensor(xs, dtype=torch.int64, device=dev)
+    tabs = [i64([vw[k].data_ptr() for vw in views]) for k in range(4)]
+    numels, tct, tci = i64(sizes), torch.tensor(ct_, dtype=torch.int32, device=dev), torch.tensor(ci_, dtype=torch.int32, device=dev)
+    scal = torch.tensor([c0, c1, c2], dtype=torch.float32, device=dev)
+    vp = lambda t: ct.c_void_p(t.data_ptr())
+    rc = native_lib.qt_adamw_tail(vp(tabs[0]), vp(tabs[1]), vp(tabs[2]), vp(tabs[3]), vp(numels), vp(tct), vp(tci), len(ct_), chunk,
+                                  vp(scal), beta1, beta2, 1 - beta1, 1 - beta2, eps,
+                                  ct.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    for (p, d, m, v), (wp, wm, wv) in zip(views, want):
+        for got, ref in ((p, wp), (m, wm), (v, wv)):
+            assert float((got - ref).norm() / ref.norm()) < 1e-6
+    # a chunk size that is not a multiple of four is refused, nothing is launched
+    assert native_lib.qt_adamw_tail(vp(tabs[0]), vp(tabs[1]), vp(tabs[2]), vp(tabs[3]), vp(numels), vp(tct), vp(tci), len(ct_), 6,
+                                    vp(scal), beta1, beta2, 1 - beta1, 1 - beta2, eps, None) != 0
