@@ -318,6 +318,16 @@ int qt_adamw_tail(const long long *p_ptrs, const long long *d_ptrs, const long l
  * clear != 0 resets it.  Additive; the reference has no device-side waits. */
 int qt_device_error(int clear);
 
+/*
+ * Self-test of the bounded device-side waits: launches one CTA that waits, with the product
+ * kernels' own wait routine, on an mbarrier that nothing arrives at.  The wait gives up after
+ * its poll limit (well under a second), writes 1 to *gave_up (device int, may be NULL) and sets
+ * the sticky error word to QT_ERR_TIMEOUT; the kernel returns normally and the context stays
+ * usable.  Additive; the reference has no device-side waits (its only failure path is
+ * exit(1), cudaC_python/csrc/ops.cuh:20-26).
+ */
+int qt_selftest_wait_timeout(int *gave_up, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

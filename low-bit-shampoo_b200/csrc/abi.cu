@@ -19,6 +19,24 @@ int check_launch() {
     return record(e == cudaSuccess ? QT_OK : QT_ERR_LAUNCH);
 }
 
+int current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return -1; }
+    return dev;
+}
+int device_sm_count() {
+    static std::atomic<int> cache[kMaxDevices];
+    const int dev = current_device();
+    if (dev >= 0 && dev < kMaxDevices) {
+        const int c = cache[dev].load(std::memory_order_relaxed);
+        if (c > 0) return c;
+    }
+    int n = 0;
+    if (dev < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (dev >= 0 && dev < kMaxDevices) cache[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
+
 static void legacy_quantize(const void *A, int dtype, const float *code, int order, float *absmax, float *diag,
                             unsigned char *out, int blocksize, int bits, bool diagreal) {
     if (diagreal && !diag) { record(QT_ERR_ARG); return; }

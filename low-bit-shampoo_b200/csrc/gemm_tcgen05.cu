@@ -33,7 +33,6 @@ static constexpr int RING_BYTES = 12 * PLANE_TILE_BYTES;             // 3 stages
                                                                      // or 2 stages x 6 tiles (three planes)
 static constexpr int GEMM_THREADS = 192;
 static constexpr int GEMM_SMEM = RING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-static int g_gemm_sms = 0;
 static constexpr unsigned WAIT_LIMIT = 1u << 18;
 
 __device__ int g_gemm_error = 0;
@@ -993,8 +992,9 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
          {k_gemm_bf16x3<true, false, 2, true>, k_gemm_bf16x3<true, true, 2, true>}},
         {{k_gemm_bf16x3<false, false, 3, true>, k_gemm_bf16x3<false, true, 3, true>},
          {k_gemm_bf16x3<true, false, 3, true>, k_gemm_bf16x3<true, true, 3, true>}}};
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_done;                      // function attributes are per device
+    const int dev = current_device();
+    if (attr_done.pending(dev)) {
         for (int i = 0; i < 8; ++i)
             if (cudaFuncSetAttribute(reinterpret_cast<const void *>(kernels[i >> 2][(i >> 1) & 1][i & 1]),
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
@@ -1003,15 +1003,10 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
             if (cudaFuncSetAttribute(reinterpret_cast<const void *>(qkernels[i >> 2][(i >> 1) & 1][i & 1]),
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
                 return record(QT_ERR_LAUNCH);
-        attr_done = true;
+        attr_done.mark(dev);
     }
-    if (g_gemm_sms == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        g_gemm_sms = n;
-    }
-    const unsigned grid = (unsigned)(ctas < g_gemm_sms ? ctas : g_gemm_sms);     // persistent: one CTA per SM
+    const int sms = device_sm_count();
+    const unsigned grid = (unsigned)(ctas < sms ? ctas : sms);                   // persistent: one CTA per SM
     if (qs) qkernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
     else kernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
     count_launch(1);
@@ -1024,11 +1019,16 @@ int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) { return launch_gemm_p
 // (global memory owned by the caller), then multiplied on the tensor cores.
 static inline long long pitch8(long long cols) { return (cols + 7) / 8 * 8; }
 
+// Bytes of plane scratch for one product; SIZE_MAX for negative or absurd sizes, so that a
+// comparison against any real buffer size fails instead of wrapping around.
 size_t matmul_f32_scratch_bytes(int M, int N, int K, int batch, int trans_a, int trans_b) {
-    const long long a_rows = trans_a ? K : M, a_cols = trans_a ? M : K;
-    const long long b_rows = trans_b ? N : K, b_cols = trans_b ? K : N;
-    const long long elems = (long long)batch * (a_rows * pitch8(a_cols) + b_rows * pitch8(b_cols));
-    return (size_t)elems * 2 /*planes*/ * 2 /*bytes*/ + 64;
+    if (M < 0 || N < 0 || K < 0 || batch < 0) return SIZE_MAX;
+    const unsigned __int128 a_rows = trans_a ? K : M, a_cols = trans_a ? M : K;
+    const unsigned __int128 b_rows = trans_b ? N : K, b_cols = trans_b ? K : N;
+    const unsigned __int128 elems = (unsigned __int128)batch * (a_rows * pitch8((long long)a_cols) + b_rows * pitch8((long long)b_cols));
+    const unsigned __int128 bytes = elems * 2 /*planes*/ * 2 /*bytes*/ + 64;
+    if (bytes > (unsigned __int128)1 << 46) return SIZE_MAX;             // 64 TiB: beyond any device
+    return (size_t)bytes;
 }
 
 struct MatmulF32Args {
@@ -1073,7 +1073,6 @@ int launch_matmul_f32(const MatmulF32Args &a, void *scratch, size_t scratch_byte
 static constexpr size_t kStaticScratchBytes = (size_t)QT_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-static constexpr int kMaxDevices = 64;
 static void *g_static_scratch_addr[kMaxDevices] = {nullptr};
 
 // Device address of g_static_scratch on the CURRENT device.  In host code the array's name is
@@ -1106,6 +1105,28 @@ int launch_matmul_f32_static(const MatmulF32Args &a, cudaStream_t s) {
     // element the product reads (TMA never reads the pitch padding), so stale contents of an
     // earlier call are harmless.
     return launch_matmul_f32(a, scratch, kStaticScratchBytes, s);
+}
+
+// Self-test of the bounded waits: one CTA initialises an mbarrier that nothing ever arrives at
+// and waits on it with the product kernel's own wait routine.  The wait must give up after
+// WAIT_LIMIT polls, raise the CTA's abort flag and record QT_ERR_TIMEOUT in the device error
+// word; the kernel then returns normally, so the context stays usable.
+__global__ void k_selftest_wait_timeout(int *gave_up) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag);
+        if (gave_up) *gave_up = ok ? 0 : 1;
+    }
+}
+
+int launch_selftest_wait_timeout(int *gave_up_dev, cudaStream_t s) {
+    k_selftest_wait_timeout<<<1, 32, 0, s>>>(gave_up_dev);
+    count_launch(1);
+    return check_launch();
 }
 
 int read_gemm_error(bool clear) {
@@ -1214,5 +1235,9 @@ int qt_matmul_f32_static(const float *A, long long lda, long long strideA, int t
 }
 
 int qt_device_error(int clear) { return read_gemm_error(clear != 0); }
+
+int qt_selftest_wait_timeout(int *gave_up, void *stream) {
+    return launch_selftest_wait_timeout(gave_up, static_cast<cudaStream_t>(stream));
+}
 
 }  // extern "C"

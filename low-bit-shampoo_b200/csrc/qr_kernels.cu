@@ -148,11 +148,12 @@ static int launch_panel_rpl(const float *A, long long strideA, int n, int count,
                             float *V, long long strideV, float *T, long long strideT, cudaStream_t s) {
     const int m = n - j0;
     const size_t smem = sizeof(float) * ((size_t)((m * 33 + 31) & ~31) + 2 * (RPL + RS) * 32 + 2 * kPanel * (kPanel + 1) + kPanel);
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_set;                         // function attributes are per device
+    const int dev = current_device();
+    if (attr_set.pending(dev)) {
         if (cudaFuncSetAttribute(k_householder_panel<RPL, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
             return record(QT_ERR_LAUNCH);
-        attr_set = true;
+        attr_set.mark(dev);
     }
     if (smem > 227 * 1024) return record(QT_ERR_UNSUPPORTED);
     k_householder_panel<RPL, RS><<<count, kQrThreads, smem, s>>>(A, strideA, n, j0, w, V, strideV, T, strideT);
@@ -229,11 +230,12 @@ int launch_merge_t(const float *G, long long ldg, long long strideG, const float
     if (!G || !Tp || !T) return record(QT_ERR_ARG);
     if (count == 0) return record(QT_OK);
     constexpr size_t smem = sizeof(float) * (kMergeMax * (kMergeMax + 1) + 96 * (kPanel + 1) + kPanel * (kPanel + 1));
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_set;
+    const int dev = current_device();
+    if (attr_set.pending(dev)) {
         if (cudaFuncSetAttribute(k_merge_t, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return record(QT_ERR_LAUNCH);
-        attr_set = true;
+        attr_set.mark(dev);
     }
     k_merge_t<<<count, 1024, smem, s>>>(G, ldg, strideG, Tp, strideTp, wo, T, strideT);
     count_launch(1);

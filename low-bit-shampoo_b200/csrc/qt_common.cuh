@@ -15,6 +15,19 @@ int record(int status);          // stores status as this thread's last error an
 void count_launch(int n);        // adds n to the process-wide kernel launch counter
 int check_launch();              // cudaGetLastError -> QT_OK / QT_ERR_LAUNCH (recorded)
 
+// Per-device bookkeeping: function attributes (cudaFuncSetAttribute) and the SM count belong to
+// one device, and a process may drive several.  Ordinals at or above kMaxDevices are refused.
+static constexpr int kMaxDevices = 64;
+int current_device();            // ordinal of the calling thread's current device, or -1
+int device_sm_count();           // SM count of the current device (cached per device; 148 if unknown)
+// One flag per device.  pending() is true until mark() has been called for that device; a
+// race between two first callers only repeats an idempotent set-up.
+struct PerDeviceOnce {
+    volatile unsigned char done[kMaxDevices];
+    bool pending(int dev) const { return dev < 0 || dev >= kMaxDevices || !done[dev]; }
+    void mark(int dev) { if (dev >= 0 && dev < kMaxDevices) done[dev] = 1; }
+};
+
 inline bool valid_blocksize(int bs) {
     return bs == 64 || bs == 128 || bs == 256 || bs == 512 || bs == 1024 || bs == 2048;
 }

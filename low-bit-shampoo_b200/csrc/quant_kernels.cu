@@ -596,16 +596,7 @@ int launch_selftest_division(unsigned long long seed, unsigned long long pairs, 
 // ------------------------------------------------------------------------------------
 // Host launchers.
 // ------------------------------------------------------------------------------------
-static int g_sm_count = 0;
-static int sm_count() {
-    if (g_sm_count == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        g_sm_count = n;
-    }
-    return g_sm_count;
-}
+static int sm_count() { return device_sm_count(); }
 
 static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

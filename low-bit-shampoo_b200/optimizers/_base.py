@@ -24,6 +24,33 @@ FUSED_TAIL = True              # AdamW tail as one multi-tensor launch of the li
 CODE = 'linear-2'
 
 
+def cut(d, block_size):
+    """Chunk lengths of one dimension of length d: chunks of `block_size` plus a remainder
+    (shampoo2.py:50-61); a dimension that fits is left whole."""
+    if block_size > 0 and d > block_size:
+        full, rest = divmod(d, block_size)
+        return [block_size] * full + ([rest] if rest else [])
+    return [d]
+
+
+def matrix_shape(shape):
+    """(rows, cols) a parameter is reshaped to (shampoo2.py:115-121), or None when it has fewer
+    than two non-unit dimensions (no preconditioner)."""
+    dims = [d for d in shape if d != 1]
+    if len(dims) < 2:
+        return None
+    return dims[0], math.prod(dims[1:])
+
+
+def block_shapes(shape, prec_maxorder):
+    """(rows, cols) of the gradient blocks of a parameter, in partition() order.  Pure shape
+    arithmetic: the owner map of the sharded optimizer and the optimizer itself both use it."""
+    ms = matrix_shape(tuple(shape))
+    if ms is None:
+        return []
+    return list(itertools.product(cut(ms[0], prec_maxorder), cut(ms[1], prec_maxorder)))
+
+
 class BlockPartitioner:
     """Splits every dimension longer than `block_size` into chunks of `block_size` plus a
     remainder; a tensor becomes the row-major grid of those blocks."""
@@ -34,14 +61,11 @@ class BlockPartitioner:
         self._splits = []                  # (dim, interior cut positions) for split dimensions
         self._split_sizes = []
         for dim, d in enumerate(var.shape):
-            if block_size > 0 and d > block_size:
-                full, rest = divmod(d, block_size)
-                sizes = [block_size] * full + ([rest] if rest else [])
-                self._cuts.append(sizes)
+            sizes = cut(d, block_size)
+            self._cuts.append(sizes)
+            if len(sizes) > 1:
                 self._splits.append((dim, list(itertools.accumulate(sizes))[:-1]))
                 self._split_sizes.append((dim, sizes))
-            else:
-                self._cuts.append([d])
         self._num_splits = len(self._cuts)
         self._preconditioner_shapes = []
         for combo in itertools.product(*self._cuts):
@@ -83,13 +107,7 @@ def _transformed_shape(shape):
 
 def preconditioner_orders(shape, prec_maxorder):
     """Orders of the preconditioner matrices a parameter of `shape` gets (block-major, axis-minor)."""
-    ts = _transformed_shape(shape)
-    if len(ts) <= 1:
-        return []
-    numel = math.prod(shape)
-    rows = ts[0]
-    probe = torch.empty((rows, numel // rows), device="meta")
-    return [s[0] for s in BlockPartitioner(probe, prec_maxorder).shapes_for_preconditioners()]
+    return [n for blk in block_shapes(shape, prec_maxorder) for n in blk]
 
 
 class Preconditioner:
@@ -143,9 +161,27 @@ class Preconditioner:
             self.preconditioners.append(QTensorDiagReal(eye, storage=cls.prec.storage(slot), **common))
 
     def set_device(self, device):
+        """Re-homes the per-matrix holders (reference: shampoo2.py:311-317).  The arenas the batched
+        engine works on are re-created on the parameter's device by the optimizer's
+        load_state_dict (adopt()), so nothing here has to move them."""
         for s, p in zip(self.statistics, self.preconditioners):
             s.set_device(device)
             p.set_device(device)
+
+    def adopt(self, old):
+        """Takes over the schedule flag and the contents of every state slot of `old` (a
+        preconditioner restored from a checkpoint, on any device), slot by slot, into this
+        object's own arenas."""
+        self._active = bool(old.is_active())
+        if not self._slots:
+            return
+        if isinstance(old, RemotePreconditioner) or len(old._slots) != len(self._slots):
+            raise RuntimeError(
+                f"the checkpoint holds no preconditioner state for a parameter of shape {tuple(self._original_shape)} "
+                "that this rank owns: every rank must load the state it saved itself, or a checkpoint merged with "
+                "optimizers._sharding.consolidate_state_dicts()")
+        for (cn, sn), (co, so) in zip(self._slots, old._slots):
+            cn.copy_slot_from(co, sn, so)
 
     # -- work lists consumed by the batched engine -------------------------------------
     def _grad_blocks(self, grad):
@@ -241,17 +277,68 @@ class _ShampooBase(optim.Optimizer):
             self._world = dist.get_world_size(process_group)
             self._rank = dist.get_rank(process_group)
 
-    def load_state_dict(self, state_dict):
-        super().load_state_dict(state_dict)
-        for group in self.param_groups:
-            for p in group['params']:
-                state = self.state[p]
-                if len(state) != 0:
-                    state['preconditioner'].set_device(p.device)
+    # ---- checkpoint -----------------------------------------------------------------------
+    # The reference pickles its Preconditioner objects inside optimizer.state_dict()
+    # (train_cifar.py:446-460) and re-homes them in load_state_dict (shampoo2.py:311-317,
+    # :403-409).  Same here, plus a tag: which rank of how many wrote the state (a sharded
+    # optimizer holds real state only for the parameters it owns) and the byte format of the
+    # packed codes (the reference's CPU and CUDA quantizers disagree on nibble order and on the
+    # code of an all-zero block; this library writes the CPU quantizer's format).
+    BYTE_FORMAT = {"nibble_order": "element 2j in the high nibble of byte j", "zero_block_code": 0,
+                   "normalisation": "ieee division", "ties": "lower code"}
 
-    def _create_states(self, group, params):
-        """One arena per preconditioner order for all new parameters of the group."""
-        new = [p for p in params if len(self.state[p]) == 0]
+    def _check_device_error(self):
+        """Raises if a bounded wait inside one of the library's kernels ran out since the last
+        check (its results are then garbage).  Synchronises; called where the caller does anyway."""
+        lib = F.lib
+        if lib is None:
+            return
+        devs = {p.device for g in self.param_groups for p in g['params'] if p.device.type == "cuda"}
+        for dev in devs:
+            with torch.cuda.device(dev):
+                rc = lib.qt_device_error(1)
+            if rc != 0:
+                raise RuntimeError(f"a device-side wait of libqtensor_b200 timed out on {dev} (status {rc}): "
+                                   "optimizer state written since the previous check is not valid")
+
+    def state_dict(self):
+        self._check_device_error()
+        sd = super().state_dict()
+        sd["shampoo_shard"] = {"format": 2, "rank": self._rank, "world": self._world,
+                               "byte_format": dict(self.BYTE_FORMAT)}
+        return sd
+
+    def load_state_dict(self, state_dict):
+        state_dict = dict(state_dict)
+        shard = state_dict.pop("shampoo_shard", None)
+        if shard is not None:
+            if shard.get("byte_format", self.BYTE_FORMAT) != self.BYTE_FORMAT:
+                raise RuntimeError(f"checkpoint uses another packed-code format: {shard['byte_format']}")
+            if shard["world"] != 1 and (shard["world"], shard["rank"]) != (self._world, self._rank):
+                raise RuntimeError(
+                    f"checkpoint was written by rank {shard['rank']} of {shard['world']}, this is rank {self._rank} of "
+                    f"{self._world}: load each rank's own file, or merge the files with "
+                    "optimizers._sharding.consolidate_state_dicts() first")
+        super().load_state_dict(state_dict)
+        # captured graphs, pointer tables and exchange plans refer to the state that was just replaced
+        self._graph_state = None
+        self._plans = {}
+        for name in ("_tail_cache", "_scalar_ring", "_tail_scalars", "_pending_exchange"):
+            self.__dict__.pop(name, None)
+        self._needs_eager = True                           # the next step rebuilds them eagerly
+        for group in self.param_groups:
+            loaded = [p for p in group['params'] if len(self.state[p]) != 0]
+            if loaded:
+                self._create_states(group, loaded, adopt=True)
+                for p in loaded:
+                    self.state[p]['preconditioner'].set_device(p.device)
+
+    def _create_states(self, group, params, adopt=False):
+        """One arena per preconditioner order for all new parameters of the group.  With `adopt`
+        the parameters already carry state restored from a checkpoint: ownership is recomputed
+        for the current world, arenas are created on each parameter's device, and the restored
+        slots are copied in (the restored objects themselves are dropped)."""
+        new = [p for p in params if adopt or len(self.state[p]) == 0]
         if not new:
             return
         flavour = self.preconditioner_cls.flavour
@@ -277,19 +364,28 @@ class _ShampooBase(optim.Optimizer):
                 group.get('rect_t1', 1), group.get('rect_t2', 4))
         for p, owner in zip(new, owners):
             state = self.state[p]
-            state['step'] = 0
+            old = state.get('preconditioner') if adopt else None
+            if not adopt:
+                state['step'] = 0
             state['owner'] = owner
             if owner not in (-1, self._rank):
                 state['preconditioner'] = RemotePreconditioner(owner)
-                self._init_moments(p, state)
+                if old is not None:
+                    state['preconditioner']._active = bool(old.is_active())
+                else:
+                    self._init_moments(p, state)
                 continue
-            state['preconditioner'] = self.preconditioner_cls(
+            pre = self.preconditioner_cls(
                 p, self.name2qmap,
                 stat_decay=group['stat_decay'], matrix_eps=group['matrix_eps'], prec_maxorder=group['prec_maxorder'],
                 prec_bits=bits, min_lowbit_size=group['min_lowbit_size'], quan_blocksize=group['quan_blocksize'],
                 rect_t1=group.get('rect_t1', 1), rect_t2=group.get('rect_t2', 4),
                 inv_root_mode=group.get('inv_root_mode', 0), classes=classes.get(p.device))
-            self._init_moments(p, state)
+            if old is not None:
+                pre.adopt(old)
+            else:
+                self._init_moments(p, state)
+            state['preconditioner'] = pre
 
     def _precondition(self, group, params, split_exchange=False):
         """Runs the statistics / inverse-root / apply phases for `params` (all with grads) and
@@ -394,6 +490,7 @@ class _ShampooBase(optim.Optimizer):
         E.SPLIT_CLASSES = split_before or self._use_graph
         try:
             self._step_groups()
+            self._needs_eager = False
         finally:
             E.SPLIT_CLASSES = split_before
 
@@ -405,7 +502,7 @@ class _ShampooBase(optim.Optimizer):
                     raise RuntimeError('Shampoo does not support sparse yet')
             if not params:
                 continue
-            fresh = any(len(self.state[p]) == 0 for p in params)
+            fresh = any(len(self.state[p]) == 0 for p in params) or self.__dict__.get("_needs_eager", False)
             self._create_states(group, params)
             if self._use_graph and not fresh and self._graph_eligible(group, params):
                 self._graph_step(group, params)

@@ -77,6 +77,19 @@ class QuantArena:
             st["diag"] = self.diag[i]
         return st
 
+    def copy_slot_from(self, other, dst, src):
+        """Slot `dst` of this arena <- slot `src` of `other` (same order and format; any device)."""
+        same = (self.n == other.n and self.lowbit == other.lowbit and self.bits == other.bits
+                and self.diagreal == other.diagreal and (not self.lowbit or self.blocksize == other.blocksize))
+        if not same:
+            raise RuntimeError(f"quantized state of order {other.n} ({other.bits}-bit, block {other.blocksize}) cannot be "
+                               f"loaded into state of order {self.n} ({self.bits}-bit, block {self.blocksize})")
+        self.var[dst].copy_(other.var[src])
+        if self.lowbit:
+            self.absmax[dst].copy_(other.absmax[src])
+            if self.diagreal:
+                self.diag[dst].copy_(other.diag[src])
+
     def fusable(self):
         """True if a GEMM epilogue can read / write this arena's state directly
         (qt_gemm_bf16x3_q4 / x6_q4: 4-bit, block 64, order a multiple of 16, CUDA)."""
@@ -163,6 +176,17 @@ class OrderClass:
 
     def sub_batch(self):
         return max(1, _TEMP_ELEMS // (self.n * self.n))
+
+    def copy_slot_from(self, other, dst, src):
+        """Everything slot `src` of `other` holds (statistic, spectrum, preconditioner) into slot `dst`."""
+        if self.flavour != other.flavour:
+            raise RuntimeError(f"checkpoint holds '{other.flavour}' statistics, this optimizer keeps '{self.flavour}'")
+        self.stat.copy_slot_from(other.stat, dst, src)
+        self.prec.copy_slot_from(other.prec, dst, src)
+        if self.flavour == "s2":
+            self.S[dst].copy_(other.S[src])
+            self.keep_idx[dst].copy_(other.keep_idx[src])
+            self.max_eig[dst].copy_(other.max_eig[src])
 
 
 # ---------------------------------------------------------------------------------------

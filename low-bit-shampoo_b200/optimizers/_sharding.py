@@ -10,7 +10,7 @@ No other collective is used; gradients are assumed to be already averaged (data 
 """
 import torch
 
-from optimizers._base_shapes import block_shapes
+from optimizers._base import block_shapes
 
 
 def param_cost(shape, prec_maxorder):
@@ -92,3 +92,35 @@ class GatherPlan:
         self.pack(local, rank, device, dtype)
         self.collective(group, device, dtype)
         return self.views(device, dtype)
+
+
+def consolidate_state_dicts(shards):
+    """Merges the state dicts the ranks of one sharded run saved (optimizer.state_dict() on every
+    rank, any order) into one that an optimizer of ANY world size can load: for every parameter
+    the entry of the rank that owned it - the only one with real preconditioner state - is kept;
+    moments and step counters are replicated, so any rank's copy serves.  The result is tagged
+    as a single-process checkpoint; load_state_dict() then re-shards it for the current world."""
+    shards = list(shards)
+    tags = [sd.get("shampoo_shard") for sd in shards]
+    if any(t is None for t in tags):
+        raise ValueError("not a Shampoo state dict of this package (no 'shampoo_shard' tag)")
+    world = tags[0]["world"]
+    if sorted(t["rank"] for t in tags) != list(range(world)) or any(t["world"] != world for t in tags):
+        raise ValueError(f"need the state dicts of all {world} ranks of one run, got ranks "
+                         f"{sorted(t['rank'] for t in tags)} of worlds {sorted({t['world'] for t in tags})}")
+    if any(t["byte_format"] != tags[0]["byte_format"] for t in tags):
+        raise ValueError("the shards use different packed-code formats")
+    by_rank = {t["rank"]: sd for t, sd in zip(tags, shards)}
+    base = by_rank[0]
+    state = {}
+    for idx, entry in base["state"].items():
+        owner = entry.get("owner", -1)
+        src = by_rank[owner]["state"][idx] if owner >= 0 else entry
+        merged = dict(src)
+        merged["owner"] = 0 if owner >= 0 else -1
+        state[idx] = merged
+    out = {k: v for k, v in base.items() if k not in ("state", "shampoo_shard")}
+    out["state"] = state
+    out["shampoo_shard"] = {"format": tags[0]["format"], "rank": 0, "world": 1, "byte_format": dict(tags[0]["byte_format"]),
+                            "consolidated_from": world}
+    return out

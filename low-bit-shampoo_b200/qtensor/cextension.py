@@ -21,7 +21,7 @@ LEGACY_SYMBOLS = tuple(
 )
 EXTRA_SYMBOLS = (
     "qt_version", "qt_launch_count", "qt_note_graph_replay", "qt_last_error", "qt_error_string", "qt_set_stream",
-    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_dequantize_planes", "qt_householder_panel", "qt_merge_t", "qt_selftest_division", "qt_split_bf16", "qt_split_bf16_rows", "qt_gemm_bf16x3", "qt_split_bf16_3", "qt_gemm_bf16x6", "qt_gemm_bf16x3_q4", "qt_gemm_bf16x6_q4", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error", "qt_adamw_tail",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_dequantize_planes", "qt_householder_panel", "qt_merge_t", "qt_selftest_division", "qt_split_bf16", "qt_split_bf16_rows", "qt_gemm_bf16x3", "qt_split_bf16_3", "qt_gemm_bf16x6", "qt_gemm_bf16x3_q4", "qt_gemm_bf16x6_q4", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error", "qt_adamw_tail", "qt_selftest_wait_timeout",
 )
 
 _lib = None
@@ -85,6 +85,8 @@ def _declare(lib):
                                          vp, i64, i64, vp, i64, i64, vp]
     lib.qt_device_error.restype = i32
     lib.qt_device_error.argtypes = [i32]
+    lib.qt_selftest_wait_timeout.restype = i32
+    lib.qt_selftest_wait_timeout.argtypes = [vp, vp]
     for name in LEGACY_SYMBOLS:
         getattr(lib, name).restype = None
     return lib

@@ -44,7 +44,7 @@ def test_static_scratch_matches_caller_scratch_twice(native_lib):
         torch.cuda.synchronize()
         assert lib.qt_device_error(1) == 0
         assert torch.isfinite(got).all()
-        assert rel(got, want) < TOL
+        assert torch.equal(got, want)                      # same kernels on the same planes: bit-identical
         ref = alpha * ((A.transpose(1, 2) if ta else A).double() @ (B.transpose(1, 2) if tb else B).double()) + beta * C.double()
         assert rel(got, ref) < TOL
 
@@ -58,3 +58,9 @@ def test_static_scratch_rejects_oversized_request(native_lib):
                                   None, 0, 0, one, 2048, 0, None)
     assert rc == 8
     assert b"16 MiB" in lib.qt_error_string(rc)
+    # sizes whose byte count would wrap around 2^64 are refused as well, not taken for small ones
+    big = 1 << 30
+    assert lib.qt_matmul_f32_scratch_bytes(big, big, big, 2, 0, 0) == 2 ** 64 - 1
+    rc = lib.qt_matmul_f32_static(one, big, 0, 0, one, big, 0, 0, big, big, big, 2, 1.0, 0.0,
+                                  None, 0, 0, one, big, 0, None)
+    assert rc == 8
