@@ -5,9 +5,12 @@ AdamW tail), plus the blockwise quantize / dequantize rate of the same state.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Prints ONE JSON line (rank 0).  `--impl reference` times the CPU oracle port of the same
-step (oracle/shampoo_oracle.py + oracle/qoracle.c) on this machine's host cores, on a
-bounded sample of the workload.  Multi-GPU runs are launched with torch.distributed.run.
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU side on this machine's host
+cores and never imports the CUDA package: the whole ViT-B/32 step on the CPU port of the
+reference's step (oracle/shampoo_oracle.py + oracle/qoracle.c; the reference's own Python
+quantizer needs minutes per step), and the 1024 x 1024 quantize -> dequantize round trip on the
+reference's own pure-PyTorch quantizer when a copy of it is present under oracle/_ref/py.
+Multi-GPU runs are launched with torch.distributed.run.
 """
 import argparse
 import ctypes as ct
@@ -19,8 +22,23 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "low-bit-shampoo_b200")
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "low-bit-shampoo_b200"))
+
+
+def use_package():
+    """Puts the CUDA package on the import path (GPU arm only; the CPU arm must not see it)."""
+    if PKG not in sys.path:
+        sys.path.insert(0, PKG)
+
+
+def load_workloads():
+    """The model definitions (plain torch) loaded from their file, without exposing the package."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_workloads", os.path.join(PKG, "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 METRIC = "shampoo2 4-bit optimizer step ms (ViT-B/32); quant/dequant HBM GB/s"
 HYPER = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.05, start_prec_step=1,
@@ -33,12 +51,46 @@ WORKLOAD = ("vit_base_patch32_224 parameter set (88.2M params, 226 preconditione
 
 
 def measured_peaks():
+    """(HBM GB/s, bf16 TFLOP/s burst, bf16 TFLOP/s sustained, "measured" | "fallback").  The burst
+    figure is the denominator for a kernel timed alone, the sustained one for work timed inside a
+    long step."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
-    return 6650.0, 1590.0, "fallback"
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def ncu_traffic(kernel):
+    """DRAM bytes per launch of `kernel` from the committed capture table (dram__bytes_read.sum +
+    dram__bytes_write.sum of one launch under ncu; a profiler cannot run inside the timed bench)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "roofline_traffic.json")) as f:
+            return float(json.load(f)[kernel]["bytes"])
+    except (OSError, KeyError, ValueError, TypeError):
+        return None
+
+
+def step_algorithmic_flops(shapes, maxorder=1200):
+    """Algorithmic flops of one firing shampoo2 step (mode 0) over `shapes`, counted the way the
+    reference spends them: per preconditioner matrix of order n  4 n^3 (Bjorck step) + 1.5 n^3
+    (V^T diag(S) V) + 2 n^3 (L V^T) + 4 n^3 (V^T L V) + 5.5 n^3 (four Bjorck steps on n/2 rows and the
+    root) = 17 n^3 of products plus 8/3 n^3 for the Householder QR; per gradient block m x k
+    2 (m^2 k + m k^2) for the two Gram matrices and the same for P_L G P_R."""
+    import itertools
+    total = 0.0
+    for s in shapes:
+        dims = [d for d in s if d != 1]
+        if len(dims) < 2:
+            continue
+        rows, cols = dims[0], 1
+        for d in dims[1:]:
+            cols *= d
+        cut = lambda d: [maxorder] * (d // maxorder) + ([d % maxorder] if d % maxorder else []) if d > maxorder else [d]
+        for m, k in itertools.product(cut(rows), cut(cols)):
+            total += (17.0 + 8.0 / 3.0) * (m ** 3 + k ** 3) + 4.0 * (m * m * k + m * k * k)
+    return total
 
 
 class ClockSampler:
@@ -89,67 +141,144 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------
-# CPU arm: the oracle port of the same step on the host cores.
+# CPU arm.  Runs in a process of its own that never imports the CUDA package (only the model
+# definitions of workloads.py, which are plain torch), so no GPU library is mapped into it.
 # ---------------------------------------------------------------------------------------
 
-SAMPLE_LAYERS = 4
+CPU_STEP_BUDGET_S = 200.0       # stop taking timed steps once this much time has been spent stepping
 
 
-def vit_layer_shapes(layers=SAMPLE_LAYERS):
-    d, mlp = 768, 3072
-    one = [(3 * d, d), (3 * d,), (d, d), (d,), (mlp, d), (mlp,), (d, mlp), (d,), (d,), (d,), (d,), (d,)]
-    return one * layers
+def host_threads():
+    """Threads the CPU arm uses: every core this process may run on (torch.distributed.run
+    exports OMP_NUM_THREADS=1, which would otherwise leave one)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, min(n, 64))
 
 
-def sum_cubes(shapes, maxorder=1200):
-    from optimizers._base import preconditioner_orders
-    return sum(n ** 3 for s in shapes for n in preconditioner_orders(tuple(s), maxorder))
-
-
-def cpu_reference_step_ms(steps, warmup):
-    """Oracle port on SAMPLE_LAYERS encoder layers (of 12) scaled to the full model by the
-    sum of n^3 over preconditioner orders."""
-    import torch
-    from oracle.shampoo_oracle import OracleShampoo
-    import workloads
-    shapes = vit_layer_shapes()
-    full = [tuple(p.shape) for p in workloads.vit_base_patch32_224().parameters()]
-    scale = sum_cubes(full) / sum_cubes(shapes)
+def config1_matrix(torch, n=1024):
+    """Q diag(lambda) Q^T, Q from the QR of a seeded N(0,1) matrix, lambda log-uniform in [1e-6, 1]."""
     g = torch.Generator().manual_seed(0)
-    params = [torch.randn(s, generator=g) * 0.02 for s in shapes]
+    q, _ = torch.linalg.qr(torch.randn(n, n, dtype=torch.float64, generator=g))
+    lam = torch.exp(torch.empty(n, dtype=torch.float64).uniform_(-13.815510557964274, 0.0, generator=g))
+    a = (q * lam) @ q.T
+    return (0.5 * (a + a.T)).float().contiguous()
+
+
+def cpu_config1(torch):
+    """The 1024 x 1024 round trip (4-bit, block 64) on the host: the reference's own pure-PyTorch
+    quantizer (qtensor/functional.py:526-688) when oracle/_ref/py holds a copy of it, else the C port."""
+    n, bs = 1024, 64
+    A = config1_matrix(torch, n)
+    nbytes = 4 * n * n + n * n // 2 + 4 * n * (n // bs)
+    refpy = os.path.join(ROOT, "oracle", "_ref", "py")
+    if os.path.isfile(os.path.join(refpy, "qtensor", "functional.py")):
+        sys.path.insert(0, refpy)
+        import qtensor.functional as RF                    # the reference's module (this process has no other qtensor)
+        assert os.path.realpath(RF.__file__).startswith(os.path.realpath(refpy))
+        code = RF.create_linear_map(True, 4, 2)
+        tq, td = [], []
+        for _ in range(2):
+            t0 = time.perf_counter()
+            q, am = RF.quantize_blockwise(A, code, n, blocksize=bs, bits=4)
+            t1 = time.perf_counter()
+            RF.dequantize_blockwise(q, code, n, am, blocksize=bs, bits=4)
+            t2 = time.perf_counter()
+            tq.append(t1 - t0)
+            td.append(t2 - t1)
+        kind = "reference"
+    else:
+        from oracle import qoracle
+        code = qoracle.linear_map(True, 4, 2)
+        a = A.numpy()
+        tq, td = [], []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            q, am = qoracle.quantize(a, code, n, bs, 4)[:2]
+            t1 = time.perf_counter()
+            qoracle.dequantize(q, code, n, am, bs, 4)
+            t2 = time.perf_counter()
+            tq.append(t1 - t0)
+            td.append(t2 - t1)
+        kind = "port"
+    return {"case": "1 x 1024^2 SPD fp32, 4-bit linear-2 code, block 64", "kind": kind, "cores": 1 if kind == "port" else torch.get_num_threads(),
+            "quantize_s": min(tq), "dequantize_s": min(td), "bytes_per_direction": nbytes,
+            "quantize_gbs": nbytes / min(tq) / 1e9, "dequantize_gbs": nbytes / min(td) / 1e9}
+
+
+def cpu_reference_step(steps, warmup):
+    """The full ViT-B/32 step (all 226 preconditioner matrices, every interval firing) on the CPU
+    port, gradients from the same bf16-autocast backward as the GPU arm (seed 0, batch 256)."""
+    import torch
+    torch.set_num_threads(host_threads())
+    from oracle.shampoo_oracle import OracleShampoo
+    workloads = load_workloads()
+    torch.manual_seed(0)
+    model = workloads.vit_base_patch32_224()
+    workloads.synthetic_gradients(model, 256, 224, 1000, "cpu", autocast_bf16=True, seed=0)
+    params = [p.detach().clone() for p in model.parameters()]
+    grads = [p.grad.detach().clone() for p in model.parameters()]
+    del model
     opt = OracleShampoo(params, kind="adamw", flavour="s2", **{
         "lr": HYPER["lr"], "betas": HYPER["betas"], "eps": HYPER["eps"], "weight_decay": HYPER["weight_decay"],
         "stat_compute_steps": 1, "prec_compute_steps": 1, "stat_decay": HYPER["stat_decay"],
         "matrix_eps": HYPER["matrix_eps"], "prec_maxorder": 1200, "prec_bits": 4, "quan_blocksize": 64,
         "rect_t1": 1, "rect_t2": 4, "inv_root_mode": 0})
-    times = []
-    for it in range(warmup + steps):
-        grads = [torch.randn(s, generator=g) * 1e-2 for s in shapes]
+    times, spent = [], 0.0
+    warm = max(1, min(warmup, 2))
+    for it in range(warm + steps):
         t0 = time.perf_counter()
-        opt.step(grads)
+        opt.step([g.clone() for g in grads])
         dt = time.perf_counter() - t0
-        if it >= warmup:
+        if it >= warm:
             times.append(dt)
+            spent += dt
+            if spent > CPU_STEP_BUDGET_S:
+                break
     ms = 1e3 * sum(times) / len(times)
-    sample = (f"{SAMPLE_LAYERS} of 12 ViT-B/32 encoder layers ({len(shapes)} tensors, {18 * SAMPLE_LAYERS} preconditioner matrices), {steps} step(s) after "
-              f"{warmup} warm-up, {ms:.0f} ms per sample step, scaled x{scale:.2f} by sum n^3 to the full model")
-    return ms * scale, torch.get_num_threads(), sample
+    sample = (f"whole workload (all {len(params)} tensors, 226 preconditioner matrices), {len(times)} timed step(s) of {steps} requested "
+              f"after {warm} warm-up, {torch.get_num_threads()} threads; CPU port of the reference's step (torch CPU products and QR, C quantizer)")
+    return ms, torch.get_num_threads(), sample, len(times), warm, torch
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
-    ms, cores, sample = cpu_reference_step_ms(steps, warmup)
+    ms, cores, sample, steps_run, warm_run, torch = cpu_reference_step(args.steps, args.warmup)
+    c1 = cpu_config1(torch)
     line = {"impl": "reference", "metric": METRIC, "value": ms, "unit": "ms/step", "n_gpus": args.gpus,
-            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "steps": steps_run, "warmup": warm_run, "requested": {"steps": args.steps, "warmup": args.warmup},
+            "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 arithmetic on 4-bit state", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in HYPER.items()}},
+            "config": {"workload": WORKLOAD, "gradients": "one bf16-autocast cross-entropy backward on the host, batch 256 of N(0,1) "
+                       "224x224 images, uniform labels, seed 0 (computed once, reused every step)",
+                       "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in HYPER.items()}},
             "cpu_baseline": {"value": ms, "unit": "ms/step", "cores": cores, "kind": "port", "sample": sample},
+            "config1": c1,
             "e2e": {"value": ms, "unit": "ms/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_subprocess(steps=2, warmup=1, timeout=600):
+    """Runs the CPU arm as a separate process (so that the reference's `qtensor` package and this
+    package's never meet) and returns its parsed JSON line, or None."""
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "OMP_NUM_THREADS"):
+        env.pop(k, None)
+    env["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", str(steps),
+                              "--warmup", str(warmup)], capture_output=True, text=True, timeout=timeout, env=env)
+        for ln in reversed(out.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)
+    except (subprocess.SubprocessError, ValueError, OSError):
+        pass
+    return None
 
 
 # ---------------------------------------------------------------------------------------
@@ -243,7 +372,7 @@ def kernel_sweep(torch, device, orders=(128, 512, 1200, 2048, 4096, 8192), count
     import qtensor.functional as F
     from optimizers import _gemm, matrix_functions as MF
     from optimizers import _engine as E
-    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    hbm_peak, tensor_peak, _, peak_kind = measured_peaks()
     code = F.create_linear_map(True, 4, 2).to(device)
     gen = torch.Generator(device=device).manual_seed(0)
     beta = 0.95
@@ -308,10 +437,76 @@ def kernel_sweep(torch, device, orders=(128, 512, 1200, 2048, 4096, 8192), count
                 "algorithmic_bytes": algo_bytes, "gbs": algo_bytes / (t_fused + t_split) / 1e6,
                 "gbs_frac_of_measured_copy": algo_bytes / (t_fused + t_split) / 1e6 / hbm_peak,
                 "tflops_algorithmic": flops / t_fused / 1e9, "tflops_executed": 6 * flops / t_fused / 1e9,
-                "tensor_frac_of_measured_sustained": 6 * flops / t_fused / 1e9 / tensor_peak,
+                "tensor_frac_of_measured_burst": 6 * flops / t_fused / 1e9 / tensor_peak,
                 "peaks": peak_kind, "factor_root_us": t_root * 1e3, "newton_root_us": None if t_newton is None else t_newton * 1e3}
         print(json.dumps(line), flush=True)
         del G, P, arena, out, st
+
+
+def config1_gpu(torch, lib, device):
+    """The 1024 x 1024 configuration on the GPU: one matrix (launch-latency bound: 4.8 MB is under
+    a microsecond of HBM traffic) and a batch of 64 such matrices (306 MB per pass, larger than L2)."""
+    import qtensor.functional as F
+    n, bs = 1024, 64
+    nb = n // bs
+    code = F.create_linear_map(True, 4, 2).to(device)
+    p = lambda t: ct.c_void_p(t.data_ptr())
+    st = ct.c_void_p(torch.cuda.current_stream().cuda_stream)
+    res = {"case": "1024^2 SPD fp32 (Q diag(lambda) Q^T, lambda log-uniform in [1e-6, 1]), 4-bit linear-2 code, block 64"}
+    A1 = config1_matrix(torch, n).to(device)
+    for count, tag in ((1, "single"), (64, "batch64")):
+        A = A1.unsqueeze(0).expand(count, n, n).contiguous()
+        packed = torch.empty(count, n * n // 2, dtype=torch.uint8, device=device)
+        absmax = torch.empty(count, n * nb, device=device)
+        out = torch.empty_like(A)
+        q = lambda: lib.qt_quantize_blockwise(p(A), 0, n * n, p(code), n, count, p(absmax), n * nb, None, 0,
+                                              p(packed), n * n // 2, bs, 4, st)
+        d = lambda: lib.qt_dequantize_blockwise(p(packed), n * n // 2, p(code), n, count, p(absmax), n * nb, None, 0,
+                                                p(out), 0, n * n, bs, 4, st)
+        nbytes = count * (4 * n * n + n * n // 2 + 4 * n * nb)
+        for name, fn in (("quantize", q), ("dequantize", d)):
+            ms = _time_cuda(torch, fn, 3, 50 if count == 1 else 20)
+            res[f"{tag}_{name}_us"] = ms * 1e3
+            res[f"{tag}_{name}_gbs"] = nbytes / ms / 1e6
+    return res
+
+
+def reference_cuda_quantizer(torch, device):
+    """Context figure: the reference's own CUDA quantizer (cudaC_python/csrc, compiled unmodified
+    for sm_100a into oracle/_ref/) on the 125 x 768^2 class, one launch per matrix on the legacy
+    default stream as the reference does.  It writes a different byte format; only its rate is used."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libqtensor_cuda_ref.so")
+    if not os.path.isfile(path):
+        return None
+    try:
+        ref = ct.CDLL(path)
+        import qtensor.functional as F
+        n, count, bs = 768, 125, 64
+        nb = n // bs
+        A = torch.randn(count, n, n, device=device)
+        packed = torch.empty(count, n * n // 2, dtype=torch.uint8, device=device)
+        absmax = torch.empty(count, n * nb, device=device)
+        out = torch.empty_like(A)
+        code = F.create_linear_map(True, 4, 2).to(device)
+        vp = lambda t, off=0: ct.c_void_p(t.data_ptr() + off)
+
+        def q():
+            for m in range(count):
+                ref.cquantize_blockwise_4bit_fp32(vp(A, 4 * m * n * n), vp(code), ct.c_int32(n), vp(absmax, 4 * m * n * nb),
+                                                  vp(packed, m * n * n // 2), ct.c_int32(bs))
+
+        def d():
+            for m in range(count):
+                ref.cdequantize_blockwise_4bit_fp32(vp(packed, m * n * n // 2), vp(code), ct.c_int32(n), vp(absmax, 4 * m * n * nb),
+                                                    vp(out, 4 * m * n * n), ct.c_int32(bs))
+        nbytes = count * (4 * n * n + n * n // 2 + 4 * n * nb)
+        with torch.cuda.stream(torch.cuda.default_stream(device)):
+            tq = _time_cuda(torch, q, 2, 5)
+            td = _time_cuda(torch, d, 2, 5)
+        return {"what": "reference CUDA quantizer compiled for sm_100a, 125 launches per pass (one per matrix)",
+                "quantize_gbs": nbytes / tq / 1e6, "dequantize_gbs": nbytes / td / 1e6}
+    except Exception as exc:                                  # context only: never fail the bench for it
+        return {"unavailable": repr(exc)}
 
 
 def run_ours(args):
@@ -326,11 +521,14 @@ def run_ours(args):
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    use_package()
     import workloads
     from optimizers.shampoo2 import ShampooAdamW
     from qtensor.cextension import get_lib
     lib = get_lib()
 
+    # every rank holds the same model and the same gradients (seed 0 everywhere, as after a
+    # data-parallel all-reduce), so parameters - and the checksum below - do not depend on N
     torch.manual_seed(0)
     model = workloads.vit_base_patch32_224().to(device)
     params = [p for p in model.parameters()]
@@ -339,17 +537,19 @@ def run_ours(args):
     if world > 1:
         kwargs["process_group"] = dist.group.WORLD
     opt = ShampooAdamW(params, **kwargs)
-    loss = workloads.synthetic_gradients(model, 256, 224, 1000, device, autocast_bf16=True, seed=rank)
-    if world > 1:
-        for p in params:                     # data-parallel replicas: average gradients once
-            dist.all_reduce(p.grad, op=dist.ReduceOp.AVG)
+    loss = workloads.synthetic_gradients(model, 256, 224, 1000, device, autocast_bf16=True, seed=0)
     grads = [p.grad.detach().clone() for p in params]
-    grad_bytes = sum(g.numel() * g.element_size() for g in grads)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     # ---- kernel-level: device-resident inputs ------------------------------------------
     for _ in range(args.warmup):
@@ -363,31 +563,36 @@ def run_ours(args):
             opt.step()
         e1.record()
         barrier()
-    ms_total = e0.elapsed_time(e1)
     launches = lib.qt_launch_count() - launches0
-    t = torch.tensor([ms_total], device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+    ms_step = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    # sharded == single: the same number for every N (all ranks hold identical parameters)
+    checksum = float(sum(p.detach().double().sum() for p in params))
 
-    # ---- end to end: gradients arrive from pinned host memory, a scalar goes back -----
-    host = [torch.empty(g.shape, dtype=g.dtype).pin_memory() for g in grads]
-    for h, g in zip(host, grads):
-        h.copy_(g)
+    # ---- end to end: this rank's gradients arrive from pinned host memory, a scalar goes back.
+    # A rank reads the gradients of the parameters whose preconditioners it owns and of those that
+    # have none; the directions of the others reach it through the all-gather.
+    consumed = opt.consumed_params()
+    idx = [k for k, p in enumerate(params) if p in consumed]
+    host = [torch.empty(grads[k].shape, dtype=grads[k].dtype).pin_memory() for k in idx]
+    for h, k in zip(host, idx):
+        h.copy_(grads[k])
+    grad_bytes = sum(h.numel() * h.element_size() for h in host)
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
     for _ in range(args.steps):
-        for p, h in zip(params, host):
-            p.grad.copy_(h, non_blocking=True)
+        for h, k in zip(host, idx):
+            params[k].grad.copy_(h, non_blocking=True)
         opt.step()
-        checksum = float(params[-1].detach().float().sum().cpu())
+        back = float(params[-1].detach().float().sum().cpu())
     e3.record()
     barrier()
-    t = torch.tensor([e2.elapsed_time(e3)], device=device)
+    e2e_ms = max_over_ranks(e2.elapsed_time(e3)) / args.steps
+    gb = torch.tensor([float(grad_bytes), float(grad_bytes)], device=device)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / args.steps
+        dist.all_reduce(gb[0:1], op=dist.ReduceOp.SUM)
+        dist.all_reduce(gb[1:2], op=dist.ReduceOp.MAX)
+    h2d_total, h2d_max = int(gb[0].item()), int(gb[1].item())
 
     # ---- steady-state step: no interval fires (the common step at T1=100, T2=500): only the
     # preconditioned direction P_L G P_R, grafting, the exchange and the AdamW tail run
@@ -402,55 +607,63 @@ def run_ours(args):
         opt.step()
     e5.record()
     barrier()
-    t = torch.tensor([e4.elapsed_time(e5)], device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    steady_ms = float(t.item()) / args.steps
+    steady_ms = max_over_ranks(e4.elapsed_time(e5)) / args.steps
+    opt._check_device_error()                                 # a bounded wait that ran out would have voided the numbers
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    hbm_peak, tf_burst, tf_sustained, peak_kind = measured_peaks()
     qres, qbytes, qdesc = quantizer_roofline(torch, lib, device)
     gres = gemm_roofline(torch, device)
-    # dominant kernel of the step: the tcgen05 product.  `achieved` counts algorithmic flops
-    # (2 M N K per product); the kernel executes three bf16 MMAs per product (hi*hi + hi*lo +
-    # lo*hi), so the tensor pipe runs at 3x that rate (`executed`).
+    step_flops = step_algorithmic_flops([tuple(p.shape) for p in params])
+    # dominant kernel of the step: the tcgen05 product, timed alone -> burst peak.  `achieved`
+    # counts algorithmic flops (2 M N K per product); the kernel executes three bf16 MMAs per
+    # product (hi*hi + hi*lo + lo*hi), so the tensor pipe runs at 3x that rate (`executed`).
     roof = {"bound": "tensor", "kernel": "k_gemm_bf16x3 (tcgen05 kind::f16, bf16 x3 split, fp32 accumulate in TMEM)",
-            "achieved": gres["tflops_algorithmic"], "peak": tf_peak, "unit": "TFLOP/s",
-            "frac": gres["tflops_algorithmic"] / tf_peak, "peak_kind": f"of {peak_kind} (sustained bf16)",
-            "executed": gres["tflops_executed"], "frac_executed": gres["tflops_executed"] / tf_peak,
-            "emulation_factor": 3, "traffic": 550.6e6,
-            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case under ncu "
-                              "(profiles/gemm_bf16x3_768x125.md); algorithmic operand + result bytes: 590e6",
+            "achieved": gres["tflops_algorithmic"], "peak": tf_burst, "unit": "TFLOP/s",
+            "frac": gres["tflops_algorithmic"] / tf_burst, "peak_kind": f"of {peak_kind} (burst bf16: the kernel is timed alone)",
+            "executed": gres["tflops_executed"], "frac_executed": gres["tflops_executed"] / tf_burst,
+            "emulation_factor": 3, "traffic": ncu_traffic("k_gemm_bf16x3"),
             "flops_per_launch": gres["flops_per_launch"], "case": gres["case"],
             "us_per_launch": gres["us_per_launch"],
+            "step": {"algorithmic_flops": step_flops, "achieved": step_flops / ms_step / 1e9 / world, "unit": "TFLOP/s per GPU",
+                     "peak": tf_sustained, "frac": step_flops / ms_step / 1e9 / world / tf_sustained,
+                     "peak_kind": f"of {peak_kind} (sustained bf16: timed inside the whole step)",
+                     "counting": "17 n^3 of products + 8/3 n^3 of QR per preconditioner matrix, 4 (m^2 k + m k^2) per gradient block"},
             "quantize": {"bound": "hbm", "achieved": qres["quantize"]["gbs"], "peak": hbm_peak, "unit": "GB/s",
-                         "frac": qres["quantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc,
-                         "traffic": 327.2e6},
+                         "frac": qres["quantize"]["gbs"] / hbm_peak, "frac_of_nominal_8000": qres["quantize"]["gbs"] / 8000.0,
+                         "bytes_per_launch": qbytes, "case": qdesc, "traffic": ncu_traffic("k_quantize_vec")},
             "dequantize": {"bound": "hbm", "achieved": qres["dequantize"]["gbs"], "peak": hbm_peak, "unit": "GB/s",
-                           "frac": qres["dequantize"]["gbs"] / hbm_peak, "bytes_per_launch": qbytes, "case": qdesc,
-                           "traffic": 279.0e6}}
+                           "frac": qres["dequantize"]["gbs"] / hbm_peak, "frac_of_nominal_8000": qres["dequantize"]["gbs"] / 8000.0,
+                           "bytes_per_launch": qbytes, "case": qdesc, "traffic": ncu_traffic("k_dequantize_vec")}}
     line = {"metric": METRIC, "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 arithmetic on 4-bit state", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "gradients": "one bf16-autocast cross-entropy backward, batch 256 per GPU of "
-                       "N(0,1) 224x224 images, uniform labels (computed once, reused every step)",
-                       "execution": "eager" if args.no_graph else ("whole step captured once per schedule phase and replayed as a CUDA graph (ShampooAdamW(cuda_graph=True))" if world == 1 else "two CUDA graphs per schedule phase around an eager NCCL all-gather (ShampooAdamW(cuda_graph=True))"),
+            "config": {"workload": WORKLOAD, "gradients": "one bf16-autocast cross-entropy backward, batch 256 of "
+                       "N(0,1) 224x224 images, uniform labels, seed 0 on every rank (computed once, reused every step)",
+                       "execution": "eager" if args.no_graph else ("whole step captured once per schedule phase and replayed as a CUDA graph (ShampooAdamW(cuda_graph=True))" if world == 1 else "CUDA graphs per schedule phase around the NCCL exchange (ShampooAdamW(cuda_graph=True))"),
                        "l2": "per-step working set (4-bit state 130 MB + fp32 temporaries > 2 GB) exceeds the 126 MB L2",
                        "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in HYPER.items()}},
             "clocks": clocks.summary(),
-            "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": grad_bytes, "d2h_bytes_per_step": 4},
+            "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": h2d_total, "h2d_bytes_per_step_rank_max": h2d_max,
+                    "d2h_bytes_per_step": 4 * world},
             "gpu_launches": int(launches),
             "steady_state_step": {"value": steady_ms, "unit": "ms/step",
                                   "what": "same optimizer with no interval firing (apply + grafting + AdamW tail only)"},
+            "param_checksum": checksum,
             "quant_gbs": qres["quantize"]["gbs"], "dequant_gbs": qres["dequantize"]["gbs"],
-            "roofline": roof, "loss": loss}
-    if world == 1:
-        ms, cores, sample = cpu_reference_step_ms(1, 1)
-        line["cpu_baseline"] = {"value": ms, "unit": "ms/step", "cores": cores, "kind": "port", "sample": sample}
+            "roofline": roof, "config1": config1_gpu(torch, lib, device), "loss": loss}
+    refq = reference_cuda_quantizer(torch, device)
+    if refq is not None:
+        line["reference_gpu_quantizer"] = refq
+    if world == 1 and not args.no_cpu_baseline:
+        ref = cpu_baseline_subprocess()
+        if ref is not None:
+            line["cpu_baseline"] = ref["cpu_baseline"]
+            line["config1"]["cpu"] = ref.get("config1")
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -463,12 +676,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of as a captured CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg of the N=1 run")
     ap.add_argument("--sweep", action="store_true",
                     help="kernel sweep of the fused 4-bit statistics update and the inverse 4th root over orders 128..8192")
     ap.add_argument("--sweep-orders", default="128,512,1200,2048,4096,8192")
     ap.add_argument("--profile-case", default=None, choices=["quant", "gemm", "step"],
                     help="run only one small kernel case (for an ncu capture) and print its rates")
     args = ap.parse_args()
+    if args.impl != "reference":
+        use_package()
     if args.sweep:
         import torch
         from qtensor.cextension import get_lib

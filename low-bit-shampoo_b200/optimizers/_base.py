@@ -277,6 +277,19 @@ class _ShampooBase(optim.Optimizer):
             self._world = dist.get_world_size(process_group)
             self._rank = dist.get_rank(process_group)
 
+    def consumed_params(self):
+        """Parameters whose .grad this rank reads in step(): those whose preconditioners it owns and
+        those that have none.  The update directions of the others arrive through the exchange, so
+        in a sharded run their gradients need not be present on this rank (their .grad may hold
+        anything of the right shape).  Before the first step every parameter is listed."""
+        out = set()
+        for group in self.param_groups:
+            for p in group['params']:
+                st = self.state.get(p)
+                if not st or st.get('owner', -1) in (-1, self._rank):
+                    out.add(p)
+        return out
+
     # ---- checkpoint -----------------------------------------------------------------------
     # The reference pickles its Preconditioner objects inside optimizer.state_dict()
     # (train_cifar.py:446-460) and re-homes them in load_state_dict (shampoo2.py:311-317,

@@ -104,10 +104,14 @@ def newton_inverse_root(G, p, iters=10, tol=1e-6, ridge=1e-6, v0=None):
 
 
 class EigenFactorStat:
-    """shampoo2 statistic: quantized basis Vt + lower half of the spectrum."""
+    """shampoo2 statistic: quantized basis Vt + lower half of the spectrum.
+    cfg["wide"]: every product and the QR run in float64 and only what the reference STORES
+    (4-bit codes of fp32 values, fp32 spectrum) is rounded - the exact-arithmetic twin used by
+    the tests to measure how far fp32 evaluation order alone moves the result."""
 
     def __init__(self, n, eps, cfg):
         self.n, self.cfg = n, cfg
+        self.wt = torch.float64 if cfg.get("wide") else torch.float32
         self.keep = max(1, n // 2)
         self.keep_idx = torch.arange(self.keep)
         self.S = torch.full((self.keep,), eps, dtype=torch.float32)
@@ -115,29 +119,29 @@ class EigenFactorStat:
         self.q = QState(torch.eye(n), cfg["bits"], cfg["blocksize"], cfg["min_lowbit_size"], cfg["code"], False)
 
     def reconstruct(self):
-        Vt = self.q.load()
+        Vt = self.q.load().to(self.wt)
         if self.q.lowbit:
             for _ in range(self.cfg["rect_t1"]):
                 Vt = bjorck(Vt)
         rows = Vt[self.keep_idx]
-        return rows.T @ self.S.diag() @ rows, Vt
+        return rows.T @ self.S.to(self.wt).diag() @ rows, Vt
 
     def refresh(self, L, Vt):
         V, _ = torch.linalg.qr(L @ Vt.T)
         eigs = (V.T @ L @ V).diag()
         vals, idx = torch.sort(eigs)
-        self.keep_idx, self.S = idx[: self.keep], vals[: self.keep]
-        self.max_eig = eigs.max()
-        self.q.store(V.T.contiguous())
+        self.keep_idx, self.S = idx[: self.keep], vals[: self.keep].float()
+        self.max_eig = eigs.max().float()
+        self.q.store(V.T.contiguous().float())
 
     def inverse_root(self, p, eps):
-        Vt = self.q.load()
+        Vt = self.q.load().to(self.wt)
         rows = Vt[self.keep_idx]
         if self.q.lowbit:
             for _ in range(self.cfg["rect_t2"]):
                 rows = bjorck(rows)
         w = 1 / (self.S + eps * self.max_eig).pow(1 / p)
-        return rows.T @ w.diag() @ rows
+        return (rows.T @ w.to(self.wt).diag() @ rows).float()
 
 
 def split_sizes(d, block):
@@ -178,7 +182,7 @@ class OracleShampoo:
                  weight_decay=0.0, momentum=0.9, nesterov=False, start_prec_step=1, stat_compute_steps=100,
                  prec_compute_steps=500, stat_decay=0.95, matrix_eps=1e-6, prec_maxorder=1200, prec_bits=32,
                  min_lowbit_size=4096, quan_blocksize=64, rect_t1=1, rect_t2=4, inv_root_mode=0,
-                 diagreal_none=False):
+                 diagreal_none=False, alternate_rounding=False, wide_arithmetic=False):
         self.params = params
         self.kind, self.h = kind, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, momentum=momentum,
                                        nesterov=nesterov, start=start_prec_step, t1=stat_compute_steps,
@@ -186,8 +190,15 @@ class OracleShampoo:
         code = qoracle.linear_map(True, prec_bits, 2) if prec_bits in (4, 8) else None
         self.cfg = dict(flavour=flavour, bits=prec_bits, blocksize=quan_blocksize, min_lowbit_size=min_lowbit_size,
                         code=code, rect_t1=rect_t1, rect_t2=rect_t2, matrix_eps=matrix_eps,
-                        prec_maxorder=prec_maxorder)
+                        prec_maxorder=prec_maxorder, wide=wide_arithmetic)
+        # float64 twin (shampoo2 flavour, inverse-root mode 0 only): see EigenFactorStat
+        self.wt = torch.float64 if wide_arithmetic else torch.float32
         self.diagreal_none = diagreal_none
+        # Sensitivity yardstick for tests: evaluates the statistics update beta*L + (1-beta)*S in
+        # another, algebraically identical order (one fp32 rounding differs per element).  How far the
+        # parameters move under that change is how finely ANY implementation can be compared
+        # with the reference on the same inputs.
+        self.alternate_rounding = alternate_rounding
         self.state = [None] * len(params)
 
     def _load_diagreal(self, q):
@@ -201,13 +212,16 @@ class OracleShampoo:
         w2 = 1.0 if w1 == 1.0 else 1.0 - w1
         G2 = grad.reshape(st.mat_shape)
         for j, (rs, cs) in enumerate(st.blocks):
-            g = G2[rs, cs].float()
+            g = G2[rs, cs].to(self.wt)
             for axis in range(2):
                 stat = g.T @ g if axis == 1 else g @ g.T
                 s = st.stats[2 * j + axis]
                 if self.cfg["flavour"] == "s2":
                     L, Vt = s.reconstruct()
-                    L = L * w1 + w2 * stat
+                    if self.alternate_rounding:
+                        L = L * w1 + w2 * stat
+                    else:
+                        L.mul_(w1).add_(stat, alpha=w2)       # same operation order as shampoo2.py:199
                     s.refresh(L, Vt)
                 else:
                     L = self._load_diagreal(s)
@@ -242,7 +256,7 @@ class OracleShampoo:
             P1 = self._load_diagreal(st.precs[2 * j + 1])
             P0 = torch.eye(g.shape[0]) if P0 is None else P0
             P1 = torch.eye(g.shape[1]) if P1 is None else P1
-            out[rs, cs] = (P0 @ g) @ P1
+            out[rs, cs] = ((P0.to(self.wt) @ g.to(self.wt)) @ P1.to(self.wt)).to(out.dtype)
         return out.reshape(grad.shape)
 
     def step(self, grads):

@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden.py [--ref /path/to/reference]
+    python tests/golden/make_golden.py --ref /path/to/reference
 
 The reference (qtensor/functional.py) is imported, never copied.  Every case stores its
 inputs and the reference's outputs, so the fixtures are self-contained on machines
@@ -35,7 +35,7 @@ def bf16_bits(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of a checkout of the reference project")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
     import qtensor.functional as RF

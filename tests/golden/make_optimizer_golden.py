@@ -1,6 +1,6 @@
 """Generates tests/golden/optimizer_cases.npz by running the REFERENCE optimizers on CPU.
 
-    python tests/golden/make_optimizer_golden.py [--ref /path/to/reference]
+    python tests/golden/make_optimizer_golden.py --ref /path/to/reference
 
 The reference is imported, never copied or edited.  Three ways of running it:
 
@@ -94,7 +94,7 @@ def run_case(optim_cls, extra, seed, mode, modules):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of a checkout of the reference project")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
     cwd = os.getcwd()

@@ -1,0 +1,245 @@
+"""Parity of the optimizer step at the preconditioner orders the headline benchmark runs on
+(672 .. 1200, ViT-B/32) and at the orders of the ResNet-34 and Swin-Tiny configurations.
+
+Three layers of evidence:
+  1. tests/golden/large_order_cases.npz - parameters produced by the REFERENCE shampoo2-AdamW
+     (CPU, 4-bit forced) on 768 x 768 and 1200 x 1200 parameters.  The CPU oracle is checked
+     against it here without a GPU, the CUDA path with one (eager and CUDA-graph replay).
+  2. CUDA path against the oracle run on the fly, per matrix: the dequantized 4-bit
+     preconditioner P = L^(-1/4), the preconditioned block P_L G P_R, and the parameters.
+  3. The real (non-square) shapes of one ViT-B/32 encoder layer and of ResNet-34 / Swin-Tiny
+     layers.  Their statistics are rank-deficient by construction (G G^T of a 1200 x 768
+     block has rank <= 768), and there the reference's own result is not a function of its
+     inputs to better than the 4-bit quantisation noise: the basis of the null space comes
+     out of rounding noise in the QR, and a different basis quantises to different codes.  The
+     bound used for those cases is stated next to each assertion.
+
+Tolerance: 1e-4 relative Frobenius error on post-step parameters, preconditioners and
+preconditioned blocks - or, where that is larger, three times the SENSITIVITY YARDSTICK of the
+case: the distance between the oracle and the same oracle with one fp32 rounding of the statistics
+update evaluated in another order (OracleShampoo(alternate_rounding=True)).  The reference's
+step amplifies rounding (lower-half truncation of the spectrum, 4-bit codes that flip): at order
+1200 that single rounding moves its second-step parameters by 1.4e-4, so no implementation -
+its own CUDA path included - can be closer to it than that on such a case."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import GOLDEN, hashed_matrix, wellposed_matrix
+
+TOL = 1e-4
+
+
+def load_large():
+    blob = np.load(os.path.join(GOLDEN, "large_order_cases.npz"))
+    meta = json.loads(bytes(blob["meta"]).decode())
+    return blob, meta
+
+
+def large_inputs(meta):
+    shapes = [tuple(s) for s in meta["shapes"]]
+    init = [torch.from_numpy(hashed_matrix(s, seed, meta["init_scale"])) for s, seed in zip(shapes, meta["init_seeds"])]
+    grads = [[torch.from_numpy(wellposed_matrix(s, seed, meta["grad_scale"])) for s, seed in zip(shapes, row)]
+             for row in meta["grad_seeds"]]
+    return shapes, init, grads
+
+
+def hyper_of(meta):
+    h = dict(meta["hyper"])
+    h["betas"] = tuple(h["betas"])
+    return h
+
+
+def sample_errors(blob, meta, mode, t, params, init):
+    """(parameter error, update error) of `params` against the stored sample of the reference's
+    parameters after step t; both relative Frobenius over the sampled elements of all tensors."""
+    stride = meta["stride"]
+    num = den = upd = 0.0
+    for i, p in enumerate(params):
+        got = np.asarray(p, dtype=np.float64).reshape(-1)[::stride]
+        want = blob[f"{mode}.after.{t}.{i}.sample"].astype(np.float64)
+        prev = (blob[f"{mode}.after.{t - 1}.{i}.sample"] if t > 0 else init[i].numpy().reshape(-1)[::stride]).astype(np.float64)
+        num += float(((got - want) ** 2).sum())
+        den += float((want ** 2).sum())
+        upd += float(((want - prev) ** 2).sum())
+    return (num / den) ** 0.5, (num / upd) ** 0.5
+
+
+# --------------------------------------------------------------------------------------
+# 1. reference fixtures at orders 768 and 1200
+# --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode", ["bits4_ret", "bits4"])
+def test_oracle_matches_reference_at_orders_768_and_1200(mode):
+    """Pins the CPU oracle at large order: same inputs, parameters within 1e-4 of the reference's."""
+    from oracle.shampoo_oracle import OracleShampoo
+    blob, meta = load_large()
+    shapes, init, grads = large_inputs(meta)
+    params = [t.clone() for t in init]
+    h = hyper_of(meta)
+    opt = OracleShampoo(params, kind="adamw", flavour="s2", prec_bits=4, diagreal_none=(mode == "bits4"), **h)
+    for t in range(meta["steps"]):
+        opt.step([g.clone() for g in grads[t]])
+        perr, uerr = sample_errors(blob, meta, mode, t, [p.numpy() for p in params], init)
+        print(mode, "step", t, "param err", perr, "update err", uerr)
+        assert perr < TOL, (mode, t, perr, uerr)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("graph", [False, True], ids=["eager", "graph"])
+@pytest.mark.parametrize("mode", ["bits4_ret", "bits4"])
+def test_cuda_step_matches_reference_at_orders_768_and_1200(native_lib, mode, graph):
+    from optimizers import _engine
+    from optimizers.shampoo2 import ShampooAdamW
+    from oracle.shampoo_oracle import OracleShampoo
+    blob, meta = load_large()
+    shapes, init, grads = large_inputs(meta)
+    ps = [torch.nn.Parameter(t.clone().cuda()) for t in init]
+    alt = [t.clone() for t in init]
+    ora_alt = OracleShampoo(alt, kind="adamw", flavour="s2", prec_bits=4, diagreal_none=(mode == "bits4"),
+                            alternate_rounding=True, **hyper_of(meta))
+    _engine.REFERENCE_DIAGREAL_NONE = (mode == "bits4")
+    try:
+        opt = ShampooAdamW(ps, prec_bits=4, cuda_graph=graph, **hyper_of(meta))
+        for t in range(meta["steps"]):
+            for p, g in zip(ps, grads[t]):
+                p.grad = g.clone().cuda()
+            opt.step()
+            torch.cuda.synchronize()
+            ora_alt.step([g.clone() for g in grads[t]])
+            yard, _ = sample_errors(blob, meta, mode, t, [p.numpy() for p in alt], init)
+            perr, uerr = sample_errors(blob, meta, mode, t, [p.detach().cpu().numpy() for p in ps], init)
+            print(mode, "graph" if graph else "eager", "step", t, "param err", perr, "update err", uerr, "yardstick", yard)
+            assert perr < max(TOL, 3 * yard), (mode, t, perr, uerr, yard)
+    finally:
+        _engine.REFERENCE_DIAGREAL_NONE = False
+    assert native_lib.qt_device_error(1) == 0
+
+
+# --------------------------------------------------------------------------------------
+# 2. per-matrix intermediates against the oracle, square blocks of every model order
+# --------------------------------------------------------------------------------------
+HEADLINE_HYPER = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.05, stat_compute_steps=1,
+                      prec_compute_steps=1, prec_maxorder=1200, stat_decay=0.95, matrix_eps=1e-6, quan_blocksize=64,
+                      rect_t1=1, rect_t2=4, inv_root_mode=0)
+
+
+def rel(a, b):
+    a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-300))
+
+
+class Run:
+    """Steps the CUDA optimizer, the CPU oracle and the oracle's alternate-rounding twin on the
+    same deterministic inputs."""
+
+    def __init__(self, shapes, steps, seed, hyper=HEADLINE_HYPER, graph=False, cuda=True):
+        from oracle.shampoo_oracle import OracleShampoo
+        self.shapes = shapes
+        init = [torch.from_numpy(hashed_matrix(s, seed + i, 2.0 ** -5)) for i, s in enumerate(shapes)]
+        self.ref = [t.clone() for t in init]
+        self.alt = [t.clone() for t in init]
+        self.ora = OracleShampoo(self.ref, kind="adamw", flavour="s2", prec_bits=4, **hyper)
+        self.ora_alt = OracleShampoo(self.alt, kind="adamw", flavour="s2", prec_bits=4, alternate_rounding=True, **hyper)
+        self.ps = self.opt = None
+        if cuda:
+            from optimizers.shampoo2 import ShampooAdamW
+            self.ps = [torch.nn.Parameter(t.clone().cuda()) for t in init]
+            self.opt = ShampooAdamW(self.ps, prec_bits=4, cuda_graph=graph, **hyper)
+        for t in range(steps):
+            self.grads = [torch.from_numpy(wellposed_matrix(s, seed + 100 * (t + 1) + i)) for i, s in enumerate(shapes)]
+            if cuda:
+                for p, g in zip(self.ps, self.grads):
+                    p.grad = g.clone().cuda()
+                self.opt.step()
+            self.ora.step([g.clone() for g in self.grads])
+            self.ora_alt.step([g.clone() for g in self.grads])
+        if cuda:
+            torch.cuda.synchronize()
+
+    def tolerance(self, i):
+        """max(1e-4, 3 x yardstick) for the parameters of tensor i."""
+        return max(TOL, 3.0 * rel(self.alt[i].numpy(), self.ref[i].numpy()))
+
+    def param_error(self, i):
+        return rel(self.ps[i].detach().cpu().numpy(), self.ref[i].numpy())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [672, 768, 1000, 1104, 1200, 100, 336, 576, 1008, 1152])
+def test_square_block_intermediates_match_oracle(native_lib, n):
+    """One n x n parameter, two steps: the dequantized 4-bit preconditioners, the preconditioned
+    gradient block and the parameters against the oracle's."""
+    r = Run([(n, n)], 2, seed=7 * n)
+    pre = r.opt.state[r.ps[0]]["preconditioner"]
+    st, st_alt = r.ora.state[0], r.ora_alt.state[0]
+    for axis in range(2):
+        P_gpu = pre.preconditioners[axis].dequantize().cpu().numpy()
+        P_ref = st.precs[axis].load().numpy()
+        yard = rel(st_alt.precs[axis].load().numpy(), P_ref)
+        e = rel(P_gpu, P_ref)
+        print(f"order {n} axis {axis}: preconditioner error {e:.3e} (yardstick {yard:.3e})")
+        assert e < max(TOL, 3 * yard), (n, axis, e, yard)
+    g = r.grads[0]
+    blk_ref = r.ora._preconditioned(st, g.clone()).numpy()
+    yard = rel(r.ora_alt._preconditioned(st_alt, g.clone()).numpy(), blk_ref)
+    e = rel(pre.preconditioned_grad(g.cuda()).cpu().numpy(), blk_ref)
+    print(f"order {n}: preconditioned block error {e:.3e} (yardstick {yard:.3e})")
+    assert e < max(TOL, 3 * yard), (n, e, yard)
+    e = r.param_error(0)
+    print(f"order {n}: parameter error {e:.3e} (tolerance {r.tolerance(0):.3e})")
+    assert e < r.tolerance(0), (n, e)
+    assert native_lib.qt_device_error(1) == 0
+
+
+# --------------------------------------------------------------------------------------
+# 3. real layer shapes (rank-deficient statistics)
+# --------------------------------------------------------------------------------------
+VIT_LAYER = [(2304, 768), (2304,), (768, 768), (768,), (3072, 768), (3072,), (768, 3072), (768,)]
+RESNET_SUBSET = [(64, 3, 3, 3), (64, 64, 3, 3), (128, 64, 1, 1), (128, 128, 3, 3), (256, 256, 3, 3), (512, 512, 3, 3),
+                 (100, 512), (100,)]
+SWIN_SUBSET = [(96, 3, 2, 2), (49, 3), (49, 6), (9, 24), (288, 96), (96, 384), (192, 384), (576, 192), (384, 1536), (1152, 384),
+               (768, 3072), (2304, 768), (100, 768)]
+
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("graph", [False, True], ids=["eager", "graph"])
+def test_vit_encoder_layer_step(native_lib, graph):
+    """qkv, proj, fc1, fc2 of one ViT-B/32 encoder layer (orders 672, 768, 1104, 1200), two steps,
+    T1 = T2 = 1, eager and replayed as a CUDA graph."""
+    r = Run(VIT_LAYER, 2, seed=31, graph=graph)
+    for i, s in enumerate(VIT_LAYER):
+        e = r.param_error(i)
+        print("vit layer", s, "graph" if graph else "eager", f"parameter error {e:.3e} (tolerance {r.tolerance(i):.3e})")
+        assert e < r.tolerance(i), (s, e, r.tolerance(i))
+    assert native_lib.qt_device_error(1) == 0
+
+
+@pytest.mark.gpu
+def test_vit_encoder_layer_graph_replay_equals_eager(native_lib):
+    a = Run(VIT_LAYER, 3, seed=31, graph=False)
+    b = Run(VIT_LAYER, 3, seed=31, graph=True)
+    assert b.opt._use_graph and b.opt._graph_state is not None
+    for s, x, y in zip(VIT_LAYER, a.ps, b.ps):
+        e = rel(y.detach().cpu().numpy(), x.detach().cpu().numpy())
+        assert e < 1e-5, (s, e)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,shapes", [("resnet34", RESNET_SUBSET), ("swin_tiny", SWIN_SUBSET)])
+def test_model_subsets_cover_every_order(native_lib, name, shapes):
+    """One step on a subset of each model's parameter shapes that contains every distinct
+    preconditioner order of the model (100, 336, 576, 1008, 1152, ... and the small fp32 ones)."""
+    import workloads
+    model = workloads.resnet34_cifar() if name == "resnet34" else workloads.swin_tiny_32()
+    full = workloads.preconditioner_census([tuple(p.shape) for p in model.parameters()])
+    assert set(workloads.preconditioner_census(shapes)) == set(full), "subset misses an order of the model"
+    r = Run(shapes, 1, seed=57)
+    for i, s in enumerate(shapes):
+        e = r.param_error(i)
+        print(name, s, f"parameter error {e:.3e} (tolerance {r.tolerance(i):.3e})")
+        assert e < r.tolerance(i), (s, e, r.tolerance(i))
+    assert native_lib.qt_device_error(1) == 0

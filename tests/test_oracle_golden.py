@@ -77,3 +77,13 @@ def test_config1_hashes_when_input_reproduces():
     assert sha(pd) == rec["diag_packed_sha256"]
     assert sha(ad) == rec["diag_absmax_sha256"]
     assert sha(dg) == rec["diag_sha256"]
+
+
+def test_product_codebooks_equal_reference_codebooks():
+    """create_linear_map / create_dynamic_map of the package (no GPU needed) against the
+    codebooks the reference's functions produced (functional.py:87-113), bit for bit."""
+    import qtensor.functional as F
+    blob, _ = load_quant_cases()
+    assert bits_equal(F.create_linear_map(True, 4, 2).numpy(), blob["code.linear4"])
+    assert bits_equal(F.create_linear_map(True, 8, 2).numpy(), blob["code.linear8"])
+    assert bits_equal(F.create_dynamic_map(True, 4, 1).numpy(), blob["code.dynamic4"])
