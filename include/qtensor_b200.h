@@ -225,6 +225,70 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
                    float *D, long long ldd, long long strideD, void *stream);
 
 /*
+ * General form of the two products above, for chains of products that hand bf16 planes from one
+ * epilogue to the next prologue (the coupled Newton iteration of the inverse root,
+ * optimizers/matrix_functions.py:127-140: root * T, T^2, T^4, T^4 * M, max |M - I|):
+ *   - A, B: planes {hi, mid, lo}; mid == NULL on both selects the two-plane product (three MMAs),
+ *     otherwise the three-plane one (six MMAs);
+ *   - result as fp32 D and / or as planes P {hi, mid, lo} (mid only for three-plane products);
+ *   - T (three-plane products): also writes t_c0 * I + t_c1 * result as three planes, same pitch;
+ *   - maxdev: per matrix, max |result - I| is combined into maxdev[m] with an atomic maximum
+ *     (non-negative floats; the caller zeroes it; NaN / inf count as +inf);
+ *   - a_slot / b_slot / d_slot: per matrix, which entry of A's / B's storage is read and which
+ *     entry of the outputs is written (NULL: the matrix number); a_entries / b_entries give the
+ *     number of matrices in A's / B's storage (0: batch);
+ *   - active: per matrix, 0 = skip all tiles of this matrix (NULL: none skipped).
+ * All index and flag arrays are device int32 arrays read when the kernel runs.
+ */
+typedef struct qt_gemm_desc {
+    const void *A[3]; long long lda, strideA; int a_mn, a_entries;
+    const void *B[3]; long long ldb, strideB; int b_mn, b_entries;
+    int M, N, K, batch; float alpha, beta;
+    const float *C; long long ldc, strideC;
+    float *D; long long ldd, strideD;
+    void *P[3]; long long ldp, strideP;
+    void *T[3]; float t_c0, t_c1;
+    float *maxdev;
+    const int *a_slot, *b_slot, *d_slot, *active;
+} qt_gemm_desc;
+int qt_gemm_ex(const qt_gemm_desc *desc, void *stream);
+
+/*
+ * Largest eigenvalue of each of `batch` symmetric n x n fp32 matrices (G + m*strideG) by power
+ * iteration from the given start vectors v0 (batch x n), following PowerIter of the reference
+ * (optimizers/matrix_functions.py:22-48) step by step: normalise, multiply, Rayleigh quotient,
+ * stop when the quotient moves by <= tol or after max_iters steps.  One launch for the batch, no
+ * host synchronisation (the reference synchronises once per step, :40).  max_ev: batch floats;
+ * iters (may be NULL): steps taken per matrix; vec (may be NULL): batch x n, the last iterate G v
+ * (not normalised).
+ */
+int qt_power_iter(float *G, long long strideG, int n, int batch, const float *v0, float tol, int max_iters,
+                  float *max_ev, int *iters, float *vec, void *stream);
+
+/*
+ * (G + ridge_eps * lambda_max(G) I)^(-1/p) for `batch` SPD fp32 matrices by the coupled Newton
+ * iteration, i.e. ComputePower of the reference (optimizers/matrix_functions.py:80-141; callers
+ * optimizers/shampoo1.py:181-201 and optimizers/shampoo2.py:220-230) for a whole batch:
+ * power iteration from v0 (batch x n; the reference draws torch.rand(n) * 2 - 1 per matrix),
+ * ridge added to G's diagonal IN PLACE (as the reference does, :112), then up to iter_count
+ * iterations root' = root T, M' = T^p M with every product on the three-plane tcgen05 kernel,
+ * max |M' - I| reduced in the epilogue and the reference's accept / stop rule (:131-140) applied
+ * per matrix through flags in device memory - no host synchronisation anywhere.
+ * p must be a power of two >= 2 (the optimizers use 4).  workspace: caller-owned device memory of
+ * qt_inverse_root_newton_workspace_bytes(n, batch) bytes, 256-byte aligned (42 bytes per matrix
+ * element: ping-pong planes of M and root, T and two powers of T).  out + m*strideOut: n x n fp32.
+ * max_ev, iters (may be NULL): per matrix lambda_max estimate and accepted iterations.
+ */
+unsigned long long qt_inverse_root_newton_workspace_bytes(int n, int batch);
+int qt_inverse_root_newton(float *G, long long strideG, int n, int batch, int p, int iter_count, float tol, float ridge_eps,
+                           const float *v0, void *workspace, unsigned long long workspace_bytes,
+                           float *out, long long strideOut, float *max_ev, int *iters, void *stream);
+
+/* Test hook: 128 or 256 forces the output-tile width of two-plane products, -1 restores the
+ * choice by problem size.  Additive; no counterpart in the reference. */
+void qt_gemm_force_tile(int bn);
+
+/*
  * The three-product (qt_gemm_bf16x3_q4) and six-product (qt_gemm_bf16x6_q4) GEMMs with 4-bit
  * blockwise state (block size 64, the byte format of qt_quantize_blockwise) as C operand and as
  * result, square n x n, n a multiple of 16:

@@ -27,13 +27,26 @@
 
 namespace qt {
 
-static constexpr int BM = 128, BN = 128, BK = 64;
-static constexpr int PLANE_TILE_BYTES = BM * BK * 2;                 // 16 KiB per plane tile
-static constexpr int RING_BYTES = 12 * PLANE_TILE_BYTES;             // 3 stages x 4 tiles (two planes per operand)
-                                                                     // or 2 stages x 6 tiles (three planes)
-static constexpr int GEMM_THREADS = 192;
+static constexpr int BM = 128, BK = 64;
+static constexpr int PLANE_TILE_BYTES = BM * BK * 2;                 // 16 KiB: a 128 x 64 bf16 tile of one plane
+static constexpr int RING_BYTES = 12 * PLANE_TILE_BYTES;             // 192 KiB of operand stages
 static constexpr int GEMM_SMEM = RING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 static constexpr unsigned WAIT_LIMIT = 1u << 18;
+
+// Tile configuration: NP planes per operand, output tile 128 x BN_.
+//   NP = 2, BN_ = 128: 64 KiB per stage, 3 stages   (small problems: more tiles than SMs matter more)
+//   NP = 2, BN_ = 256: 96 KiB per stage, 2 stages   (the tensor core reads 12 KiB of operands per
+//                      128x256x16 MMA instead of 8 KiB per 128x128x16 one: 25 % less shared-memory
+//                      traffic per flop, which is what bounds the 128 x 128 tile)
+//   NP = 3, BN_ = 128: 96 KiB per stage, 2 stages
+template <int NP, int BN_> struct TileCfg {
+    static constexpr int B_TILES = BN_ / 128;
+    static constexpr int STAGE_BYTES = NP * (1 + B_TILES) * PLANE_TILE_BYTES;
+    static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
+    static constexpr int EPI_WARPS = BN_ / 32;                       // 4 or 8 epilogue warps (128 columns each per row quarter)
+    static constexpr int THREADS = (EPI_WARPS + 2) * 32;
+    static constexpr int TMEM_COLS = 2 * BN_;                        // two accumulators
+};
 
 __device__ int g_gemm_error = 0;
 
@@ -42,7 +55,11 @@ struct GemmParams {
     float alpha, beta;
     const float *C; long long ldc, strideC;
     float *D; long long ldd, strideD;
-    __nv_bfloat16 *Dhi, *Dlo; long long ldp, strideP;
+    __nv_bfloat16 *Dhi, *Dmid, *Dlo; long long ldp, strideP;              // result as bf16 planes (Dmid: three-plane kernels)
+    __nv_bfloat16 *Thi, *Tmid, *Tlo; float t_c0, t_c1;                    // t_c0 * I + t_c1 * result as three planes
+    float *maxdev;                                                        // per matrix: max |result - I| (atomic max)
+    const int *a_slot, *b_slot, *d_slot;                                  // per matrix: entry of A / B / outputs (null: the matrix number)
+    const int *active;                                                    // per matrix: 0 = skip (null: all)
     int tiles_m, tiles_n;
     // 4-bit state as C operand and as result (QOUT kernels only): block size 64, order N == M
     const unsigned char *q_in; const float *q_absmax_in, *q_diag_in;      // q_in == nullptr: no C operand
@@ -264,21 +281,70 @@ __device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, c
     }
 }
 
-template <bool A_MN, bool B_MN, int NP, bool QOUT = false>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// 16 consecutive result values of one row -> NP bf16 planes (x = hi [+ mid] + lo).  `wide`: one
+// 256-bit store per plane (32-byte aligned); otherwise element by element, `nvalid` of them.
+template <int NP>
+__device__ __forceinline__ void store_planes(__nv_bfloat16 *hi, __nv_bfloat16 *mid, __nv_bfloat16 *lo, const float (&v)[16],
+                                             bool wide, int nvalid) {
+    unsigned short H[16], M[16], L[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(v[t]);
+        const float r1 = v[t] - __bfloat162float(h);
+        H[t] = __bfloat16_as_ushort(h);
+        if constexpr (NP == 3) {
+            const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+            M[t] = __bfloat16_as_ushort(m);
+            L[t] = __bfloat16_as_ushort(__float2bfloat16_rn(r1 - __bfloat162float(m)));
+        } else {
+            L[t] = __bfloat16_as_ushort(__float2bfloat16_rn(r1));
+        }
+    }
+    if (wide) {
+        unsigned w[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = (unsigned)H[2 * t] | ((unsigned)H[2 * t + 1] << 16);
+        stg256u(hi, w);
+        if constexpr (NP == 3) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) w[t] = (unsigned)M[2 * t] | ((unsigned)M[2 * t + 1] << 16);
+            stg256u(mid, w);
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = (unsigned)L[2 * t] | ((unsigned)L[2 * t + 1] << 16);
+        stg256u(lo, w);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+            if (t < nvalid) {
+                hi[t] = __ushort_as_bfloat16(H[t]);
+                if constexpr (NP == 3) mid[t] = __ushort_as_bfloat16(M[t]);
+                lo[t] = __ushort_as_bfloat16(L[t]);
+            }
+        }
+    }
+}
+
+template <bool A_MN, bool B_MN, int NP, int BN_, bool QOUT = false>
+__global__ void __launch_bounds__((BN_ / 32 + 2) * 32, 1)
 k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+    using Cfg = TileCfg<NP, BN_>;
     __shared__ QuantTablesHolder<QOUT> qtab;
-    constexpr int STAGES = NP == 2 ? 3 : 2;
-    constexpr int STAGE_BYTES = 2 * NP * PLANE_TILE_BYTES;
-    // The tensor core's fp32 accumulation truncates: its error grows linearly with the length of
-    // one accumulation chain (measured 6.5e-9 * K relative).  The three-plane variant therefore
-    // accumulates at most KC k-blocks (128 k) per TMEM accumulator and adds the partial sums in
-    // fp32 registers in the epilogue warps; the two-plane variant (1e-5 target) uses one chain.
-    constexpr int KC = NP == 3 ? 2 : 0;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int EPI_WARPS = Cfg::EPI_WARPS;
+    constexpr int B_PLANE_BYTES = Cfg::B_TILES * PLANE_TILE_BYTES;
+    // The tensor core's fp32 accumulation truncates: the error of one accumulation chain grows
+    // linearly with its length (measured 6.5e-9 * K relative, biased).  The three-plane variant
+    // therefore accumulates at most KC k-blocks (128 k) per TMEM accumulator and the epilogue
+    // warps add the partial sums in fp32 registers (round to nearest) while the next chunk is
+    // being multiplied; the two-plane variant, whose operands carry 16 significant bits anyway,
+    // keeps one chain per tile (chunking it cost 2 ms of a 32 ms step and bought no accuracy).
+    constexpr int KC = NP == 3 ? 2 : (1 << 20);
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *aligned = smem_raw + (base - smem_u32(smem_raw));
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(aligned + STAGES * STAGE_BYTES);
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(aligned + RING_BYTES);
     // bars[0..S): full, [S..2S): empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
     unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -293,15 +359,16 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     if (*reinterpret_cast<volatile int *>(&g_gemm_error) != 0) return;
     const int num_kb = (p.K + BK - 1) / BK;
     const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
+    const int nchunks = (num_kb + KC - 1) / KC;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    if (warp == EPI_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -310,7 +377,11 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const unsigned tmem_base = *tmem_slot;
     if constexpr (QOUT) build_tables<16>(qtab.t, p.q_code);    // all threads; ends with a barrier
 
-    if (warp == 4) {
+    // A matrix whose entry of `active` is zero is skipped by all three roles alike (the array
+    // does not change while the kernel runs), so their ring and accumulator counters stay in step.
+    auto skipped = [&](int b) { return p.active != nullptr && __ldg(p.active + b) == 0; };
+
+    if (warp == EPI_WARPS) {
         // ---------------- TMA producer: one ring of stages shared by all tiles of this CTA
         if (lane == 0) {
             unsigned it = 0;
@@ -318,7 +389,10 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int tm, tn, b;
                 tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
-                const int m0 = tm * BM, n0 = tn * BN;
+                if (skipped(b)) continue;
+                const int za = p.a_slot ? __ldg(p.a_slot + b) : b;
+                const int zb = p.b_slot ? __ldg(p.b_slot + b) : b;
+                const int m0 = tm * BM, n0 = tn * BN_;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
@@ -328,29 +402,31 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                     const int k0 = kb * BK;
 #pragma unroll
                     for (int pl = 0; pl < NP; ++pl) {
-                        const unsigned ta = stage + pl * PLANE_TILE_BYTES, tb = stage + (NP + pl) * PLANE_TILE_BYTES;
+                        const unsigned ta = stage + pl * PLANE_TILE_BYTES;
+                        const unsigned tb = stage + NP * PLANE_TILE_BYTES + pl * B_PLANE_BYTES;
                         if (!A_MN) {
-                            tma_load_3d(ta, &maps.a[pl], full_bar(s), k0, m0, b);
+                            tma_load_3d(ta, &maps.a[pl], full_bar(s), k0, m0, za);
                         } else {
-                            tma_load_3d(ta, &maps.a[pl], full_bar(s), m0, k0, b);
-                            tma_load_3d(ta + PLANE_TILE_BYTES / 2, &maps.a[pl], full_bar(s), m0 + 64, k0, b);
+                            tma_load_3d(ta, &maps.a[pl], full_bar(s), m0, k0, za);
+                            tma_load_3d(ta + PLANE_TILE_BYTES / 2, &maps.a[pl], full_bar(s), m0 + 64, k0, za);
                         }
                         if (!B_MN) {
-                            tma_load_3d(tb, &maps.b[pl], full_bar(s), k0, n0, b);
+                            tma_load_3d(tb, &maps.b[pl], full_bar(s), k0, n0, zb);
                         } else {
-                            tma_load_3d(tb, &maps.b[pl], full_bar(s), n0, k0, b);
-                            tma_load_3d(tb + PLANE_TILE_BYTES / 2, &maps.b[pl], full_bar(s), n0 + 64, k0, b);
+#pragma unroll
+                            for (int c = 0; c < BN_ / 64; ++c)
+                                tma_load_3d(tb + c * (PLANE_TILE_BYTES / 2), &maps.b[pl], full_bar(s), n0 + 64 * c, k0, zb);
                         }
                     }
                 }
             }
         }
-    } else if (warp == 5) {
-        // ---------------- MMA issuer: accumulator i&1 in TMEM columns [ (i&1)*BN, +BN )
+    } else if (warp == EPI_WARPS + 1) {
+        // ---------------- MMA issuer: accumulator j&1 in TMEM columns [ (j&1)*BN_, +BN_ )
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N, M
             const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-                                   ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+                                   ((unsigned)(BN_ >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
             // descriptors differ only in their 14-bit start-address field: build one per operand
             // plane for stage 0, k-slice 0 and add (byte offset >> 4) afterwards
             const unsigned a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
@@ -358,7 +434,7 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
 #pragma unroll
             for (int pl = 0; pl < NP; ++pl) {
                 dA[pl] = smem_desc(base + pl * PLANE_TILE_BYTES, a_lbo, 1024u);
-                dB[pl] = smem_desc(base + (NP + pl) * PLANE_TILE_BYTES, b_lbo, 1024u);
+                dB[pl] = smem_desc(base + NP * PLANE_TILE_BYTES + pl * B_PLANE_BYTES, b_lbo, 1024u);
             }
             constexpr unsigned a_step = (A_MN ? 2048u : 32u) >> 4, b_step = (B_MN ? 2048u : 32u) >> 4;
             unsigned it = 0;
@@ -369,17 +445,17 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 // the tensor core's time per MMA scales with N
                 int tm_, tn_, b_;
                 tile_coords(tile, p.tiles_m, p.tiles_n, tm_, tn_, b_);
-                const int ncur = min(BN, (p.N - tn_ * BN + 15) & ~15);
+                if (skipped(b_)) continue;
+                const int ncur = min(BN_, (p.N - tn_ * BN_ + 15) & ~15);
                 const unsigned idesc_tile = (idesc & ~(0x3Fu << 17)) | ((unsigned)(ncur >> 3) << 17);
-                const int nchunks = KC ? (num_kb + KC - 1) / KC : 1;
                 int kb = 0;
                 for (int ch = 0; ch < nchunks && ok; ++ch, ++j) {
                     const int acc = j & 1;
                     ok = mbar_wait(acc_empty(acc), ((j >> 1) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
-                    const int kend = KC ? min(num_kb, kb + KC) : num_kb;
+                    const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN_);
+                    const int kend = min(num_kb, kb + KC);
                     for (bool fresh = true; kb < kend; ++kb, ++it, fresh = false) {
                         const int s = it % STAGES;
                         ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
@@ -410,230 +486,121 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             }
         }
     } else {
-        // ---------------- epilogue: warp q owns TMEM lanes 32q .. 32q+31; lane = output row.
-        // Each thread combines and stores 32 consecutive columns of its own row with 128-bit
-        // accesses straight from registers: no shared-memory staging, because the tensor core's
-        // operand fetch already uses the whole shared-memory bandwidth.  C (beta != 0) is fetched
-        // one 32-column chunk ahead, the first chunk before waiting for the accumulator.  The
-        // epilogue of tile i overlaps the main loop of tile i+1.
+        // ---------------- epilogue: warp e reads TMEM lanes 32 (e & 3) .. +31 (lane = output row) and
+        // the 128 accumulator columns [128 (e >> 2), +128) of the tile.  Partial sums of the chunks
+        // are added in registers; the final combine / conversion / store works on 16 columns at a
+        // time with 256-bit accesses straight from registers (no shared-memory staging: the tensor
+        // core's operand fetch already uses the shared-memory bandwidth).
+        const int quad = warp & 3, half = warp >> 2;
         const bool has_c = p.C != nullptr && p.beta != 0.0f;
-        const bool vec_ok = ((p.ldc | p.ldd | p.strideC | p.strideD) & 3) == 0 &&
-                            ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 15) == 0 &&
-                            ((p.ldp | p.strideP) & 7) == 0 &&
-                            ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dlo)) & 15) == 0;
-        // 256-bit accesses: every 32-column chunk of a row starts on a 32-byte boundary
-        const bool wide_ok = vec_ok && ((p.ldc | p.ldd | p.strideC | p.strideD) & 7) == 0 &&
-                             ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 31) == 0 &&
-                             ((p.ldp | p.strideP) & 15) == 0 &&
-                             ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dlo)) & 31) == 0;
-        if constexpr (KC > 0) {
-            // chunked accumulation: partial sums of KC k-blocks are added in registers
-            int j = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                int tm, tn, b;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
-                const int m0 = tm * BM, n0 = tn * BN;
-                const int row = m0 + warp * 32 + lane;
-                const bool row_ok = row < p.M;
-                float sum[BN];
+        const bool wide_d = ((p.ldc | p.ldd | p.strideC | p.strideD) & 7) == 0 &&
+                            ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 31) == 0;
+        const bool wide_p = ((p.ldp | p.strideP) & 15) == 0 &&
+                            ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dmid) | reinterpret_cast<uintptr_t>(p.Dlo) |
+                              reinterpret_cast<uintptr_t>(p.Thi) | reinterpret_cast<uintptr_t>(p.Tmid) | reinterpret_cast<uintptr_t>(p.Tlo)) & 31) == 0;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            int tm, tn, b;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
+            if (skipped(b)) continue;
+            const int m0 = tm * BM, n0 = tn * BN_ + half * 128;
+            const int row = m0 + quad * 32 + lane;
+            const bool row_ok = row < p.M;
+            const int valid = min(128, p.N - n0);              // columns of this warp's half that exist (may be <= 0)
+            float sum[128];
 #pragma unroll
-                for (int q = 0; q < BN; ++q) sum[q] = 0.0f;
-                const int nchunks = (num_kb + KC - 1) / KC;
-                bool ok = true;
-                for (int ch = 0; ch < nchunks; ++ch, ++j) {
-                    const int acc = j & 1;
-                    ok = mbar_wait_warp(acc_full(acc), (j >> 1) & 1, abort_flag);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
+            for (int q = 0; q < 128; ++q) sum[q] = 0.0f;
+            bool ok = true;
+            for (int ch = 0; ch < nchunks; ++ch, ++j) {
+                const int acc = j & 1;
+                ok = mbar_wait_warp(acc_full(acc), (j >> 1) & 1, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN_ + half * 128);
+                if (valid > 0) {
 #pragma unroll
-                    for (int c = 0; c < BN / 32; ++c) {
+                    for (int c = 0; c < 4; ++c) {
                         float v[32];
-                        tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(c * 32), v);
+                        tmem_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), v);
 #pragma unroll
                         for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
                     }
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
-                }
-                if (!ok) break;
-                if constexpr (QOUT) {
-                    if (row_ok) quantizing_epilogue<BN>(qtab.t, p, sum, b, row, n0);
-                } else
-                if (row_ok && p.D) {
-                    const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
-                    float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + n0;
-                    const int valid = min(BN, p.N - n0);
-                    if (wide_ok && valid == BN) {
-#pragma unroll
-                        for (int q = 0; q < BN; q += 8) {
-                            float cv8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, o[8];
-                            if (has_c) ldg256f(crow + q, cv8);
-#pragma unroll
-                            for (int t = 0; t < 8; ++t) o[t] = fmaf(p.beta, cv8[t], p.alpha * sum[q + t]);
-                            stg256f(drow + q, o);
-                        }
-                    } else
-#pragma unroll
-                    for (int q = 0; q < BN; q += 4) {
-                        if (vec_ok && q + 4 <= valid) {
-                            float4 cval = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (has_c) cval = __ldg(reinterpret_cast<const float4 *>(crow + q));
-                            *reinterpret_cast<float4 *>(drow + q) =
-                                make_float4(fmaf(p.beta, cval.x, p.alpha * sum[q]), fmaf(p.beta, cval.y, p.alpha * sum[q + 1]),
-                                            fmaf(p.beta, cval.z, p.alpha * sum[q + 2]), fmaf(p.beta, cval.w, p.alpha * sum[q + 3]));
-                        } else {
-#pragma unroll
-                            for (int t = 0; t < 4; ++t)
-                                if (q + t < valid)
-                                    drow[q + t] = fmaf(p.beta, has_c ? __ldg(crow + q + t) : 0.0f, p.alpha * sum[q + t]);
-                        }
-                    }
-                }
-            }
-        } else {
-        int i = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
-            int tm, tn, b;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
-            const int m0 = tm * BM, n0 = tn * BN;
-            const int acc = i & 1;
-            const int row = m0 + warp * 32 + lane;
-            const bool row_ok = row < p.M;
-            if constexpr (QOUT) {
-                // result (and C operand) are 4-bit state: one 64-column quantization block at a time
-                const bool okq = mbar_wait_warp(acc_full(acc), (i >> 1) & 1, abort_flag);
-                if (!okq) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
-#pragma unroll 1
-                for (int h = 0; h < BN / 64; ++h) {
-                    float v[64];
-                    {
-                        float t0[32], t1[32];
-                        tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(h * 64), t0);
-                        tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(h * 64 + 32), t1);
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) { v[j] = t0[j]; v[32 + j] = t1[j]; }
-                    }
-                    if (row_ok) quantizing_epilogue<64>(qtab.t, p, v, b, row, n0 + h * 64);
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
-                continue;
             }
-            const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
-            float *drow = p.D + (long long)b * p.strideD + (long long)row * p.ldd + n0;
-            __nv_bfloat16 *hrow = p.Dhi + (long long)b * p.strideP + (long long)row * p.ldp + n0;
-            __nv_bfloat16 *lrow = p.Dlo + (long long)b * p.strideP + (long long)row * p.ldp + n0;
-            float cv[32];
-            auto fetch_c = [&](int c, float (&dst)[32]) {
-                const int valid = p.N - (n0 + c * 32);
-                if (has_c && row_ok && valid > 0) {
-                    if (wide_ok && valid >= 32) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) ldg256f(crow + c * 32 + j, &dst[j]);
-                    } else if (vec_ok && valid >= 32) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            const float4 t = __ldg(reinterpret_cast<const float4 *>(crow + c * 32 + j));
-                            dst[j] = t.x; dst[j + 1] = t.y; dst[j + 2] = t.z; dst[j + 3] = t.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) dst[j] = (j < valid) ? __ldg(crow + c * 32 + j) : 0.0f;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) dst[j] = 0.0f;
-                }
-            };
-            fetch_c(0, cv);
-            const bool ok = mbar_wait_warp(acc_full(acc), (i >> 1) & 1, abort_flag);
             if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                float v[32];
-                tmem_ld32(tmem_acc + ((unsigned)(warp * 32) << 16) + (unsigned)(c * 32), v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, cv[j], p.alpha * v[j]);
-                if (c + 1 < BN / 32) fetch_c(c + 1, cv);
-                const int valid = p.N - (n0 + c * 32);
+            if constexpr (QOUT) {
+                if (row_ok && valid > 0) quantizing_epilogue<128>(qtab.t, p, sum, b, row, n0);
+            } else {
+                const int bo = p.d_slot ? __ldg(p.d_slot + b) : b;
+                float dev = 0.0f;                               // max |result - I| over this thread's elements
                 if (row_ok && valid > 0) {
-                    if (wide_ok && valid >= 32) {
-                        if (p.D) {
+                    const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
+                    float *drow = p.D + (long long)bo * p.strideD + (long long)row * p.ldd + n0;
+                    const long long po = (long long)bo * p.strideP + (long long)row * p.ldp + n0;
+                    const long long to = (long long)b * p.strideP + (long long)row * p.ldp + n0;   // T is stored by matrix number
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) stg256f(drow + c * 32 + j, &v[j]);
+                    for (int q = 0; q < 128; q += 16) {
+                        if (q >= valid) continue;
+                        const bool full16 = q + 16 <= valid;
+                        float o[16];
+                        if (has_c) {
+                            if (full16 && wide_d) { ldg256f(crow + q, o); ldg256f(crow + q + 8, o + 8); }
+                            else {
+#pragma unroll
+                                for (int t = 0; t < 16; ++t) o[t] = (q + t < valid) ? __ldg(crow + q + t) : 0.0f;
+                            }
+#pragma unroll
+                            for (int t = 0; t < 16; ++t) o[t] = fmaf(p.beta, o[t], p.alpha * sum[q + t]);
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 16; ++t) o[t] = p.alpha * sum[q + t];
                         }
-                        if (p.Dhi) {
+                        if (p.D) {
+                            if (full16 && wide_d) { stg256f(drow + q, o); stg256f(drow + q + 8, o + 8); }
+                            else {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 16) {
-                                unsigned h[8], l[8];
-#pragma unroll
-                                for (int q = 0; q < 8; ++q) {
-                                    const __nv_bfloat16 h0 = __float2bfloat16_rn(v[j + 2 * q]), h1 = __float2bfloat16_rn(v[j + 2 * q + 1]);
-                                    const __nv_bfloat16 l0 = __float2bfloat16_rn(v[j + 2 * q] - __bfloat162float(h0));
-                                    const __nv_bfloat16 l1 = __float2bfloat16_rn(v[j + 2 * q + 1] - __bfloat162float(h1));
-                                    h[q] = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
-                                    l[q] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
-                                }
-                                stg256u(hrow + c * 32 + j, h);
-                                stg256u(lrow + c * 32 + j, l);
+                                for (int t = 0; t < 16; ++t) if (q + t < valid) drow[q + t] = o[t];
                             }
                         }
-                    } else if (vec_ok && valid >= 32) {
-                        if (p.D) {
+                        if (p.Dhi) store_planes<NP>(p.Dhi + po + q, NP == 3 ? p.Dmid + po + q : nullptr, p.Dlo + po + q, o,
+                                                    full16 && wide_p, valid - q);
+                        if (p.maxdev || p.Thi) {
+                            const int dcol = row - (n0 + q);    // position of the diagonal inside this group, if any
+                            if (p.maxdev) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4 *>(drow + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        }
-                        if (p.Dhi) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                unsigned h[4], l[4];
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    const __nv_bfloat16 h0 = __float2bfloat16_rn(v[j + 2 * q]), h1 = __float2bfloat16_rn(v[j + 2 * q + 1]);
-                                    const __nv_bfloat16 l0 = __float2bfloat16_rn(v[j + 2 * q] - __bfloat162float(h0));
-                                    const __nv_bfloat16 l1 = __float2bfloat16_rn(v[j + 2 * q + 1] - __bfloat162float(h1));
-                                    h[q] = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
-                                    l[q] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
+                                for (int t = 0; t < 16; ++t) {
+                                    if (q + t < valid) {
+                                        float a = fabsf(o[t] - (t == dcol ? 1.0f : 0.0f));
+                                        if (!(a <= 3.0e38f)) a = CUDART_INF_F;     // NaN or inf: never "converged"
+                                        dev = fmaxf(dev, a);
+                                    }
                                 }
-                                *reinterpret_cast<uint4 *>(hrow + c * 32 + j) = make_uint4(h[0], h[1], h[2], h[3]);
-                                *reinterpret_cast<uint4 *>(lrow + c * 32 + j) = make_uint4(l[0], l[1], l[2], l[3]);
                             }
-                        }
-                    } else {
+                            if (p.Thi) {
+                                float tv[16];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < valid) {
-                                if (p.D) drow[c * 32 + j] = v[j];
-                                if (p.Dhi) {
-                                    const __nv_bfloat16 h = __float2bfloat16_rn(v[j]);
-                                    hrow[c * 32 + j] = h;
-                                    lrow[c * 32 + j] = __float2bfloat16_rn(v[j] - __bfloat162float(h));
-                                }
+                                for (int t = 0; t < 16; ++t) tv[t] = fmaf(p.t_c1, o[t], t == dcol ? p.t_c0 : 0.0f);
+                                store_planes<3>(p.Thi + to + q, p.Tmid + to + q, p.Tlo + to + q, tv, full16 && wide_p, valid - q);
                             }
                         }
                     }
                 }
+                if (p.maxdev) {
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) dev = fmaxf(dev, __shfl_xor_sync(0xffffffffu, dev, off));
+                    if (lane == 0 && dev > 0.0f) atomicMax(reinterpret_cast<int *>(p.maxdev + b), __float_as_int(dev));
+                }
             }
-            // this warp has drained its quarter of the accumulator: let the MMA warp reuse it
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
-        }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == EPI_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
     }
 }
 
@@ -924,6 +891,17 @@ struct GemmArgs {
     void *Dhi, *Dlo; long long ldp, strideP;
 };
 
+// Optional extras of a product (all pointers device memory, any of them may be null).
+struct GemmExtras {
+    void *Dmid = nullptr;                                   // middle result plane (three-plane products)
+    void *Thi = nullptr, *Tmid = nullptr, *Tlo = nullptr;   // t_c0 * I + t_c1 * result, three planes (pitch of the result planes)
+    float t_c0 = 0.0f, t_c1 = 0.0f;
+    float *maxdev = nullptr;                                // per matrix max |result - I|
+    const int *a_slot = nullptr, *b_slot = nullptr, *d_slot = nullptr;
+    const int *active = nullptr;
+    int a_entries = 0, b_entries = 0;                       // matrices in A's / B's storage (0: batch)
+};
+
 static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // 4-bit state operands of the quantizing variant (all device pointers; see GemmParams).
@@ -934,10 +912,50 @@ struct QuantStateArgs {
     long long stride_codes, stride_absmax, stride_diag;
 };
 
-// a.Ahi/Alo (+ amid/bmid for three planes: order hi, mid, lo).  With `qs` the result (and the C
+typedef void (*GemmKern)(const GemmMaps, const GemmParams);
+
+// Kernel table: [tile configuration][A major][B major][quantizing epilogue].
+// Configurations: 0 = two planes, 128 x 128; 1 = two planes, 128 x 256; 2 = three planes, 128 x 128.
+template <int NP, int BN_> static void fill_kernels(GemmKern (&t)[2][2][2]) {
+    t[0][0][0] = k_gemm_bf16x3<false, false, NP, BN_, false>; t[0][0][1] = k_gemm_bf16x3<false, false, NP, BN_, true>;
+    t[0][1][0] = k_gemm_bf16x3<false, true, NP, BN_, false>;  t[0][1][1] = k_gemm_bf16x3<false, true, NP, BN_, true>;
+    t[1][0][0] = k_gemm_bf16x3<true, false, NP, BN_, false>;  t[1][0][1] = k_gemm_bf16x3<true, false, NP, BN_, true>;
+    t[1][1][0] = k_gemm_bf16x3<true, true, NP, BN_, false>;   t[1][1][1] = k_gemm_bf16x3<true, true, NP, BN_, true>;
+}
+static GemmKern g_kernels[3][2][2][2];
+static const int g_cfg_threads[3] = {TileCfg<2, 128>::THREADS, TileCfg<2, 256>::THREADS, TileCfg<3, 128>::THREADS};
+static const int g_cfg_bn[3] = {128, 256, 128};
+
+static bool prepare_kernels() {
+    static bool filled = false;
+    if (!filled) {
+        fill_kernels<2, 128>(g_kernels[0]);
+        fill_kernels<2, 256>(g_kernels[1]);
+        fill_kernels<3, 128>(g_kernels[2]);
+        filled = true;
+    }
+    static PerDeviceOnce attr_done;                      // function attributes are per device
+    const int dev = current_device();
+    if (attr_done.pending(dev)) {
+        for (int i = 0; i < 24; ++i)
+            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(g_kernels[i / 8][(i >> 2) & 1][(i >> 1) & 1][i & 1]),
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
+                return false;
+        attr_done.mark(dev);
+    }
+    return true;
+}
+
+// Test hook: force a tile configuration for two-plane products (-1: choose by problem size).
+static int g_force_bn = -1;
+
+// a.Ahi/Alo (+ Amid/Bmid for three planes: order hi, mid, lo).  With `qs` the result (and the C
 // operand, if qs->q_in) is 4-bit state instead of a.C / a.D.
-int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cudaStream_t s, const QuantStateArgs *qs) {
+int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cudaStream_t s, const QuantStateArgs *qs,
+                       const GemmExtras *ex = nullptr) {
     const int np = (Amid && Bmid) ? 3 : 2;
+    static const GemmExtras none;
+    const GemmExtras &x = ex ? *ex : none;
     if (qs) {
         if (a.M != a.N || a.N % 16 != 0) return record(QT_ERR_UNSUPPORTED);
         if (!qs->code || !qs->q_out || !qs->absmax_out) return record(QT_ERR_ARG);
@@ -949,30 +967,50 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     if (a.M < 0 || a.N < 0 || a.K < 0 || a.batch < 0) return record(QT_ERR_ARG);
     if (a.M == 0 || a.N == 0 || a.batch == 0) return record(QT_OK);
     if (a.K == 0) return record(QT_ERR_UNSUPPORTED);
-    if (!a.Ahi || !a.Alo || !a.Bhi || !a.Blo || (!qs && !a.D && !a.Dhi)) return record(QT_ERR_ARG);
+    if (!a.Ahi || !a.Alo || !a.Bhi || !a.Blo || (!qs && !a.D && !a.Dhi && !x.Thi && !x.maxdev)) return record(QT_ERR_ARG);
     if ((a.Dhi == nullptr) != (a.Dlo == nullptr) || (Amid == nullptr) != (Bmid == nullptr)) return record(QT_ERR_ARG);
+    if (a.Dhi && np == 3 && !x.Dmid) return record(QT_ERR_ARG);                  // three-plane result needs all three planes
+    if (x.Thi && (!x.Tmid || !x.Tlo || np != 3 || a.ldp <= 0)) return record(QT_ERR_ARG);
+    if ((x.Thi || x.maxdev || x.Dmid) && qs) return record(QT_ERR_UNSUPPORTED);
+    const int a_entries = x.a_entries > 0 ? x.a_entries : a.batch, b_entries = x.b_entries > 0 ? x.b_entries : a.batch;
     const void *Ap[3] = {a.Ahi, np == 3 ? Amid : a.Alo, a.Alo};
     const void *Bp[3] = {a.Bhi, np == 3 ? Bmid : a.Blo, a.Blo};
     // TMA: 16-byte aligned bases, row pitches and batch strides
     for (int i = 0; i < np; ++i)
         if (!al16(Ap[i]) || !al16(Bp[i])) return record(QT_ERR_ARG);
     if (a.lda % 8 || a.ldb % 8 || a.strideA % 8 || a.strideB % 8) return record(QT_ERR_ARG);
+    if (!prepare_kernels()) return record(QT_ERR_LAUNCH);
+    const int sms = device_sm_count();
+    const int tiles_m = (a.M + BM - 1) / BM;
+    // tile configuration: the wide tile when it still leaves every SM at least two tiles
+    int cfg = np == 3 ? 2 : 0;
+    if (np == 2 && a.N > 128) {
+        const long long wide_tiles = (long long)tiles_m * ((a.N + 255) / 256) * a.batch;
+        if (wide_tiles >= 2LL * sms) cfg = 1;
+        if (g_force_bn == 128) cfg = 0;
+        if (g_force_bn == 256) cfg = 1;
+    }
+    const int bn = g_cfg_bn[cfg];
     GemmMaps maps;
     bool ok = true;
     for (int i = 0; i < 3; ++i) {
         const void *pa = Ap[i < np ? i : 0], *pb = Bp[i < np ? i : 0];
-        if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);   // stored [M][K]
-        else         ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);   // stored [K][M]
-        if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, a.batch, a.ldb, a.strideB, BK, BN);   // stored [N][K]
-        else         ok = ok && make_map(&maps.b[i], pb, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);   // stored [K][N]
+        if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a_entries, a.lda, a.strideA, BK, BM);   // stored [M][K]
+        else         ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a_entries, a.lda, a.strideA, 64, BK);   // stored [K][M]
+        if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, b_entries, a.ldb, a.strideB, BK, bn);   // stored [N][K]
+        else         ok = ok && make_map(&maps.b[i], pb, a.N, a.K, b_entries, a.ldb, a.strideB, 64, BK);   // stored [K][N]
     }
     if (!ok) return record(QT_ERR_LAUNCH);
     GemmParams p;
     p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch; p.alpha = a.alpha; p.beta = a.beta;
     p.C = a.C; p.ldc = a.ldc; p.strideC = a.strideC; p.D = a.D; p.ldd = a.ldd; p.strideD = a.strideD;
     p.Dhi = static_cast<__nv_bfloat16 *>(a.Dhi); p.Dlo = static_cast<__nv_bfloat16 *>(a.Dlo);
+    p.Dmid = static_cast<__nv_bfloat16 *>(x.Dmid);
     p.ldp = a.ldp; p.strideP = a.strideP;
-    p.tiles_m = (a.M + BM - 1) / BM; p.tiles_n = (a.N + BN - 1) / BN;
+    p.Thi = static_cast<__nv_bfloat16 *>(x.Thi); p.Tmid = static_cast<__nv_bfloat16 *>(x.Tmid); p.Tlo = static_cast<__nv_bfloat16 *>(x.Tlo);
+    p.t_c0 = x.t_c0; p.t_c1 = x.t_c1; p.maxdev = x.maxdev;
+    p.a_slot = x.a_slot; p.b_slot = x.b_slot; p.d_slot = x.d_slot; p.active = x.active;
+    p.tiles_m = tiles_m; p.tiles_n = (a.N + bn - 1) / bn;
     p.q_in = nullptr; p.q_absmax_in = p.q_diag_in = nullptr; p.q_out = nullptr; p.q_absmax_out = p.q_diag_out = nullptr;
     p.q_stride_codes = p.q_stride_absmax = p.q_stride_diag = 0; p.q_code = nullptr; p.q_nb = 0;
     if (qs) {
@@ -983,34 +1021,26 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     }
     const long long ctas = (long long)p.tiles_m * p.tiles_n * a.batch;
     if (ctas > 0x7fffffffLL) return record(QT_ERR_UNSUPPORTED);
-    typedef void (*Kern)(const GemmMaps, const GemmParams);
-    static const Kern kernels[2][2][2] = {
-        {{k_gemm_bf16x3<false, false, 2>, k_gemm_bf16x3<false, true, 2>}, {k_gemm_bf16x3<true, false, 2>, k_gemm_bf16x3<true, true, 2>}},
-        {{k_gemm_bf16x3<false, false, 3>, k_gemm_bf16x3<false, true, 3>}, {k_gemm_bf16x3<true, false, 3>, k_gemm_bf16x3<true, true, 3>}}};
-    static const Kern qkernels[2][2][2] = {
-        {{k_gemm_bf16x3<false, false, 2, true>, k_gemm_bf16x3<false, true, 2, true>},
-         {k_gemm_bf16x3<true, false, 2, true>, k_gemm_bf16x3<true, true, 2, true>}},
-        {{k_gemm_bf16x3<false, false, 3, true>, k_gemm_bf16x3<false, true, 3, true>},
-         {k_gemm_bf16x3<true, false, 3, true>, k_gemm_bf16x3<true, true, 3, true>}}};
-    static PerDeviceOnce attr_done;                      // function attributes are per device
-    const int dev = current_device();
-    if (attr_done.pending(dev)) {
-        for (int i = 0; i < 8; ++i)
-            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(kernels[i >> 2][(i >> 1) & 1][i & 1]),
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
-                return record(QT_ERR_LAUNCH);
-        for (int i = 0; i < 8; ++i)
-            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(qkernels[i >> 2][(i >> 1) & 1][i & 1]),
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
-                return record(QT_ERR_LAUNCH);
-        attr_done.mark(dev);
-    }
-    const int sms = device_sm_count();
     const unsigned grid = (unsigned)(ctas < sms ? ctas : sms);                   // persistent: one CTA per SM
-    if (qs) qkernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
-    else kernels[np - 2][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0]<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(maps, p);
+    g_kernels[cfg][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0][qs ? 1 : 0]<<<grid, g_cfg_threads[cfg], GEMM_SMEM, s>>>(maps, p);
     count_launch(1);
     return check_launch();
+}
+
+// One product of the Newton chain: n x n, three planes in, three planes out (row-major
+// operands: A is K-major, B is MN-major), with the optional extras of GemmExtras.
+int launch_newton_product(void *const A[3], const int *a_slot, int a_entries,
+                          void *const B[3], const int *b_slot, int b_entries,
+                          void *const P[3], const int *d_slot, void *const T[3], float t_c0, float t_c1, float *maxdev,
+                          const int *active, int n, int batch, long long ld, long long stride, cudaStream_t s) {
+    GemmArgs a{A[0], A[2], ld, stride, 0, B[0], B[2], ld, stride, 1, n, n, n, batch, 1.0f, 0.0f,
+               nullptr, 0, 0, nullptr, 0, 0, P[0], P[2], ld, stride};
+    GemmExtras x;
+    x.Dmid = P[1];
+    x.Thi = T[0]; x.Tmid = T[1]; x.Tlo = T[2]; x.t_c0 = t_c0; x.t_c1 = t_c1;
+    x.maxdev = maxdev; x.a_slot = a_slot; x.b_slot = b_slot; x.d_slot = d_slot; x.active = active;
+    x.a_entries = a_entries; x.b_entries = b_entries;
+    return launch_gemm_planes(a, A[1], B[1], s, nullptr, &x);
 }
 
 int launch_gemm_bf16x3(const GemmArgs &a, cudaStream_t s) { return launch_gemm_planes(a, nullptr, nullptr, s, nullptr); }
@@ -1235,6 +1265,23 @@ int qt_matmul_f32_static(const float *A, long long lda, long long strideA, int t
 }
 
 int qt_device_error(int clear) { return read_gemm_error(clear != 0); }
+
+void qt_gemm_force_tile(int bn) { g_force_bn = bn; }
+
+int qt_gemm_ex(const qt_gemm_desc *d, void *stream) {
+    if (!d) return record(QT_ERR_ARG);
+    const bool three = d->A[1] != nullptr || d->B[1] != nullptr;
+    GemmArgs a{d->A[0], d->A[2], d->lda, d->strideA, d->a_mn, d->B[0], d->B[2], d->ldb, d->strideB, d->b_mn,
+               d->M, d->N, d->K, d->batch, d->alpha, d->beta, d->C, d->ldc, d->strideC, d->D, d->ldd, d->strideD,
+               d->P[0], d->P[2], d->ldp, d->strideP};
+    GemmExtras x;
+    x.Dmid = d->P[1];
+    x.Thi = d->T[0]; x.Tmid = d->T[1]; x.Tlo = d->T[2]; x.t_c0 = d->t_c0; x.t_c1 = d->t_c1;
+    x.maxdev = d->maxdev; x.a_slot = d->a_slot; x.b_slot = d->b_slot; x.d_slot = d->d_slot; x.active = d->active;
+    x.a_entries = d->a_entries; x.b_entries = d->b_entries;
+    if (three && (!d->A[1] || !d->B[1])) return record(QT_ERR_ARG);
+    return launch_gemm_planes(a, three ? d->A[1] : nullptr, three ? d->B[1] : nullptr, static_cast<cudaStream_t>(stream), nullptr, &x);
+}
 
 int qt_selftest_wait_timeout(int *gave_up, void *stream) {
     return launch_selftest_wait_timeout(gave_up, static_cast<cudaStream_t>(stream));

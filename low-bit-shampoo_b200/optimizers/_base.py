@@ -536,7 +536,11 @@ class _ShampooBase(optim.Optimizer):
         if len(self.param_groups) != 1 or not hasattr(self, "_graph_scalars"):
             return False
         if self.preconditioner_cls.flavour != "s2" or group.get('inv_root_mode', 0) != 0:
-            return False                                  # the Schur-Newton loop synchronises with the host
+            # the Schur-Newton root runs inside the library without host synchronisation when its
+            # start vectors are drawn on the device (a capture that meets a host sync falls back to eager)
+            from optimizers import matrix_functions as MF
+            if MF.START_VECTORS != "device":
+                return False
         dev = params[0].device
         if dev.type != "cuda" or any(p.device != dev or p.grad.dtype != torch.float32 for p in params):
             return False

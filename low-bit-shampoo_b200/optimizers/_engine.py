@@ -204,6 +204,13 @@ DEQUANTIZE_TO_PLANES = True    # preconditioners are dequantized straight into b
 # processed: those paths have no quantisation noise to hide the ~1e-5 relative error of the
 # split-bf16 products (and the Newton iteration amplifies it), so they stay on fp32 products.
 _EXACT = False
+# The eigenbasis V of the statistics ends up as 4-bit codes: a relative error of 4e-6 in V (what
+# two-plane operands, rounded to 16 significant bits, leave) already flips one code in 10^4, and
+# those flips are what separates two implementations of the step.  With this switch the chain
+# that produces V - L V^T, the far updates of the QR and the accumulation of Q - runs on three
+# planes per operand (fp32-level accuracy) at twice the MMA count of those products.
+PRECISE_BASIS = True
+PRECISE_STATS = False          # experiment: also the rectification and reconstruction of the statistic on three planes
 
 
 class _exact:
@@ -265,8 +272,11 @@ def mm(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, want_flo
     return Mat(out if alpha == 1.0 else out * alpha)
 
 
-def op_bjorck(V, want_planes=False):
+def op_bjorck(V, want_planes=False, exact=False):
     """1.5 V - 0.5 (V V^T) V on the rows of each V in the batch (utils.py:196, functional.py:757)."""
+    if exact and _tc(V.f32):
+        W = mm(V, V, trans_b=True, exact=True)
+        return mm(W, V, alpha=-0.5, beta=1.5, C=V.f32, exact=True)
     W = mm(V, V, trans_b=True, want_float=not _tc(V.f32), want_planes=_tc(V.f32))
     return mm(W, V, alpha=-0.5, beta=1.5, C=V.f32, want_planes=want_planes and _tc(V.f32))
 
@@ -304,7 +314,8 @@ def op_ema_gram(L, G, axis, w1, w2):
 def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
     quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
-    V = householder_q(mm(L, Vt, trans_b=True).f32, tensor_cores=_tc(L.f32))
+    tc = _tc(L.f32)
+    V = householder_q(mm(L, Vt, trans_b=True, exact=PRECISE_BASIS and tc).f32, tensor_cores=tc, precise=PRECISE_BASIS and tc)
     LV = mm(L, Mat(V), exact=True).f32          # Rayleigh quotients need fp32 (see op_ema_gram)
     eigs = (LV * V).sum(dim=1)
     return V, eigs
@@ -501,8 +512,12 @@ def _class_statistics(cls, entries, w1, w2, eps, exact):
             Vt = Mat(cls.stat.dequantize(a, b))
             if cls.stat.lowbit:
                 for _ in range(cls.rect_t1):
-                    Vt = op_bjorck(Vt, want_planes=True)
-            L = op_scaled_gram_gathered(Vt.f32, cls.keep_idx[a:b], cls.S[a:b]).f32
+                    Vt = op_bjorck(Vt, want_planes=True, exact=PRECISE_STATS)
+            if PRECISE_STATS and _tc(Vt.f32):
+                rows = Mat(_gather_rows(Vt.f32, cls.keep_idx[a:b]))
+                L = mm(rows, Mat(cls.S[a:b].unsqueeze(2) * rows.f32), trans_a=True, exact=True).f32
+            else:
+                L = op_scaled_gram_gathered(Vt.f32, cls.keep_idx[a:b], cls.S[a:b]).f32
             L = _ema_update(L, ga, w1, w2)
             V, eigs = op_subspace_step(Mat(L), Vt)
             vals, idx = torch.sort(eigs, dim=1)
@@ -512,18 +527,32 @@ def _class_statistics(cls, entries, w1, w2, eps, exact):
             cls.stat.quantize(a, b, V.transpose(1, 2).contiguous())
 
 
+def _newton_starts(root_items, inv_root_mode):
+    """Start vectors of the power iterations behind the Schur-Newton roots, drawn one matrix at
+    a time in the order the reference reaches them (parameter by parameter, statistic by
+    statistic: shampoo2.py:206-230 -> matrix_functions.py:36), whatever order the classes are
+    processed in afterwards.  {(class, slot): vector}; empty when no class takes the Newton path."""
+    starts = {}
+    for cls, slot in root_items:
+        if (cls.flavour == "s1" or inv_root_mode != 0) and cls.n >= 2:
+            starts[(cls, slot)] = MF.draw_start_vectors(1, cls.n, cls.device)[0]
+    return starts
+
+
 def compute_preconditioners(items, eps, inv_root_mode, exponent=4):
     """items: list of (OrderClass, slot).  Writes L^(-1/exponent) into the preconditioner arenas."""
+    starts = _newton_starts(items, inv_root_mode)
     by_class = defaultdict(list)
     for cls, slot in items:
         by_class[cls].append(slot)
     for cls, slots in _over_classes(by_class):
-        _class_roots(cls, slots, eps, inv_root_mode, exponent)
+        _class_roots(cls, slots, eps, inv_root_mode, exponent, starts)
 
 
 def refresh(stat_items, root_items, w1, w2, eps, inv_root_mode, exact=False, exponent=4):
     """add_statistics followed by compute_preconditioners, pipelined per order class: a class
     starts its inverse roots as soon as its own statistics are done, on the same stream."""
+    starts = _newton_starts(root_items, inv_root_mode)
     stats, roots = defaultdict(list), defaultdict(list)
     for cls, slot, g, axis in stat_items:
         stats[cls].append((slot, g, axis))
@@ -534,10 +563,14 @@ def refresh(stat_items, root_items, w1, w2, eps, inv_root_mode, exact=False, exp
         if entries:
             _class_statistics(cls, entries, w1, w2, eps, exact)
         if slots:
-            _class_roots(cls, slots, eps, inv_root_mode, exponent)
+            _class_roots(cls, slots, eps, inv_root_mode, exponent, starts)
 
 
-def _class_roots(cls, slots, eps, inv_root_mode, exponent):
+def _class_roots(cls, slots, eps, inv_root_mode, exponent, starts=None):
+        def v0_of(a, b):
+            if not starts:
+                return None
+            return torch.stack([starts[(cls, s)] for s in range(a, b)])
         for a, b, _ in _split_runs(_runs(slots), cls.sub_batch()):
           with _exact((not cls.stat.lowbit) or cls.flavour == "s1" or inv_root_mode != 0):
             if cls.flavour == "s1":
@@ -545,7 +578,7 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent):
                     L = _eps_identity(cls, b - a, eps)
                 else:
                     L = cls.stat.dequantize(a, b)
-                P = MF.ComputePower(L, exponent, ridge_epsilon=eps)
+                P = MF.ComputePower(L, exponent, ridge_epsilon=eps, v0=v0_of(a, b))
             elif inv_root_mode == 0:
                 Vt = cls.stat.dequantize(a, b)
                 rows = Mat(_gather_rows(Vt, cls.keep_idx[a:b]))
@@ -566,7 +599,7 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent):
                     for _ in range(cls.rect_t1):
                         Vt = op_bjorck(Vt)
                 rows = Mat(_gather_rows(Vt.f32, cls.keep_idx[a:b]))
-                P = MF.ComputePower(op_scaled_gram(rows, cls.S[a:b]).f32, exponent, ridge_epsilon=eps)
+                P = MF.ComputePower(op_scaled_gram(rows, cls.S[a:b]).f32.contiguous(), exponent, ridge_epsilon=eps, v0=v0_of(a, b))
             cls.prec.quantize(a, b, P)
 
 

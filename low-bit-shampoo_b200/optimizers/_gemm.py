@@ -29,7 +29,8 @@ class Planes:
         self.batch, self.rows, self.cols = batch, rows, cols
         self.mid = None
         if _share is not None:
-            self.hi, self.lo, self.ld, self.stride, self.offset = _share
+            self.hi, self.lo, self.ld, self.stride, self.offset = _share[:5]
+            self.mid = _share[5] if len(_share) > 5 else None
             return
         self.ld = _pitch(cols)
         self.stride = rows * self.ld
@@ -43,7 +44,7 @@ class Planes:
         """Planes of the sub-matrix [row0:row0+rows, col0:col0+cols]; col0 must be a multiple of 8."""
         assert col0 % 8 == 0 and row0 + rows <= self.rows and col0 + cols <= self.cols
         return Planes(self.batch, rows, cols, self.hi.device,
-                      _share=(self.hi, self.lo, self.ld, self.stride, self.offset + row0 * self.ld + col0))
+                      _share=(self.hi, self.lo, self.ld, self.stride, self.offset + row0 * self.ld + col0, self.mid))
 
     def ptr_hi(self):
         return ct.c_void_p(self.hi.data_ptr() + 2 * self.offset)
@@ -51,9 +52,15 @@ class Planes:
     def ptr_lo(self):
         return ct.c_void_p(self.lo.data_ptr() + 2 * self.offset)
 
+    def ptr_mid(self):
+        return None if self.mid is None else ct.c_void_p(self.mid.data_ptr() + 2 * self.offset)
+
     def to_float(self):
         n = (self.rows - 1) * self.ld + self.cols
         idx = self.hi[:, self.offset: self.offset + n].float() + self.lo[:, self.offset: self.offset + n].float()
+        if self.mid is not None:
+            idx = (self.hi[:, self.offset: self.offset + n].float() + self.mid[:, self.offset: self.offset + n].float()) + \
+                self.lo[:, self.offset: self.offset + n].float()
         full = torch.zeros(self.batch, self.rows * self.ld, device=idx.device)
         full[:, :n] = idx
         return full.view(self.batch, self.rows, self.ld)[:, :, : self.cols]
@@ -130,11 +137,19 @@ def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=
     a_mn = 1 if trans_a else 0
     b_mn = 0 if trans_b else 1
     if A.mid is not None or B.mid is not None:
-        assert A.mid is not None and B.mid is not None and P is None and D is not None
+        assert A.mid is not None and B.mid is not None
+        if P is not None:
+            # fp32-level product whose result is also handed on as three planes
+            if out_planes is None:
+                P = Planes(b, M, N, dev, planes=3)
+            assert P.mid is not None
+            gemm_ex(A, B, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C, D=D, P=P)
+            return D, P
+        assert D is not None
         with torch.cuda.device(dev):
             rc = F.lib.qt_gemm_bf16x6(
-                A.ptr_hi(), _ptr(A.mid), A.ptr_lo(), A.ld, A.stride, a_mn,
-                B.ptr_hi(), _ptr(B.mid), B.ptr_lo(), B.ld, B.stride, b_mn,
+                A.ptr_hi(), A.ptr_mid(), A.ptr_lo(), A.ld, A.stride, a_mn,
+                B.ptr_hi(), B.ptr_mid(), B.ptr_lo(), B.ld, B.stride, b_mn,
                 M, N, K, b, float(alpha), float(beta),
                 _ptr(C), C.stride(1) if C is not None else 0, C.stride(0) if C is not None else 0,
                 _ptr(D), D.stride(1), D.stride(0), F._stream(A.hi))
@@ -191,3 +206,37 @@ def matmul_q4(A, B, code, out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0
                 A.ptr_hi(), A.ptr_lo(), A.ld, A.stride, 1 if trans_a else 0,
                 B.ptr_hi(), B.ptr_lo(), B.ld, B.stride, 0 if trans_b else 1, *tail)
     F._check(rc, "gemm_q4")
+
+
+def gemm_ex(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, D=None, P=None, T=None, t_c0=0.0, t_c1=0.0,
+            maxdev=None, a_slot=None, b_slot=None, d_slot=None, active=None, batch=None):
+    """General product (qt_gemm_ex): A, B are Planes (two- or three-plane, possibly holding more
+    entries than `batch` when slot arrays select among them); results go to the fp32 tensor D and / or
+    the Planes P, and optionally T = t_c0 * I + t_c1 * result (three planes, indexed by matrix number).
+    maxdev: fp32 (batch,) combined with max |result - I|; *_slot, active: int32 (batch,) device tensors."""
+    from qtensor.cextension import GemmDesc
+    M = A.cols if trans_a else A.rows
+    K = A.rows if trans_a else A.cols
+    N = B.rows if trans_b else B.cols
+    b = batch if batch is not None else A.batch
+    d = GemmDesc()
+    ip = lambda t: None if t is None else t.data_ptr()
+    po = lambda X, t: None if t is None else t.data_ptr() + 2 * X.offset
+    d.A[0], d.A[1], d.A[2] = po(A, A.hi), po(A, A.mid), po(A, A.lo)
+    d.B[0], d.B[1], d.B[2] = po(B, B.hi), po(B, B.mid), po(B, B.lo)
+    d.lda, d.strideA, d.a_mn, d.a_entries = A.ld, A.stride, 1 if trans_a else 0, A.batch
+    d.ldb, d.strideB, d.b_mn, d.b_entries = B.ld, B.stride, 0 if trans_b else 1, B.batch
+    d.M, d.N, d.K, d.batch, d.alpha, d.beta = M, N, K, b, float(alpha), float(beta)
+    if C is not None:
+        d.C, d.ldc, d.strideC = C.data_ptr(), C.stride(1), C.stride(0)
+    if D is not None:
+        d.D, d.ldd, d.strideD = D.data_ptr(), D.stride(1), D.stride(0)
+    for X, field in ((P, d.P), (T, d.T)):
+        if X is not None:
+            field[0], field[1], field[2] = po(X, X.hi), po(X, X.mid), po(X, X.lo)
+            d.ldp, d.strideP = X.ld, X.stride
+    d.t_c0, d.t_c1 = float(t_c0), float(t_c1)
+    d.maxdev, d.a_slot, d.b_slot, d.d_slot, d.active = ip(maxdev), ip(a_slot), ip(b_slot), ip(d_slot), ip(active)
+    with torch.cuda.device(A.hi.device):
+        rc = F.lib.qt_gemm_ex(ct.byref(d), F._stream(A.hi))
+    F._check(rc, "gemm_ex")

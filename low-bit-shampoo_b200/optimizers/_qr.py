@@ -28,18 +28,20 @@ USE_TENSOR_CORES = True     # rank-128 far updates on the tcgen05 kernel (panel-
 def _reflect(Vk, Tk, target, target_planes, transpose_t, Pv=None):
     """target <- (I - Vk T Vk^T) target (or with T^T), fp32 in place; when `target_planes` (the
     bf16 planes of `target`) is given the two large products run on the tensor cores and the
-    planes are kept in step with the fp32 values.  `Pv`: planes of Vk if the caller has them."""
+    planes are kept in step with the fp32 values.  `Pv`: planes of Vk if the caller has them.
+    Two-plane or three-plane operands alike (the planes decide the kernel)."""
     from optimizers import _gemm
     if target_planes is None:
         W = torch.bmm(Vk.transpose(1, 2), target)
         W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
         target.baddbmm_(Vk, W, alpha=-1.0)
         return
+    split = _gemm.split3 if target_planes.mid is not None else _gemm.split
     if Pv is None:
-        Pv = _gemm.split(Vk)
+        Pv = split(Vk)
     W, _ = _gemm.matmul(Pv, target_planes, trans_a=True)                   # Vk^T target, (w x t)
     W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
-    _gemm.matmul(Pv, _gemm.split(W), alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
+    _gemm.matmul(Pv, split(W), alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes, want_planes=True)
 
 
 def _merge_t(Vo, Tp, widths, Pv=None):
@@ -76,9 +78,11 @@ def _merge_t(Vo, Tp, widths, Pv=None):
     return T
 
 
-def householder_q(X, tensor_cores=True):
+def householder_q(X, tensor_cores=True, precise=False):
     """Q of the QR factorisation of each X[b] (X: (B, n, n) fp32 CUDA, overwritten).
-    `tensor_cores=False` keeps every product in fp32."""
+    `tensor_cores=False` keeps every product in fp32 library products; `precise` runs the
+    tensor-core products on three bf16 planes per operand (fp32-level accuracy, twice the MMAs)
+    instead of two (operands rounded to 16 significant bits)."""
     B, n, _ = X.shape
     if (not X.is_cuda) or n > MAX_ORDER or n < 2:
         return torch.linalg.qr(X).Q
@@ -92,8 +96,9 @@ def householder_q(X, tensor_cores=True):
     T = torch.empty(B, npan, PANEL, PANEL, dtype=torch.float32, device=X.device)
     stream = F._stream(X)
     blocks = []                                           # (J0, wo, T_big)
+    split = _gemm.split3 if precise else _gemm.split
     with torch.cuda.device(X.device):
-        Xp = _gemm.split(X) if tc else None
+        Xp = split(X) if tc else None
         for J0 in range(0, n, OUTER):
             wo = min(OUTER, n - J0)
             widths = []
@@ -107,14 +112,14 @@ def householder_q(X, tensor_cores=True):
                 if j0 + w < J0 + wo:                      # rest of this outer block: rank-32 update in fp32
                     _reflect(V[:, j0:, j0:j0 + w], T[:, k, :w, :w], X[:, j0:, j0 + w:J0 + wo], None, True)
             Vo = V[:, J0:, J0:J0 + wo]
-            Pv = _gemm.split(Vo) if tc else None          # shared by the merge, the far update and the accumulation of Q
+            Pv = split(Vo) if tc else None                # shared by the merge, the far update and the accumulation of Q
             Tb = _merge_t(Vo, T[:, J0 // PANEL:], widths, Pv)
             blocks.append((J0, wo, Tb, Pv))
             if J0 + wo < n:
                 m, t = n - J0, n - J0 - wo
                 _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True, Pv)
         Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
-        Qp = _gemm.split(Q) if tc else None
+        Qp = split(Q) if tc else None
         for J0, wo, Tb, Pv in reversed(blocks):
             m = n - J0
             _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False, Pv)

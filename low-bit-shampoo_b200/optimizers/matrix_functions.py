@@ -2,15 +2,45 @@
 
 Same names and return values as the reference's optimizers/matrix_functions.py
 (PowerIter :22-48, MatPower :52-76, ComputePower :80-141).  Each function also accepts a
-batch (m, n, n): every matrix follows its own stopping rule through masks, so a whole
-order class runs as batched products with no per-matrix host synchronisation (the
-reference synchronises twice per Newton iteration per matrix, :131,:136).
+batch (m, n, n): every matrix follows its own stopping rule, so a whole order class runs
+together with no per-matrix host synchronisation (the reference synchronises twice per
+Newton iteration per matrix, :131,:136).
+
+CUDA fp32 input runs inside the native library: one fused power-iteration kernel, then the
+Newton chain root T, T^2, T^4, T^4 M as three-plane tcgen05 products whose epilogues write
+the next product's operands, reduce max |M - I| and obey per-matrix accept / stop flags in
+device memory (qt_inverse_root_newton).  CPU tensors (the 32-bit mode the reference itself runs
+in on CPU) take the batched torch statement of the same algorithm below.
 """
+import ctypes as ct
+
 import torch
 
+import qtensor.functional as F
 
-def _bmm(a, b):
-    return torch.matmul(a, b)
+# Where the start vector of the power iteration comes from when the caller gives none.  The
+# reference draws torch.rand(n, device=mat.device) * 2 - 1 once per matrix (:36), i.e. from the
+# generator of the matrix's device: "device" does exactly that, one draw per matrix in batch
+# order.  "host" draws from the CPU generator instead (what the reference does when it runs on CPU
+# tensors); it exists so that a CUDA run can be compared with CPU-generated reference results and
+# is not usable under CUDA-graph capture.
+START_VECTORS = "device"
+_WORKSPACE_CAP = 6 << 30           # bytes of Newton workspace per launch group; larger batches are cut
+
+
+def _ptr(t):
+    return None if t is None else ct.c_void_p(t.data_ptr())
+
+
+def draw_start_vectors(m, n, device):
+    """m start vectors of length n, uniform in (-1, 1), drawn one matrix at a time (the reference's order)."""
+    if START_VECTORS == "host" or torch.device(device).type != "cuda":
+        return torch.stack([torch.rand(n) * 2 - 1 for _ in range(m)]).to(device)
+    return torch.stack([torch.rand(n, device=device) * 2 - 1 for _ in range(m)])
+
+
+def _native(G):
+    return (G.is_cuda and G.dtype == torch.float32 and F.lib is not None and G.shape[-1] >= 2 and G.shape[-1] <= 25000)
 
 
 @torch.no_grad()
@@ -24,9 +54,23 @@ def PowerIter(mat_g, error_tolerance=1e-6, num_iters=10, v0=None):
     G = mat_g if batched else mat_g.unsqueeze(0)
     m, n = G.shape[0], G.shape[-1]
     if v0 is None:
-        v = torch.rand(m, n, device=G.device) * 2 - 1
+        v = draw_start_vectors(m, n, G.device)
     else:
         v = v0.reshape(m, n).to(G.device, torch.float32).clone()
+    if _native(G):
+        Gc = G.contiguous()
+        v = v.contiguous()
+        sval = torch.empty(m, device=G.device)
+        iters = torch.empty(m, dtype=torch.int32, device=G.device)
+        vec = torch.empty(m, n, device=G.device)
+        with torch.cuda.device(G.device):
+            rc = F.lib.qt_power_iter(_ptr(Gc), n * n, n, m, _ptr(v), float(error_tolerance), int(num_iters),
+                                     _ptr(sval), _ptr(iters), _ptr(vec), F._stream(Gc))
+        F._check(rc, "power iteration")
+        vec = vec / torch.linalg.vector_norm(vec, dim=1, keepdim=True)
+        if batched:
+            return sval, vec, iters.to(torch.int64)
+        return sval[0], vec[0], int(iters[0])
     sval = torch.zeros(m, device=G.device)
     active = torch.ones(m, dtype=torch.bool, device=G.device)
     iters = torch.zeros(m, dtype=torch.int64, device=G.device)
@@ -45,22 +89,52 @@ def PowerIter(mat_g, error_tolerance=1e-6, num_iters=10, v0=None):
     return sval[0], vec[0], int(iters[0])
 
 
+def _mm(a, b):
+    """a @ b for batches; CUDA fp32 operands run on the three-plane tcgen05 product."""
+    if a.dim() == 3 and _native(a) and a.shape == b.shape:
+        from optimizers import _gemm
+        D, _ = _gemm.matmul(_gemm.split3(a.contiguous()), _gemm.split3(b.contiguous()))
+        return D
+    return torch.matmul(a, b)
+
+
 @torch.no_grad()
 def MatPower(mat_m, p):
     """mat_m ** p for a positive integer p (repeated squaring)."""
+    single = mat_m.dim() == 2
+    M = mat_m.unsqueeze(0) if single else mat_m
     if p in (1, 2, 4, 8, 16, 32):
-        out, done = mat_m, 1
+        out, done = M, 1
         while done < p:
-            out = _bmm(out, out)
+            out = _mm(out, out)
             done *= 2
-        return out
-    acc = None
-    while p > 0:
-        if p % 2 == 1:
-            acc = _bmm(mat_m, acc) if acc is not None else mat_m
-        p //= 2
-        mat_m = _bmm(mat_m, mat_m)
-    return acc
+    else:
+        out = None
+        while p > 0:
+            if p % 2 == 1:
+                out = _mm(M, out) if out is not None else M
+            p //= 2
+            M = _mm(M, M)
+    return out[0] if single else out
+
+
+def _compute_power_native(G, p, iter_count, error_tolerance, ridge_epsilon, v0):
+    """Batched inverse root inside the library.  G: (m, n, n) CUDA fp32 contiguous, modified in place."""
+    m, n = G.shape[0], G.shape[-1]
+    lib = F.lib
+    out = torch.empty_like(G)
+    per = int(lib.qt_inverse_root_newton_workspace_bytes(n, 1))
+    chunk = max(1, min(m, _WORKSPACE_CAP // max(per, 1)))
+    with torch.cuda.device(G.device):
+        for a in range(0, m, chunk):
+            b = min(m, a + chunk)
+            need = int(lib.qt_inverse_root_newton_workspace_bytes(n, b - a))
+            ws = torch.empty(need, dtype=torch.uint8, device=G.device)
+            rc = lib.qt_inverse_root_newton(_ptr(G[a:b]), n * n, n, b - a, int(p), int(iter_count), float(error_tolerance),
+                                            float(ridge_epsilon), _ptr(v0[a:b]), _ptr(ws), need, _ptr(out[a:b]), n * n,
+                                            None, None, F._stream(G))
+            F._check(rc, "inverse root (Newton)")
+    return out
 
 
 @torch.no_grad()
@@ -76,6 +150,12 @@ def ComputePower(mat_g, p, iter_count=10, error_tolerance=1e-6, ridge_epsilon=1e
     eye = torch.eye(n, device=G.device)
     if n == 1:
         return eye.expand(m, 1, 1).clone() if batched else eye
+    if _native(G) and G.is_contiguous() and p >= 2 and (p & (p - 1)) == 0 and p <= 64:
+        if v0 is None:
+            v0 = draw_start_vectors(m, n, G.device)
+        v0 = v0.reshape(m, n).to(G.device, torch.float32).contiguous()
+        root = _compute_power_native(G, p, iter_count, error_tolerance, ridge_epsilon, v0)
+        return root if batched else root[0]
     alpha = -1.0 / p
     max_ev, _, _ = PowerIter(G, v0=v0)
     G.diagonal(dim1=1, dim2=2).add_((ridge_epsilon * max_ev).unsqueeze(1))
@@ -88,8 +168,8 @@ def ComputePower(mat_g, p, iter_count=10, error_tolerance=1e-6, ridge_epsilon=1e
         if not bool(active.any()):
             break
         T = (1 - alpha) * eye + alpha * M
-        new_root = _bmm(root, T)
-        new_M = _bmm(MatPower(T, p), M)
+        new_root = torch.matmul(root, T)
+        new_M = torch.matmul(MatPower(T, p), M)
         new_err = (new_M - eye).abs().amax(dim=(1, 2))
         accept = active & ~(new_err > err * 1.2)
         sel = accept.view(m, 1, 1)

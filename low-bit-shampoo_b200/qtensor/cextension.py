@@ -21,10 +21,24 @@ LEGACY_SYMBOLS = tuple(
 )
 EXTRA_SYMBOLS = (
     "qt_version", "qt_launch_count", "qt_note_graph_replay", "qt_last_error", "qt_error_string", "qt_set_stream",
-    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_dequantize_planes", "qt_householder_panel", "qt_merge_t", "qt_selftest_division", "qt_split_bf16", "qt_split_bf16_rows", "qt_gemm_bf16x3", "qt_split_bf16_3", "qt_gemm_bf16x6", "qt_gemm_bf16x3_q4", "qt_gemm_bf16x6_q4", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error", "qt_adamw_tail", "qt_selftest_wait_timeout",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_dequantize_planes", "qt_householder_panel", "qt_merge_t", "qt_selftest_division", "qt_split_bf16", "qt_split_bf16_rows", "qt_gemm_bf16x3", "qt_split_bf16_3", "qt_gemm_bf16x6", "qt_gemm_bf16x3_q4", "qt_gemm_bf16x6_q4", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error", "qt_adamw_tail", "qt_selftest_wait_timeout", "qt_gemm_ex", "qt_gemm_force_tile", "qt_power_iter",
+    "qt_inverse_root_newton", "qt_inverse_root_newton_workspace_bytes",
 )
 
 _lib = None
+
+
+class GemmDesc(ct.Structure):
+    """Mirror of qt_gemm_desc (include/qtensor_b200.h)."""
+    _fields_ = [("A", ct.c_void_p * 3), ("lda", ct.c_longlong), ("strideA", ct.c_longlong), ("a_mn", ct.c_int), ("a_entries", ct.c_int),
+                ("B", ct.c_void_p * 3), ("ldb", ct.c_longlong), ("strideB", ct.c_longlong), ("b_mn", ct.c_int), ("b_entries", ct.c_int),
+                ("M", ct.c_int), ("N", ct.c_int), ("K", ct.c_int), ("batch", ct.c_int), ("alpha", ct.c_float), ("beta", ct.c_float),
+                ("C", ct.c_void_p), ("ldc", ct.c_longlong), ("strideC", ct.c_longlong),
+                ("D", ct.c_void_p), ("ldd", ct.c_longlong), ("strideD", ct.c_longlong),
+                ("P", ct.c_void_p * 3), ("ldp", ct.c_longlong), ("strideP", ct.c_longlong),
+                ("T", ct.c_void_p * 3), ("t_c0", ct.c_float), ("t_c1", ct.c_float),
+                ("maxdev", ct.c_void_p),
+                ("a_slot", ct.c_void_p), ("b_slot", ct.c_void_p), ("d_slot", ct.c_void_p), ("active", ct.c_void_p)]
 
 
 def library_path() -> Path:
@@ -85,6 +99,16 @@ def _declare(lib):
                                          vp, i64, i64, vp, i64, i64, vp]
     lib.qt_device_error.restype = i32
     lib.qt_device_error.argtypes = [i32]
+    lib.qt_gemm_ex.restype = i32
+    lib.qt_gemm_ex.argtypes = [ct.POINTER(GemmDesc), vp]
+    lib.qt_gemm_force_tile.restype = None
+    lib.qt_gemm_force_tile.argtypes = [i32]
+    lib.qt_power_iter.restype = i32
+    lib.qt_power_iter.argtypes = [vp, i64, i32, i32, vp, f32, i32, vp, vp, vp, vp]
+    lib.qt_inverse_root_newton_workspace_bytes.restype = ct.c_ulonglong
+    lib.qt_inverse_root_newton_workspace_bytes.argtypes = [i32, i32]
+    lib.qt_inverse_root_newton.restype = i32
+    lib.qt_inverse_root_newton.argtypes = [vp, i64, i32, i32, i32, i32, f32, f32, vp, vp, ct.c_ulonglong, vp, i64, vp, vp, vp]
     lib.qt_selftest_wait_timeout.restype = i32
     lib.qt_selftest_wait_timeout.argtypes = [vp, vp]
     for name in LEGACY_SYMBOLS:
