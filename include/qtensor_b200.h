@@ -40,6 +40,7 @@ extern "C" {
 #define QT_ERR_UNSUPPORTED    6   /* shape outside what the kernel family supports       */
 #define QT_ERR_TIMEOUT        7   /* a bounded device-side wait gave up                  */
 #define QT_ERR_TOO_LARGE      8   /* operands exceed the fixed scratch of a *_static call */
+#define QT_ERR_RANGE          9   /* a value left the range of a scaled fp16 operand plane */
 
 /* Size of the built-in scratch array used by qt_matmul_f32_static (16 MiB per GPU). */
 #define QT_STATIC_SCRATCH_BYTES (16u << 20)
@@ -130,6 +131,17 @@ int qt_dequantize_planes(const unsigned char *A, long long strideA, const float 
                          const float *absmax, long long stride_absmax, const float *diag, long long stride_diag,
                          const int *slots, void *hi, void *lo, long long ldp, long long strideP,
                          int blocksize, int bits, void *stream);
+
+/*
+ * qt_dequantize_planes into SCALED FP16 planes (operands of qt_gemm_ex with f16 != 0): entry =
+ * value * 2^e[j], e[j] chosen from the largest magnitude matrix j can hold (its block scales and
+ * fp32 diagonal) so that it lands just below 2^target; e is written to exp_out (count int32),
+ * amax_scratch is `count` floats of device scratch.  22 significant bits instead of 16.
+ */
+int qt_dequantize_planes_f16(const unsigned char *A, long long strideA, const float *code, int order, int count,
+                             const float *absmax, long long stride_absmax, const float *diag, long long stride_diag,
+                             const int *slots, float *amax_scratch, int target, int *exp_out,
+                             void *hi, void *lo, long long ldp, long long strideP, int blocksize, int bits, void *stream);
 
 /*
  * Self-test of the quantizer's division: the kernels replace x / absmax by an exact
@@ -237,8 +249,21 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
  *   - a_slot / b_slot / d_slot: per matrix, which entry of A's / B's storage is read and which
  *     entry of the outputs is written (NULL: the matrix number); a_entries / b_entries give the
  *     number of matrices in A's / B's storage (0: batch);
- *   - active: per matrix, 0 = skip all tiles of this matrix (NULL: none skipped).
- * All index and flag arrays are device int32 arrays read when the kernel runs.
+ *   - active: per matrix, 0 = skip all tiles of this matrix (NULL: none skipped);
+ *   - f16 != 0 (two-plane products): the planes are SCALED FP16 planes - an entry holds
+ *     value * 2^(exp[entry] + exp0) as hi = fp16(.), lo = fp16(. - hi), 22 significant bits while
+ *     the scaled values stay within fp16's normal range (qt_planes_exponents picks exponents from
+ *     each matrix's largest magnitude).  a_exp / b_exp: per storage entry exponents (NULL: 0),
+ *     ab_exp0: sum of the two common parts; the epilogue undoes the scaling.  Plane output P
+ *     then is fp16 too, entry = value * 2^e with e = out_exp[entry] + out_exp0 if out_exp is
+ *     given, else (out_rel != 0) the operands' exponents + out_exp0, else out_exp0; e is written
+ *     to out_exp_w[entry] if that is given.  A value that leaves the fp16 range is clamped and
+ *     sets the sticky device error QT_ERR_RANGE.  kc: k-blocks (of 64) per accumulation chain in
+ *     tensor memory, partial sums added in fp32 registers (0: one chain; the tensor core's
+ *     accumulation truncates, so long chains lose about 6.5e-9 * K);
+ *   - q_out != NULL: the result is written as 4-bit state exactly as qt_gemm_bf16x3_q4 does
+ *     (q_* fields as that function's arguments), instead of D / P.
+ * All index, exponent and flag arrays are device int32 arrays read when the kernel runs.
  */
 typedef struct qt_gemm_desc {
     const void *A[3]; long long lda, strideA; int a_mn, a_entries;
@@ -250,6 +275,11 @@ typedef struct qt_gemm_desc {
     void *T[3]; float t_c0, t_c1;
     float *maxdev;
     const int *a_slot, *b_slot, *d_slot, *active;
+    int f16, ab_exp0, out_exp0, out_rel, kc;
+    const int *a_exp, *b_exp, *out_exp; int *out_exp_w;
+    const float *q_code; const unsigned char *q_in; const float *q_absmax_in, *q_diag_in;
+    unsigned char *q_out; float *q_absmax_out, *q_diag_out;
+    long long q_stride_codes, q_stride_absmax, q_stride_diag;
 } qt_gemm_desc;
 int qt_gemm_ex(const qt_gemm_desc *desc, void *stream);
 
@@ -283,6 +313,21 @@ unsigned long long qt_inverse_root_newton_workspace_bytes(int n, int batch);
 int qt_inverse_root_newton(float *G, long long strideG, int n, int batch, int p, int iter_count, float tol, float ridge_eps,
                            const float *v0, void *workspace, unsigned long long workspace_bytes,
                            float *out, long long strideOut, float *max_ev, int *iters, void *stream);
+
+/*
+ * fp32 matrices -> scaled fp16 planes (the operand format of qt_gemm_ex with f16 != 0), with the
+ * optional row gather and row scale of qt_split_bf16_rows.  Plane entry = x * 2^e[b] as
+ * hi = fp16(.), lo = fp16(. - hi).  Exponents:
+ *   amax_scratch != NULL: e[b] is chosen from the largest magnitude of matrix b so that it lands
+ *     just below 2^target_or_exp0 (amax_scratch: `batch` floats of device scratch, overwritten);
+ *   amax_scratch == NULL: e[b] = exp_in[b] (NULL: 0) + target_or_exp0.
+ * exp_out (may be NULL) receives e[b].  Additive; the reference multiplies fp32 tensors with
+ * torch.matmul (e.g. optimizers/shampoo2.py:188-190).
+ */
+int qt_split_f16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                 const long long *index, long long stride_index, const float *scale, long long stride_scale,
+                 float *amax_scratch, const int *exp_in, int target_or_exp0, int *exp_out,
+                 void *hi, void *lo, long long ldp, long long strideP, void *stream);
 
 /* Test hook: 128 or 256 forces the output-tile width of two-plane products, -1 restores the
  * choice by problem size.  Additive; no counterpart in the reference. */

@@ -90,6 +90,7 @@ const char *qt_error_string(int status) {
         case QT_ERR_DTYPE: return "dtype tag must be QT_F32 or QT_BF16";
         case QT_ERR_UNSUPPORTED: return "shape not supported by this kernel family";
         case QT_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case QT_ERR_RANGE: return "a value left the range of a scaled fp16 operand plane (operand exponents too large for the data)";
         case QT_ERR_TOO_LARGE: return "operands need more scratch than the library's fixed 16 MiB array holds";
         default: return "unknown status";
     }
@@ -119,6 +120,16 @@ int qt_dequantize_planes(const unsigned char *A, long long strideA, const float 
     DequantArgs a{A, strideA, code, order, count, blocksize, bits, absmax, stride_absmax,
                   diag, stride_diag, nullptr, QT_BF16, 0};
     return launch_dequantize_planes(a, slots, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
+}
+
+int qt_dequantize_planes_f16(const unsigned char *A, long long strideA, const float *code, int order, int count,
+                             const float *absmax, long long stride_absmax, const float *diag, long long stride_diag,
+                             const int *slots, float *amax_scratch, int target, int *exp_out,
+                             void *hi, void *lo, long long ldp, long long strideP, int blocksize, int bits, void *stream) {
+    if (!amax_scratch) return record(QT_ERR_ARG);
+    DequantArgs a{A, strideA, code, order, count, blocksize, bits, absmax, stride_absmax,
+                  diag, stride_diag, nullptr, QT_BF16, 0};
+    return launch_dequantize_planes(a, slots, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream), amax_scratch, target, exp_out);
 }
 
 int qt_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches, void *stream) {

@@ -24,6 +24,7 @@
 // Every wait is bounded: on expiry the kernel records an error word and drains.
 #include "quant_device.cuh"
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 namespace qt {
 
@@ -60,6 +61,12 @@ struct GemmParams {
     float *maxdev;                                                        // per matrix: max |result - I| (atomic max)
     const int *a_slot, *b_slot, *d_slot;                                  // per matrix: entry of A / B / outputs (null: the matrix number)
     const int *active;                                                    // per matrix: 0 = skip (null: all)
+    // Scaled fp16 planes (two-plane kernels): a plane entry holds value * 2^(exp[entry] + exp0).
+    int f16;                                                              // operands and plane outputs are fp16 (else bf16, unscaled)
+    const int *a_exp, *b_exp; int ab_exp0;                                // per storage entry exponents of A and B (null: 0) + common part
+    const int *out_exp; int *out_exp_w; int out_exp0, out_rel;            // exponent of the plane output: given per entry, or
+                                                                          // (out_rel) operand exponents + out_exp0; written to out_exp_w
+    int kc;                                                               // k-blocks per accumulation chain (two-plane kernels)
     int tiles_m, tiles_n;
     // 4-bit state as C operand and as result (QOUT kernels only): block size 64, order N == M
     const unsigned char *q_in; const float *q_absmax_in, *q_diag_in;      // q_in == nullptr: no C operand
@@ -119,7 +126,10 @@ __device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity, vo
                          : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
             if (ok) break;
             if ((it & 255u) == 255u && *abort_flag) break;
-            __nanosleep(40);
+            // try_wait already suspends the thread for a while; an extra sleep only pays once the
+            // wait is clearly a long one (an accumulator hand-off every few hundred cycles must not
+            // be delayed by a sleep that overshoots)
+            if (it > 32u) __nanosleep(20);
         }
         if (!ok && !*abort_flag) {
             *abort_flag = 1;
@@ -195,7 +205,7 @@ struct GemmMaps { CUtensorMap a[3]; CUtensorMap b[3]; };
 // written by this thread only, reads first.
 template <int LEN>
 __device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, const GemmParams &p, float (&sum)[LEN],
-                                                    int b, int row, int n0) {
+                                                    int b, int row, int n0, float alpha) {
     const bool lean_launch = !tab.lut_bad && !tab.need_clamp && tab.perm_identity && !tab.tiny_thr;
     const float lut_scale = tab.lut_scale;
 #pragma unroll
@@ -222,7 +232,7 @@ __device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, c
                         const unsigned idx = (j & 1) ? (byte & 15u) : (byte >> 4);
                         float old = fmaf(tab.raw[idx], am, z);
                         if (has_d && c0 + g * 16 + j == row) old = dold;
-                        sum[h * 64 + g * 16 + j] = fmaf(p.beta, old, p.alpha * sum[h * 64 + g * 16 + j]);
+                        sum[h * 64 + g * 16 + j] = fmaf(p.beta, old, alpha * sum[h * 64 + g * 16 + j]);
                     }
                 } else {
 #pragma unroll
@@ -231,7 +241,7 @@ __device__ __forceinline__ void quantizing_epilogue(const CodeTables<16> &tab, c
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) sum[h * 64 + j] = (j < valid) ? fmaf(p.beta, 0.0f, p.alpha * sum[h * 64 + j]) : 0.0f;
+            for (int j = 0; j < 64; ++j) sum[h * 64 + j] = (j < valid) ? fmaf(p.beta, 0.0f, alpha * sum[h * 64 + j]) : 0.0f;
         }
         if (p.q_diag_out != nullptr && on_diag) {              // functional.py:574-578
             float dnew = 0.0f;
@@ -325,6 +335,36 @@ __device__ __forceinline__ void store_planes(__nv_bfloat16 *hi, __nv_bfloat16 *m
     }
 }
 
+// 16 consecutive result values -> two fp16 planes of value * scale (scale a power of two): x = hi + lo
+// to 22 significant bits while |x * scale| stays in fp16's normal range.  A value beyond that
+// range would turn into inf in the plane: it is clamped and the sticky error word is set.
+__device__ __forceinline__ void store_planes_f16(__half *hi, __half *lo, const float (&v)[16], float scale, bool wide, int nvalid) {
+    unsigned short H[16], L[16];
+    bool bad = false;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+        float x = v[t] * scale;
+        if (!(fabsf(x) <= 65000.0f)) { bad = bad || (t < nvalid); x = fminf(fmaxf(x, -65000.0f), 65000.0f); if (!(x == x)) x = 0.0f; }
+        const __half h = __float2half_rn(x);
+        H[t] = __half_as_ushort(h);
+        L[t] = __half_as_ushort(__float2half_rn(x - __half2float(h)));
+    }
+    if (bad) atomicCAS(&g_gemm_error, 0, QT_ERR_RANGE);
+    if (wide) {
+        unsigned w[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = (unsigned)H[2 * t] | ((unsigned)H[2 * t + 1] << 16);
+        stg256u(hi, w);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = (unsigned)L[2 * t] | ((unsigned)L[2 * t + 1] << 16);
+        stg256u(lo, w);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 16; ++t)
+            if (t < nvalid) { hi[t] = __ushort_as_half(H[t]); lo[t] = __ushort_as_half(L[t]); }
+    }
+}
+
 template <bool A_MN, bool B_MN, int NP, int BN_, bool QOUT = false>
 __global__ void __launch_bounds__((BN_ / 32 + 2) * 32, 1)
 k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
@@ -339,8 +379,10 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     // therefore accumulates at most KC k-blocks (128 k) per TMEM accumulator and the epilogue
     // warps add the partial sums in fp32 registers (round to nearest) while the next chunk is
     // being multiplied; the two-plane variant, whose operands carry 16 significant bits anyway,
-    // keeps one chain per tile (chunking it cost 2 ms of a 32 ms step and bought no accuracy).
-    constexpr int KC = NP == 3 ? 2 : (1 << 20);
+    // runs one chain per tile when its operands are bf16 planes (16 significant bits: the
+    // operand rounding dominates anyway) and chains of p.kc k-blocks when they are scaled fp16
+    // planes (22 bits).
+    const int KC = NP == 3 ? 2 : (p.kc > 0 ? p.kc : (1 << 20));
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -425,7 +467,8 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         // ---------------- MMA issuer: accumulator j&1 in TMEM columns [ (j&1)*BN_, +BN_ )
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N, M
-            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+            const unsigned fmt = p.f16 ? 0u : ((1u << 7) | (1u << 10));          // operand format: 0 = fp16, 1 = bf16
+            const unsigned idesc = (1u << 4) | fmt | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                                    ((unsigned)(BN_ >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
             // descriptors differ only in their 14-bit start-address field: build one per operand
             // plane for stage 0, k-slice 0 and add (byte offset >> 4) afterwards
@@ -531,32 +574,54 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
             }
             if (!ok) break;
+            // scaled operand planes: the accumulator holds sum(a * 2^ea * b * 2^eb)
+            int e_in = 0;
+            if (p.f16) {
+                const int za = p.a_slot ? __ldg(p.a_slot + b) : b, zb = p.b_slot ? __ldg(p.b_slot + b) : b;
+                e_in = (p.a_exp ? __ldg(p.a_exp + za) : 0) + (p.b_exp ? __ldg(p.b_exp + zb) : 0) + p.ab_exp0;
+            }
+            const float alpha_eff = p.f16 ? p.alpha * exp2f((float)-e_in) : p.alpha;
             if constexpr (QOUT) {
-                if (row_ok && valid > 0) quantizing_epilogue<128>(qtab.t, p, sum, b, row, n0);
+                if (row_ok && valid > 0) quantizing_epilogue<128>(qtab.t, p, sum, b, row, n0, alpha_eff);
             } else {
                 const int bo = p.d_slot ? __ldg(p.d_slot + b) : b;
                 float dev = 0.0f;                               // max |result - I| over this thread's elements
+                float pscale = 1.0f;                            // plane entry = value * pscale (fp16 planes)
+                if (p.f16 && p.Dhi) {
+                    const int e_out = p.out_exp ? __ldg(p.out_exp + bo) + p.out_exp0 : (p.out_rel ? e_in + p.out_exp0 : p.out_exp0);
+                    pscale = exp2f((float)e_out);
+                    if (p.out_exp_w && tm == 0 && tn == 0 && half == 0 && quad == 0 && lane == 0) p.out_exp_w[bo] = e_out;
+                }
                 if (row_ok && valid > 0) {
                     const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
                     float *drow = p.D + (long long)bo * p.strideD + (long long)row * p.ldd + n0;
                     const long long po = (long long)bo * p.strideP + (long long)row * p.ldp + n0;
                     const long long to = (long long)b * p.strideP + (long long)row * p.ldp + n0;   // T is stored by matrix number
+                    // C is fetched one 16-column group ahead of its use
+                    float cnext[16];
+                    auto fetch_c = [&](int q, float (&dst)[16]) {
+                        if (!has_c || q >= valid) return;
+                        if (q + 16 <= valid && wide_d) { ldg256f(crow + q, dst); ldg256f(crow + q + 8, dst + 8); }
+                        else {
+#pragma unroll
+                            for (int t = 0; t < 16; ++t) dst[t] = (q + t < valid) ? __ldg(crow + q + t) : 0.0f;
+                        }
+                    };
+                    fetch_c(0, cnext);
 #pragma unroll
                     for (int q = 0; q < 128; q += 16) {
                         if (q >= valid) continue;
                         const bool full16 = q + 16 <= valid;
                         float o[16];
                         if (has_c) {
-                            if (full16 && wide_d) { ldg256f(crow + q, o); ldg256f(crow + q + 8, o + 8); }
-                            else {
 #pragma unroll
-                                for (int t = 0; t < 16; ++t) o[t] = (q + t < valid) ? __ldg(crow + q + t) : 0.0f;
-                            }
+                            for (int t = 0; t < 16; ++t) o[t] = cnext[t];
+                            if (q + 16 < 128) fetch_c(q + 16, cnext);
 #pragma unroll
-                            for (int t = 0; t < 16; ++t) o[t] = fmaf(p.beta, o[t], p.alpha * sum[q + t]);
+                            for (int t = 0; t < 16; ++t) o[t] = fmaf(p.beta, o[t], alpha_eff * sum[q + t]);
                         } else {
 #pragma unroll
-                            for (int t = 0; t < 16; ++t) o[t] = p.alpha * sum[q + t];
+                            for (int t = 0; t < 16; ++t) o[t] = alpha_eff * sum[q + t];
                         }
                         if (p.D) {
                             if (full16 && wide_d) { stg256f(drow + q, o); stg256f(drow + q + 8, o + 8); }
@@ -565,8 +630,14 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                                 for (int t = 0; t < 16; ++t) if (q + t < valid) drow[q + t] = o[t];
                             }
                         }
-                        if (p.Dhi) store_planes<NP>(p.Dhi + po + q, NP == 3 ? p.Dmid + po + q : nullptr, p.Dlo + po + q, o,
-                                                    full16 && wide_p, valid - q);
+                        if (p.Dhi) {
+                            if (NP == 2 && p.f16)
+                                store_planes_f16(reinterpret_cast<__half *>(p.Dhi) + po + q, reinterpret_cast<__half *>(p.Dlo) + po + q, o,
+                                                 pscale, full16 && wide_p, valid - q);
+                            else
+                                store_planes<NP>(p.Dhi + po + q, NP == 3 ? p.Dmid + po + q : nullptr, p.Dlo + po + q, o,
+                                                 full16 && wide_p, valid - q);
+                        }
                         if (p.maxdev || p.Thi) {
                             const int dcol = row - (n0 + q);    // position of the diagonal inside this group, if any
                             if (p.maxdev) {
@@ -713,6 +784,121 @@ k_split_bf16(const float *__restrict__ X, long long ldx, long long strideX, int 
 }
 
 // ------------------------------------------------------------------------------------
+// Scaled fp16 planes.  For every matrix b of a batch the largest magnitude amax[b] of the
+// (optionally row-gathered, row-scaled) source is found first; the exponent e[b] = target - k with
+// amax = m * 2^k, m in [0.5, 1) puts the largest scaled entry just below 2^target, and the planes
+// hold hi = fp16(x * 2^e), lo = fp16(x * 2^e - hi): 22 significant bits for every entry within
+// 2^(target + 3) of the largest one and an absolute error below 2^-25 (scaled) for the rest.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_amax_rows(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
+            const long long *__restrict__ index, long long stride_index,
+            const float *__restrict__ scale, long long stride_scale, float *__restrict__ amax) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    const long long *idx = index ? index + (long long)b * stride_index : nullptr;
+    const float *sc = scale ? scale + (long long)b * stride_scale : nullptr;
+    const bool vec = (cols & 3) == 0 && (ldx & 3) == 0 && (strideX & 3) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0;
+    const int per_row = vec ? cols / 4 : cols;
+    const long long total = (long long)rows * per_row;
+    float m = 0.0f;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(e / per_row), c = (int)(e - (long long)r * per_row);
+        const long long src = idx ? idx[r] : (long long)r;
+        const float f = sc ? fabsf(sc[r]) : 1.0f;
+        if (vec) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + src * ldx + 4 * c));
+            m = fmaxf(m, f * fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        } else {
+            m = fmaxf(m, f * fabsf(x[src * ldx + c]));
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(reinterpret_cast<int *>(amax + b), __float_as_int(m));
+}
+
+// fp32 -> scaled fp16 planes with optional row gather / row scale (see k_split_bf16_rows).
+// The exponent comes from amax[b] (then it is also written to exp_out[b]) or, when amax is
+// null, from exp_in[b] (null: 0); `target` / `exp0` is added as described above.
+template <bool WIDE>
+__global__ void __launch_bounds__(256)
+k_split_f16_rows(const float *__restrict__ X, long long ldx, long long strideX, int rows, int cols,
+                 const long long *__restrict__ index, long long stride_index,
+                 const float *__restrict__ scale, long long stride_scale,
+                 const float *__restrict__ amax, const int *__restrict__ exp_in, int target_or_exp0, int *__restrict__ exp_out,
+                 __half *__restrict__ hi, __half *__restrict__ lo, long long ldp, long long strideP) {
+    const int b = blockIdx.y;
+    const float *x = X + (long long)b * strideX;
+    __half *h = hi + (long long)b * strideP, *l = lo + (long long)b * strideP;
+    const long long *idx = index ? index + (long long)b * stride_index : nullptr;
+    const float *sc = scale ? scale + (long long)b * stride_scale : nullptr;
+    const int e = amax ? exponent_for(amax[b], target_or_exp0) : (exp_in ? exp_in[b] : 0) + target_or_exp0;
+    if (exp_out && blockIdx.x == 0 && threadIdx.x == 0) exp_out[b] = e;
+    const float two_e = exp2f((float)e);
+    constexpr int E = WIDE ? 16 : 1;
+    const int per_row = cols / E;
+    const long long total = (long long)rows * per_row;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(t / per_row), c = (int)(t - (long long)r * per_row) * E;
+        const long long src = idx ? idx[r] : (long long)r;
+        const float f = (sc ? sc[r] : 1.0f) * two_e;
+        if constexpr (WIDE) {
+            float v[16];
+            ldg256f(x + src * ldx + c, v);
+            ldg256f(x + src * ldx + c + 8, v + 8);
+            unsigned H[8], L[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float a0 = v[2 * j] * f, a1 = v[2 * j + 1] * f;
+                const __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
+                const __half l0 = __float2half_rn(a0 - __half2float(h0)), l1 = __float2half_rn(a1 - __half2float(h1));
+                H[j] = (unsigned)__half_as_ushort(h0) | ((unsigned)__half_as_ushort(h1) << 16);
+                L[j] = (unsigned)__half_as_ushort(l0) | ((unsigned)__half_as_ushort(l1) << 16);
+            }
+            stg256u(h + (long long)r * ldp + c, H);
+            stg256u(l + (long long)r * ldp + c, L);
+        } else {
+            const float a = x[src * ldx + c] * f;
+            const __half vh = __float2half_rn(a);
+            h[(long long)r * ldp + c] = vh;
+            l[(long long)r * ldp + c] = __float2half_rn(a - __half2float(vh));
+        }
+    }
+}
+
+// amax (float, batch entries) is scratch the caller provides; exp_out receives the exponents.
+int launch_split_f16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                     const long long *index, long long stride_index, const float *scale, long long stride_scale,
+                     float *amax, const int *exp_in, int target_or_exp0, int *exp_out,
+                     void *hi, void *lo, long long ldp, long long strideP, cudaStream_t s) {
+    if (rows < 0 || cols < 0 || batch < 0 || batch > 65535) return record(QT_ERR_ARG);
+    if (rows == 0 || cols == 0 || batch == 0) return record(QT_OK);
+    if (!X || !hi || !lo || ldx < cols || ldp < cols) return record(QT_ERR_ARG);
+    const bool wide = cols % 16 == 0 && ldx % 8 == 0 && strideX % 8 == 0 && ldp % 16 == 0 && strideP % 16 == 0 &&
+                      ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 31) == 0;
+    const long long total = (long long)rows * (wide ? cols / 16 : cols);
+    long long ctas = (total + 256 * 4 - 1) / (256 * 4);
+    const long long cap = ((long long)device_sm_count() * 32 + batch - 1) / batch;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    dim3 grid((unsigned)ctas, batch);
+    if (amax) {
+        if (cudaMemsetAsync(amax, 0, sizeof(float) * batch, s) != cudaSuccess) return record(QT_ERR_LAUNCH);
+        k_amax_rows<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, index, stride_index, scale, stride_scale, amax);
+        count_launch(1);
+    }
+    if (wide)
+        k_split_f16_rows<true><<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, index, stride_index, scale, stride_scale,
+                                                     amax, exp_in, target_or_exp0, exp_out, static_cast<__half *>(hi), static_cast<__half *>(lo), ldp, strideP);
+    else
+        k_split_f16_rows<false><<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, index, stride_index, scale, stride_scale,
+                                                      amax, exp_in, target_or_exp0, exp_out, static_cast<__half *>(hi), static_cast<__half *>(lo), ldp, strideP);
+    count_launch(1);
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------------
 // Host side.
 // ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -733,14 +919,14 @@ static EncodeTiledFn encode_fn() {
 
 // Plane of a logical (outer x inner) bf16 matrix per batch entry, `ld` elements between rows.
 static bool make_map(CUtensorMap *map, const void *base, long long inner, long long outer, long long batch,
-                     long long ld, long long stride_batch, unsigned box_inner, unsigned box_outer) {
+                     long long ld, long long stride_batch, unsigned box_inner, unsigned box_outer, bool f16 = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
     cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)stride_batch * 2};
     cuuint32_t box[3] = {box_inner, box_outer, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+    return fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -900,6 +1086,11 @@ struct GemmExtras {
     const int *a_slot = nullptr, *b_slot = nullptr, *d_slot = nullptr;
     const int *active = nullptr;
     int a_entries = 0, b_entries = 0;                       // matrices in A's / B's storage (0: batch)
+    // scaled fp16 planes (two-plane products only)
+    int f16 = 0;
+    const int *a_exp = nullptr, *b_exp = nullptr; int ab_exp0 = 0;
+    const int *out_exp = nullptr; int *out_exp_w = nullptr; int out_exp0 = 0, out_rel = 0;
+    int kc = 0;                                             // k-blocks per accumulation chain (0: one chain)
 };
 
 static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -972,6 +1163,8 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     if (a.Dhi && np == 3 && !x.Dmid) return record(QT_ERR_ARG);                  // three-plane result needs all three planes
     if (x.Thi && (!x.Tmid || !x.Tlo || np != 3 || a.ldp <= 0)) return record(QT_ERR_ARG);
     if ((x.Thi || x.maxdev || x.Dmid) && qs) return record(QT_ERR_UNSUPPORTED);
+    if (x.f16 && np != 2) return record(QT_ERR_UNSUPPORTED);
+    if (x.kc < 0) return record(QT_ERR_ARG);
     const int a_entries = x.a_entries > 0 ? x.a_entries : a.batch, b_entries = x.b_entries > 0 ? x.b_entries : a.batch;
     const void *Ap[3] = {a.Ahi, np == 3 ? Amid : a.Alo, a.Alo};
     const void *Bp[3] = {a.Bhi, np == 3 ? Bmid : a.Blo, a.Blo};
@@ -995,10 +1188,11 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     bool ok = true;
     for (int i = 0; i < 3; ++i) {
         const void *pa = Ap[i < np ? i : 0], *pb = Bp[i < np ? i : 0];
-        if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a_entries, a.lda, a.strideA, BK, BM);   // stored [M][K]
-        else         ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a_entries, a.lda, a.strideA, 64, BK);   // stored [K][M]
-        if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, b_entries, a.ldb, a.strideB, BK, bn);   // stored [N][K]
-        else         ok = ok && make_map(&maps.b[i], pb, a.N, a.K, b_entries, a.ldb, a.strideB, 64, BK);   // stored [K][N]
+        const bool h = x.f16 != 0;
+        if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a_entries, a.lda, a.strideA, BK, BM, h);   // stored [M][K]
+        else         ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a_entries, a.lda, a.strideA, 64, BK, h);   // stored [K][M]
+        if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, b_entries, a.ldb, a.strideB, BK, bn, h);   // stored [N][K]
+        else         ok = ok && make_map(&maps.b[i], pb, a.N, a.K, b_entries, a.ldb, a.strideB, 64, BK, h);   // stored [K][N]
     }
     if (!ok) return record(QT_ERR_LAUNCH);
     GemmParams p;
@@ -1010,6 +1204,8 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     p.Thi = static_cast<__nv_bfloat16 *>(x.Thi); p.Tmid = static_cast<__nv_bfloat16 *>(x.Tmid); p.Tlo = static_cast<__nv_bfloat16 *>(x.Tlo);
     p.t_c0 = x.t_c0; p.t_c1 = x.t_c1; p.maxdev = x.maxdev;
     p.a_slot = x.a_slot; p.b_slot = x.b_slot; p.d_slot = x.d_slot; p.active = x.active;
+    p.f16 = x.f16; p.a_exp = x.a_exp; p.b_exp = x.b_exp; p.ab_exp0 = x.ab_exp0;
+    p.out_exp = x.out_exp; p.out_exp_w = x.out_exp_w; p.out_exp0 = x.out_exp0; p.out_rel = x.out_rel; p.kc = x.kc;
     p.tiles_m = tiles_m; p.tiles_n = (a.N + bn - 1) / bn;
     p.q_in = nullptr; p.q_absmax_in = p.q_diag_in = nullptr; p.q_out = nullptr; p.q_absmax_out = p.q_diag_out = nullptr;
     p.q_stride_codes = p.q_stride_absmax = p.q_stride_diag = 0; p.q_code = nullptr; p.q_nb = 0;
@@ -1268,6 +1464,14 @@ int qt_device_error(int clear) { return read_gemm_error(clear != 0); }
 
 void qt_gemm_force_tile(int bn) { g_force_bn = bn; }
 
+int qt_split_f16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
+                 const long long *index, long long stride_index, const float *scale, long long stride_scale,
+                 float *amax_scratch, const int *exp_in, int target_or_exp0, int *exp_out,
+                 void *hi, void *lo, long long ldp, long long strideP, void *stream) {
+    return launch_split_f16(X, ldx, strideX, rows, cols, batch, index, stride_index, scale, stride_scale, amax_scratch, exp_in,
+                            target_or_exp0, exp_out, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
+}
+
 int qt_gemm_ex(const qt_gemm_desc *d, void *stream) {
     if (!d) return record(QT_ERR_ARG);
     const bool three = d->A[1] != nullptr || d->B[1] != nullptr;
@@ -1279,8 +1483,13 @@ int qt_gemm_ex(const qt_gemm_desc *d, void *stream) {
     x.Thi = d->T[0]; x.Tmid = d->T[1]; x.Tlo = d->T[2]; x.t_c0 = d->t_c0; x.t_c1 = d->t_c1;
     x.maxdev = d->maxdev; x.a_slot = d->a_slot; x.b_slot = d->b_slot; x.d_slot = d->d_slot; x.active = d->active;
     x.a_entries = d->a_entries; x.b_entries = d->b_entries;
+    x.f16 = d->f16; x.a_exp = d->a_exp; x.b_exp = d->b_exp; x.ab_exp0 = d->ab_exp0;
+    x.out_exp = d->out_exp; x.out_exp_w = d->out_exp_w; x.out_exp0 = d->out_exp0; x.out_rel = d->out_rel; x.kc = d->kc;
     if (three && (!d->A[1] || !d->B[1])) return record(QT_ERR_ARG);
-    return launch_gemm_planes(a, three ? d->A[1] : nullptr, three ? d->B[1] : nullptr, static_cast<cudaStream_t>(stream), nullptr, &x);
+    QuantStateArgs qs{d->q_code, d->q_in, d->q_absmax_in, d->q_diag_in, d->q_out, d->q_absmax_out, d->q_diag_out,
+                      d->q_stride_codes, d->q_stride_absmax, d->q_stride_diag};
+    return launch_gemm_planes(a, three ? d->A[1] : nullptr, three ? d->B[1] : nullptr, static_cast<cudaStream_t>(stream),
+                              d->q_out ? &qs : nullptr, &x);
 }
 
 int qt_selftest_wait_timeout(int *gave_up, void *stream) {

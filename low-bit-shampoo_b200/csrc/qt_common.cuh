@@ -55,8 +55,10 @@ int launch_merge_t(const float *G, long long ldg, long long strideG, const float
 int launch_quantize(const QuantArgs &a, cudaStream_t stream);
 int launch_dequantize(const DequantArgs &a, cudaStream_t stream);
 // a.out / a.out_dtype / a.stride_out are ignored: output goes to the bf16 planes hi, lo
+// amax_scratch != nullptr: scaled fp16 planes (exponents from each matrix's largest magnitude and
+// `target`, written to exp_out); nullptr: plain bf16 planes.
 int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, void *lo, long long ldp, long long strideP,
-                             cudaStream_t stream);
+                             cudaStream_t stream, float *amax_scratch = nullptr, int target = 0, int *exp_out = nullptr);
 int launch_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches_dev,
                              cudaStream_t stream);
 int launch_householder_panel(const float *A, long long strideA, int n, int count, int j0, int w,

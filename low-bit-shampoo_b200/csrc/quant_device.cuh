@@ -162,6 +162,15 @@ __device__ __forceinline__ float div_by_recip(float x, float d, float r) {
     return q;
 }
 
+// Exponent of a scaled fp16 operand plane: with amax = m * 2^k, m in [0.5, 1), e = target - k puts
+// the largest scaled entry just below 2^target (0 for an all-zero or non-finite matrix).
+__device__ __forceinline__ int exponent_for(float amax, int target) {
+    if (!(amax > 0.0f) || !(amax <= 3.0e38f)) return 0;
+    int k;
+    frexpf(amax, &k);
+    return target - k;
+}
+
 // Per-lane quantization of EPL elements for every case the lean path of k_quantize_vec does
 // not cover (any codebook, clamp, permutation, extreme scales).  Kept out of line on purpose.
 // Operands and results travel by value (registers): passing the caller's arrays by reference

@@ -21,6 +21,7 @@
 //   Orders that are not a multiple of 4, unaligned buffers and block sizes above 256
 //   take a generic two-kernel path (absmax pass, then one thread per output byte).
 #include "quant_device.cuh"
+#include <cuda_fp16.h>
 
 namespace qt {
 
@@ -433,12 +434,38 @@ __device__ __forceinline__ void stg256u(void *p, const unsigned (&v)[8]) {
                  :: "l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 
-template <int BITS, int EPL>
+// Largest magnitude a dequantized state matrix can hold: max over its block scales and its fp32
+// diagonal (|code| <= 1).  One CTA per output matrix; amax[m] belongs to state slot slots[m].
+__global__ void __launch_bounds__(256)
+k_state_amax(const float *__restrict__ absmax_base, long long stride_absmax, int n_absmax,
+             const float *__restrict__ diag_base, long long stride_diag, int n_diag,
+             const int *__restrict__ slots, float *__restrict__ amax) {
+    const int m = blockIdx.x;
+    const long long src = slots ? (long long)slots[m] : (long long)m;
+    float v = 0.0f;
+    for (int i = threadIdx.x; i < n_absmax; i += blockDim.x) v = fmaxf(v, fabsf(absmax_base[src * stride_absmax + i]));
+    if (diag_base)
+        for (int i = threadIdx.x; i < n_diag; i += blockDim.x) v = fmaxf(v, fabsf(diag_base[src * stride_diag + i]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    __shared__ float red[8];
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; ++i) v = fmaxf(v, red[i]);
+        amax[m] = v;
+    }
+}
+
+// F16: the planes are scaled fp16 planes (entry = value * 2^e, e from amax[m] and `target`,
+// written to exp_out[m]); otherwise plain bf16 planes.
+template <int BITS, int EPL, bool F16>
 __global__ void __launch_bounds__(kThreads)
 k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_in, const float *__restrict__ code,
                     int n, int nb, int bs_shift, const float *__restrict__ absmax_base, long long stride_absmax,
                     const float *__restrict__ diag_base, long long stride_diag, const int *__restrict__ slots,
-                    __nv_bfloat16 *__restrict__ hi_base, __nv_bfloat16 *__restrict__ lo_base, long long ldp, long long strideP) {
+                    __nv_bfloat16 *__restrict__ hi_base, __nv_bfloat16 *__restrict__ lo_base, long long ldp, long long strideP,
+                    const float *__restrict__ amax, int target, int *__restrict__ exp_out) {
     constexpr int NC = 1 << BITS;
     __shared__ float2 pair_lut[BITS == 4 ? 256 : 1];
     __shared__ float code_s[BITS == 8 ? 256 : 16];
@@ -454,6 +481,12 @@ k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_
     const float *absmax = absmax_base + src * stride_absmax;
     const float *diag = diag_base ? diag_base + src * stride_diag : nullptr;
     __nv_bfloat16 *hi = hi_base + (long long)m * strideP, *lo = lo_base + (long long)m * strideP;
+    float two_e = 1.0f;
+    if constexpr (F16) {
+        const int e = exponent_for(amax[m], target);
+        two_e = exp2f((float)e);
+        if (exp_out && blockIdx.x == 0 && threadIdx.x == 0) exp_out[m] = e;
+    }
 
     const int chunks_per_row = n / EPL;
     const int chunks = n * chunks_per_row;
@@ -503,11 +536,19 @@ k_dequantize_planes(const unsigned char *__restrict__ in_base, long long stride_
         unsigned h[EPL / 2], l[EPL / 2];
 #pragma unroll
         for (int j = 0; j < EPL / 2; ++j) {
-            const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * j]), h1 = __float2bfloat16_rn(v[2 * j + 1]);
-            const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * j] - __bfloat162float(h0));
-            const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * j + 1] - __bfloat162float(h1));
-            h[j] = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
-            l[j] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
+            if constexpr (F16) {
+                const float a0 = v[2 * j] * two_e, a1 = v[2 * j + 1] * two_e;
+                const __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
+                const __half l0 = __float2half_rn(a0 - __half2float(h0)), l1 = __float2half_rn(a1 - __half2float(h1));
+                h[j] = (unsigned)__half_as_ushort(h0) | ((unsigned)__half_as_ushort(h1) << 16);
+                l[j] = (unsigned)__half_as_ushort(l0) | ((unsigned)__half_as_ushort(l1) << 16);
+            } else {
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * j]), h1 = __float2bfloat16_rn(v[2 * j + 1]);
+                const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * j] - __bfloat162float(h0));
+                const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * j + 1] - __bfloat162float(h1));
+                h[j] = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
+                l[j] = (unsigned)__bfloat16_as_ushort(l0) | ((unsigned)__bfloat16_as_ushort(l1) << 16);
+            }
         }
         const long long o = (long long)r * ldp + c;
         if constexpr (EPL == 16) {
@@ -754,7 +795,7 @@ int launch_dequantize(const DequantArgs &a, cudaStream_t s) {
 }
 
 int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, void *lo, long long ldp, long long strideP,
-                             cudaStream_t s) {
+                             cudaStream_t s, float *amax_scratch, int target, int *exp_out) {
     if (a.bits != 4 && a.bits != 8) return record(QT_ERR_BITS);
     if (!valid_blocksize(a.bs)) return record(QT_ERR_BLOCKSIZE);
     if (a.n < 0 || a.count < 0 || a.n > 46340 || a.count > 65535) return record(QT_ERR_ARG);
@@ -773,11 +814,22 @@ int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, v
     const bool wide = n % 16 == 0 && ldp % 16 == 0 && strideP % 16 == 0 && aligned(hi, 32) && aligned(lo, 32) &&
                       aligned(a.A, in16) && a.strideA % in16 == 0 && a.bs >= 16;
     dim3 grid(grid_x_for((long long)n * (n / (wide ? 16 : 8)), a.count, 4), a.count);
-#define QT_DQP(B, E)                                                                                                    \
-    k_dequantize_planes<B, E><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax, a.stride_absmax, \
-        a.diag, a.stride_diag, slots, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP)
-    if (a.bits == 4) { if (wide) QT_DQP(4, 16); else QT_DQP(4, 8); }
-    else { if (wide) QT_DQP(8, 16); else QT_DQP(8, 8); }
+    const bool f16 = amax_scratch != nullptr;
+    if (f16) {
+        k_state_amax<<<a.count, 256, 0, s>>>(a.absmax, a.stride_absmax, n * nb, a.diag, a.stride_diag, n, slots, amax_scratch);
+        count_launch(1);
+    }
+#define QT_DQP(B, E, H)                                                                                                 \
+    k_dequantize_planes<B, E, H><<<grid, kThreads, 0, s>>>(a.A, a.strideA, a.code, n, nb, bs_shift, a.absmax, a.stride_absmax, \
+        a.diag, a.stride_diag, slots, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo), ldp, strideP,   \
+        amax_scratch, target, exp_out)
+    if (f16) {
+        if (a.bits == 4) { if (wide) QT_DQP(4, 16, true); else QT_DQP(4, 8, true); }
+        else { if (wide) QT_DQP(8, 16, true); else QT_DQP(8, 8, true); }
+    } else {
+        if (a.bits == 4) { if (wide) QT_DQP(4, 16, false); else QT_DQP(4, 8, false); }
+        else { if (wide) QT_DQP(8, 16, false); else QT_DQP(8, 8, false); }
+    }
 #undef QT_DQP
     count_launch(1);
     return check_launch();

@@ -104,8 +104,18 @@ class QuantArena:
         """Matrices `slots` (any order, repeats allowed) as bf16 hi/lo Planes, written by the
         dequantize kernel itself: no fp32 copy, no gather, no split pass (qt_dequantize_planes)."""
         n, m = self.n, len(slots)
-        P = _gemm.Planes(m, n, n, self.device)
         idx = _index_tensor(list(slots), self.device, torch.int32)
+        if _gemm.FP16_PLANES:
+            scratch = torch.empty(2, m, dtype=torch.int32, device=self.device)     # amax bits, exponents
+            P = _gemm.Planes(m, n, n, self.device, f16=True, exp=scratch[1], tmax=_gemm.SPLIT_TARGET)
+            with torch.cuda.device(self.device):
+                rc = F.lib.qt_dequantize_planes_f16(
+                    _ptr(self.var), self.row_bytes, _ptr(self.code), n, m, _ptr(self.absmax), n * self.nb,
+                    _ptr(self.diag) if self.diagreal else None, n, _ptr(idx), _ptr(scratch[0]), _gemm.SPLIT_TARGET,
+                    _ptr(scratch[1]), P.ptr_hi(), P.ptr_lo(), P.ld, P.stride, self.blocksize, self.bits, F._stream(self.var))
+            F._check(rc, "dequantize to planes")
+            return P
+        P = _gemm.Planes(m, n, n, self.device)
         with torch.cuda.device(self.device):
             rc = F.lib.qt_dequantize_planes(
                 _ptr(self.var), self.row_bytes, _ptr(self.code), n, m, _ptr(self.absmax), n * self.nb,
@@ -204,13 +214,6 @@ DEQUANTIZE_TO_PLANES = True    # preconditioners are dequantized straight into b
 # processed: those paths have no quantisation noise to hide the ~1e-5 relative error of the
 # split-bf16 products (and the Newton iteration amplifies it), so they stay on fp32 products.
 _EXACT = False
-# The eigenbasis V of the statistics ends up as 4-bit codes: a relative error of 4e-6 in V (what
-# two-plane operands, rounded to 16 significant bits, leave) already flips one code in 10^4, and
-# those flips are what separates two implementations of the step.  With this switch the chain
-# that produces V - L V^T, the far updates of the QR and the accumulation of Q - runs on three
-# planes per operand (fp32-level accuracy) at twice the MMA count of those products.
-PRECISE_BASIS = True
-PRECISE_STATS = False          # experiment: also the rectification and reconstruction of the statistic on three planes
 
 
 class _exact:
@@ -252,17 +255,14 @@ def _tc(t):
 
 
 def mm(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, want_float=True, want_planes=False,
-       exact=False):
-    """alpha * op(A) @ op(B) + beta * C over a batch; A, B are Mat, C an fp32 tensor.
-    `exact` forces an fp32 product (operands must then be available as fp32)."""
+       out_bound=None):
+    """alpha * op(A) @ op(B) + beta * C over a batch; A, B are Mat, C an fp32 tensor.  On CUDA the
+    product runs on the tensor cores from scaled fp16 planes (fp32-level accuracy).  `out_bound`:
+    a-priori bound on |result| used to place a plane output (see _gemm.matmul)."""
     ref = A.f32 if A.f32 is not None else A._planes.hi
-    if exact and _tc(ref) and A.f32 is not None and B.f32 is not None:
-        # fp32-level accuracy on the tensor cores: three bf16 planes per operand, six MMAs per k-slice
-        D, _ = _gemm.matmul(A.planes3, B.planes3, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C)
-        return Mat(D)
-    if _tc(ref) and not exact:
+    if _tc(ref):
         D, P = _gemm.matmul(A.planes, B.planes, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C,
-                            want_float=want_float, want_planes=want_planes)
+                            want_float=want_float, want_planes=want_planes, out_bound=out_bound)
         return Mat(D, P)
     a = A.f32.transpose(1, 2) if trans_a else A.f32
     b = B.f32.transpose(1, 2) if trans_b else B.f32
@@ -272,13 +272,19 @@ def mm(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, want_flo
     return Mat(out if alpha == 1.0 else out * alpha)
 
 
-def op_bjorck(V, want_planes=False, exact=False):
+# Entries of a (nearly) orthonormal basis and of its Gram matrix stay below these bounds with a
+# wide margin (rows of a 4-bit eigenbasis have norm 1 +- 0.2); a plane output placed with them
+# keeps 22 significant bits.  An input that violates them trips QT_ERR_RANGE instead of passing
+# silently.
+_BASIS_BOUND = 8.0
+_GRAM_BOUND = 16.0
+
+
+def op_bjorck(V, want_planes=False):
     """1.5 V - 0.5 (V V^T) V on the rows of each V in the batch (utils.py:196, functional.py:757)."""
-    if exact and _tc(V.f32):
-        W = mm(V, V, trans_b=True, exact=True)
-        return mm(W, V, alpha=-0.5, beta=1.5, C=V.f32, exact=True)
-    W = mm(V, V, trans_b=True, want_float=not _tc(V.f32), want_planes=_tc(V.f32))
-    return mm(W, V, alpha=-0.5, beta=1.5, C=V.f32, want_planes=want_planes and _tc(V.f32))
+    tc = _tc(V.f32)
+    W = mm(V, V, trans_b=True, want_float=not tc, want_planes=tc, out_bound=_GRAM_BOUND)
+    return mm(W, V, alpha=-0.5, beta=1.5, C=V.f32, want_planes=want_planes and tc, out_bound=_BASIS_BOUND)
 
 
 def op_scaled_gram(rows, weights, want_planes=False):
@@ -302,21 +308,20 @@ def op_scaled_gram_gathered(Vt, idx, weights):
 def op_ema_gram(L, G, axis, w1, w2):
     """w1 L + w2 G G^T (axis 0) or w1 L + w2 G^T G (axis 1) (shampoo2.py:185-199); L fp32 tensor.
 
-    Kept in fp32: the statistic's small eigenvalues (the half of the spectrum that is kept,
-    regularised by only matrix_eps * lambda_max) must be accurate to ~1e-7 * lambda_max, which
-    the split-bf16 products (1e-5) do not deliver."""
+    The statistic's small eigenvalues (the half of the spectrum that is kept, regularised by only
+    matrix_eps * lambda_max) must be accurate to ~1e-7 * lambda_max: this needs the 22-bit operand
+    planes and the short accumulation chains of the fp16-plane product."""
     Gm = Mat(G)
     if axis == 0:
-        return mm(Gm, Gm, trans_b=True, alpha=w2, beta=w1, C=L, exact=True).f32
-    return mm(Gm, Gm, trans_a=True, alpha=w2, beta=w1, C=L, exact=True).f32
+        return mm(Gm, Gm, trans_b=True, alpha=w2, beta=w1, C=L).f32
+    return mm(Gm, Gm, trans_a=True, alpha=w2, beta=w1, C=L).f32
 
 
 def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
     quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
-    tc = _tc(L.f32)
-    V = householder_q(mm(L, Vt, trans_b=True, exact=PRECISE_BASIS and tc).f32, tensor_cores=tc, precise=PRECISE_BASIS and tc)
-    LV = mm(L, Mat(V), exact=True).f32          # Rayleigh quotients need fp32 (see op_ema_gram)
+    V = householder_q(mm(L, Vt, trans_b=True).f32, tensor_cores=_tc(L.f32))
+    LV = mm(L, Mat(V)).f32
     eigs = (LV * V).sum(dim=1)
     return V, eigs
 
@@ -374,7 +379,7 @@ def _ema_update_fused(arena, a, grads_axes, w1, w2):
     if any(ks != list(range(ks[0], ks[0] + len(ks))) for ks in groups.values()):
         return False
     for (shape, axis), ks in groups.items():
-        P = _gemm.split3(torch.stack([grads_axes[k][0].float() for k in ks]))
+        P = _gemm.split(torch.stack([grads_axes[k][0].float() for k in ks]))
         st = arena.state(a + ks[0], a + ks[0] + len(ks))
         _gemm.matmul_q4(P, P, arena.code, st, trans_a=(axis == 1), trans_b=(axis == 0), alpha=w2, beta=w1, old=st)
     return True
@@ -512,12 +517,8 @@ def _class_statistics(cls, entries, w1, w2, eps, exact):
             Vt = Mat(cls.stat.dequantize(a, b))
             if cls.stat.lowbit:
                 for _ in range(cls.rect_t1):
-                    Vt = op_bjorck(Vt, want_planes=True, exact=PRECISE_STATS)
-            if PRECISE_STATS and _tc(Vt.f32):
-                rows = Mat(_gather_rows(Vt.f32, cls.keep_idx[a:b]))
-                L = mm(rows, Mat(cls.S[a:b].unsqueeze(2) * rows.f32), trans_a=True, exact=True).f32
-            else:
-                L = op_scaled_gram_gathered(Vt.f32, cls.keep_idx[a:b], cls.S[a:b]).f32
+                    Vt = op_bjorck(Vt, want_planes=True)
+            L = op_scaled_gram_gathered(Vt.f32, cls.keep_idx[a:b], cls.S[a:b]).f32
             L = _ema_update(L, ga, w1, w2)
             V, eigs = op_subspace_step(Mat(L), Vt)
             vals, idx = torch.sort(eigs, dim=1)

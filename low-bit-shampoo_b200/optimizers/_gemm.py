@@ -1,15 +1,32 @@
-"""Host wrappers of the tcgen05 matrix-product kernels (qt_split_bf16, qt_gemm_bf16x3).
+"""Host wrappers of the tcgen05 matrix-product kernels.
 
-A `Planes` object is an fp32 matrix batch carried as two bf16 planes (hi, lo) with a row
-pitch that is a multiple of 16 elements, the operand format of the kernel.  `matmul`
-multiplies two such batches with any combination of transposes without moving data: a
-transposed operand is presented to the kernel as an MN-major tile.
+A `Planes` object is a batch of fp32 matrices in the operand format of the product kernel:
+row pitch a multiple of 16 elements, one of three encodings
+
+  * scaled fp16, two planes (the default of split()): entry = x * 2^(exp[b] + exp0) as
+    hi = fp16(.), lo = fp16(. - hi) - 22 significant bits; the per-matrix exponent exp[b] is
+    chosen from the matrix's largest magnitude so that scaled entries stay below 2^tmax.
+    Three MMAs per k-slice (hi*hi + hi*lo + lo*hi) on fp16 operands, partial sums of 128 k
+    promoted to fp32 registers: products agree with an fp32 library product to ~1e-6;
+  * bf16, two planes (split_bf16()): 16 significant bits, no scaling - the format of the
+    plain C entry points qt_split_bf16 / qt_gemm_bf16x3;
+  * bf16, three planes (split3()): 24 significant bits, six MMAs per k-slice - used by the
+    Schur-Newton chain, whose iterates have no usable a-priori bound.
+
+`matmul` multiplies two such batches with any combination of transposes without moving
+data: a transposed operand is presented to the kernel as an MN-major tile.
 """
 import ctypes as ct
+import math
 
 import torch
 
 import qtensor.functional as F
+
+FP16_PLANES = True          # split() produces scaled fp16 planes (False: bf16 planes, 16 significant bits)
+SPLIT_TARGET = 9            # scaled entries of a freshly split matrix stay below 2^9 (headroom for in-place updates)
+CHAIN_K = 2                 # k-blocks (of 64) per accumulation chain of fp16-plane products
+F16_MAX_EXP = 15            # fp16 holds magnitudes below 2^16; plane outputs are placed below 2^15
 
 
 def _ptr(t):
@@ -21,21 +38,24 @@ def _pitch(cols):
 
 
 class Planes:
-    """(batch, rows, cols) fp32 values as bf16 hi/lo planes of pitch `ld`.
+    """(batch, rows, cols) fp32 values as 16-bit planes of pitch `ld` (see the module docstring).
 
-    `offset` (elements) selects a sub-matrix of a parent's storage: window() shares memory."""
+    `offset` (elements) selects a sub-matrix of a parent's storage: window() shares memory,
+    exponents included."""
 
-    def __init__(self, batch, rows, cols, device, _share=None, planes=2):
+    def __init__(self, batch, rows, cols, device, _share=None, planes=2, f16=False, exp=None, exp0=0, tmax=None):
         self.batch, self.rows, self.cols = batch, rows, cols
         self.mid = None
+        self.f16, self.exp, self.exp0, self.tmax = f16, exp, exp0, tmax
         if _share is not None:
             self.hi, self.lo, self.ld, self.stride, self.offset = _share[:5]
             self.mid = _share[5] if len(_share) > 5 else None
             return
+        assert not (f16 and planes == 3)
         self.ld = _pitch(cols)
         self.stride = rows * self.ld
         self.offset = 0
-        buf = torch.empty(planes, batch, self.stride, dtype=torch.bfloat16, device=device)
+        buf = torch.empty(planes, batch, self.stride, dtype=torch.float16 if f16 else torch.bfloat16, device=device)
         self.hi, self.lo = buf[0], buf[planes - 1]
         if planes == 3:
             self.mid = buf[1]
@@ -44,7 +64,8 @@ class Planes:
         """Planes of the sub-matrix [row0:row0+rows, col0:col0+cols]; col0 must be a multiple of 8."""
         assert col0 % 8 == 0 and row0 + rows <= self.rows and col0 + cols <= self.cols
         return Planes(self.batch, rows, cols, self.hi.device,
-                      _share=(self.hi, self.lo, self.ld, self.stride, self.offset + row0 * self.ld + col0, self.mid))
+                      _share=(self.hi, self.lo, self.ld, self.stride, self.offset + row0 * self.ld + col0, self.mid),
+                      f16=self.f16, exp=self.exp, exp0=self.exp0, tmax=self.tmax)
 
     def ptr_hi(self):
         return ct.c_void_p(self.hi.data_ptr() + 2 * self.offset)
@@ -57,17 +78,22 @@ class Planes:
 
     def to_float(self):
         n = (self.rows - 1) * self.ld + self.cols
-        idx = self.hi[:, self.offset: self.offset + n].float() + self.lo[:, self.offset: self.offset + n].float()
+        sl = slice(self.offset, self.offset + n)
+        val = self.hi[:, sl].float() + self.lo[:, sl].float()
         if self.mid is not None:
-            idx = (self.hi[:, self.offset: self.offset + n].float() + self.mid[:, self.offset: self.offset + n].float()) + \
-                self.lo[:, self.offset: self.offset + n].float()
-        full = torch.zeros(self.batch, self.rows * self.ld, device=idx.device)
-        full[:, :n] = idx
+            val = (self.hi[:, sl].float() + self.mid[:, sl].float()) + self.lo[:, sl].float()
+        if self.f16:
+            e = torch.full((self.batch,), float(self.exp0), device=val.device)
+            if self.exp is not None:
+                e = e + self.exp.float()
+            val = val * torch.exp2(-e).unsqueeze(1)
+        full = torch.zeros(self.batch, self.rows * self.ld, device=val.device)
+        full[:, :n] = val
         return full.view(self.batch, self.rows, self.ld)[:, :, : self.cols]
 
 
 def split3(X):
-    """fp32 (batch, rows, cols) tensor -> three-plane Planes (hi, mid, lo; 24 significant bits)."""
+    """fp32 (batch, rows, cols) tensor -> three-plane bf16 Planes (hi, mid, lo; 24 significant bits)."""
     assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
     b, r, c = X.shape
     P = Planes(b, r, c, X.device, planes=3)
@@ -78,8 +104,8 @@ def split3(X):
     return P
 
 
-def split(X):
-    """fp32 (batch, rows, cols) tensor (last dim contiguous) -> Planes."""
+def split_bf16(X):
+    """fp32 (batch, rows, cols) tensor (last dim contiguous) -> two-plane bf16 Planes."""
     assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
     b, r, c = X.shape
     P = Planes(b, r, c, X.device)
@@ -90,8 +116,31 @@ def split(X):
     return P
 
 
-def split_rows(X, index=None, scale=None):
-    """Planes of the matrices whose row i is scale[b, i] * X[b, index[b, i], :] (qt_split_bf16_rows).
+def _split_f16(X, index, scale, target):
+    b, R, c = X.shape
+    rows = index.shape[1] if index is not None else R
+    scratch = torch.empty(2, b, dtype=torch.int32, device=X.device)      # [0]: amax (as float bits), [1]: exponents
+    P = Planes(b, rows, c, X.device, f16=True, exp=scratch[1], exp0=0, tmax=target)
+    with torch.cuda.device(X.device):
+        rc = F.lib.qt_split_f16(_ptr(X), X.stride(1), X.stride(0), rows, c, b,
+                                _ptr(index), index.stride(0) if index is not None else 0,
+                                _ptr(scale), scale.stride(0) if scale is not None else 0,
+                                _ptr(scratch[0]), None, target, _ptr(scratch[1]),
+                                P.ptr_hi(), P.ptr_lo(), P.ld, P.stride, F._stream(X))
+    F._check(rc, "split_f16")
+    return P
+
+
+def split(X, target=None):
+    """fp32 (batch, rows, cols) tensor (last dim contiguous) -> Planes (scaled fp16 unless FP16_PLANES is off)."""
+    assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
+    if not FP16_PLANES:
+        return split_bf16(X)
+    return _split_f16(X, None, None, SPLIT_TARGET if target is None else target)
+
+
+def split_rows(X, index=None, scale=None, target=None):
+    """Planes of the matrices whose row i is scale[b, i] * X[b, index[b, i], :].
     X: fp32 (batch, R, cols); index: int64 (batch, rows) or None; scale: fp32 (batch, rows) or None."""
     assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
     b, R, c = X.shape
@@ -100,6 +149,8 @@ def split_rows(X, index=None, scale=None):
         assert index.dtype == torch.int64 and index.shape[0] == b and index.stride(1) == 1
     if scale is not None:
         assert scale.dtype == torch.float32 and scale.shape == (b, rows) and scale.stride(1) == 1
+    if FP16_PLANES:
+        return _split_f16(X, index, scale, SPLIT_TARGET if target is None else target)
     P = Planes(b, rows, c, X.device)
     with torch.cuda.device(X.device):
         rc = F.lib.qt_split_bf16_rows(_ptr(X), X.stride(1), X.stride(0), rows, c, b,
@@ -110,12 +161,19 @@ def split_rows(X, index=None, scale=None):
     return P
 
 
+def _ceil_log2(x):
+    return int(math.ceil(math.log2(max(float(x), 1e-30))))
+
+
 def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=None, want_planes=False,
-           want_float=True, out_planes=None):
+           want_float=True, out_planes=None, out_bound=None):
     """alpha * op(A) @ op(B) + beta * C for batches held as Planes.
 
     A holds (b, M, K) (or (b, K, M) with trans_a); B holds (b, K, N) (or (b, N, K) with
-    trans_b).  Returns (fp32 tensor or None, Planes or None).
+    trans_b).  Returns (fp32 tensor or None, Planes or None).  Plane output of an fp16-plane
+    product: into `out_planes` (its exponents are kept - the caller vouches that the result fits),
+    or freshly allocated with exponent such that |result| <= out_bound fits if `out_bound` is
+    given, else with the worst-case exponent K * max|A| * max|B| * |alpha| (beta must be 0 then).
     """
     M = A.cols if trans_a else A.rows
     K = A.rows if trans_a else A.cols
@@ -128,60 +186,61 @@ def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=
     if want_float:
         D = out if out is not None else torch.empty(b, M, N, dtype=torch.float32, device=dev)
         assert D.stride(2) == 1
-    P = out_planes if out_planes is not None else (Planes(b, M, N, dev) if want_planes else None)
-    if P is not None:
-        assert P.rows == M and P.cols == N and P.batch == b
     if C is not None:
         assert C.stride(2) == 1
-    # kernel view: A logically M x K (a_mn: stored [K][M]); B logically N x K (b_mn: stored [K][N])
-    a_mn = 1 if trans_a else 0
-    b_mn = 0 if trans_b else 1
-    if A.mid is not None or B.mid is not None:
-        assert A.mid is not None and B.mid is not None
-        if P is not None:
-            # fp32-level product whose result is also handed on as three planes
-            if out_planes is None:
-                P = Planes(b, M, N, dev, planes=3)
-            assert P.mid is not None
-            gemm_ex(A, B, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C, D=D, P=P)
-            return D, P
-        assert D is not None
+    three = A.mid is not None or B.mid is not None
+    f16 = A.f16 or B.f16
+    if three:
+        assert A.mid is not None and B.mid is not None and not f16
+    else:
+        assert A.f16 == B.f16, "both operands must use the same plane encoding"
+    P = out_planes
+    if P is None and want_planes:
+        P = Planes(b, M, N, dev, planes=3 if three else 2, f16=f16)
+    if P is not None:
+        assert P.rows == M and P.cols == N and P.batch == b and P.f16 == f16 and (P.mid is not None) == three
+    if not three and not f16 and not (P is None and D is None):
+        # plain bf16 two-plane product: the fixed-signature entry point
+        a_mn, b_mn = (1 if trans_a else 0), (0 if trans_b else 1)
         with torch.cuda.device(dev):
-            rc = F.lib.qt_gemm_bf16x6(
-                A.ptr_hi(), A.ptr_mid(), A.ptr_lo(), A.ld, A.stride, a_mn,
-                B.ptr_hi(), B.ptr_mid(), B.ptr_lo(), B.ld, B.stride, b_mn,
+            rc = F.lib.qt_gemm_bf16x3(
+                A.ptr_hi(), A.ptr_lo(), A.ld, A.stride, a_mn,
+                B.ptr_hi(), B.ptr_lo(), B.ld, B.stride, b_mn,
                 M, N, K, b, float(alpha), float(beta),
                 _ptr(C), C.stride(1) if C is not None else 0, C.stride(0) if C is not None else 0,
-                _ptr(D), D.stride(1), D.stride(0), F._stream(A.hi))
-        F._check(rc, "gemm_bf16x6")
-        return D, None
-    with torch.cuda.device(dev):
-        rc = F.lib.qt_gemm_bf16x3(
-            A.ptr_hi(), A.ptr_lo(), A.ld, A.stride, a_mn,
-            B.ptr_hi(), B.ptr_lo(), B.ld, B.stride, b_mn,
-            M, N, K, b, float(alpha), float(beta),
-            _ptr(C), C.stride(1) if C is not None else 0, C.stride(0) if C is not None else 0,
-            _ptr(D), D.stride(1) if D is not None else 0, D.stride(0) if D is not None else 0,
-            P.ptr_hi() if P else None, P.ptr_lo() if P else None, P.ld if P else 0, P.stride if P else 0,
-            F._stream(A.hi))
-    F._check(rc, "gemm_bf16x3")
+                _ptr(D), D.stride(1) if D is not None else 0, D.stride(0) if D is not None else 0,
+                P.ptr_hi() if P else None, P.ptr_lo() if P else None, P.ld if P else 0, P.stride if P else 0,
+                F._stream(A.hi))
+        F._check(rc, "gemm_bf16x3")
+        return D, P
+    kw = {}
+    if f16 and P is not None:
+        if out_planes is not None:
+            kw = dict(out_exp=P.exp, out_exp0=P.exp0)
+        elif out_bound is not None:
+            P.exp, P.exp0, P.tmax = None, F16_MAX_EXP - _ceil_log2(out_bound), F16_MAX_EXP
+            kw = dict(out_exp0=P.exp0)
+        else:
+            assert beta == 0.0 or C is None, "worst-case plane exponents cannot account for a C operand"
+            rel = F16_MAX_EXP - _ceil_log2(K) - A.tmax - B.tmax - _ceil_log2(abs(alpha))
+            P.exp = torch.empty(b, dtype=torch.int32, device=dev)
+            P.exp0, P.tmax = 0, F16_MAX_EXP
+            kw = dict(out_rel=1, out_exp0=rel, out_exp_w=P.exp)
+    gemm_ex(A, B, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta, C=C, D=D, P=P, **kw)
     return D, P
 
 
 def matmul_q4(A, B, code, out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, old=None):
     """out <- quantize(alpha * op(A) @ op(B) + beta * dequantize(old)) on 4-bit block-64 state.
 
-    A, B: Planes (both two-plane or both three-plane) of a square product (b, n, n), n a multiple of 16.  `out` and
+    A, B: Planes of one encoding, of a square product (b, n, n), n a multiple of 16.  `out` and
     `old` are (codes uint8 (b, row_bytes), absmax fp32 (b, n*nb), diag fp32 (b, n) or None);
     `old=None` drops the C operand, `old is out` updates in place.  Same bytes as
-    dequantize -> six-product GEMM -> quantize, without an fp32 copy of the state in HBM
-    (qt_gemm_bf16x6_q4).
+    dequantize -> product -> quantize, without an fp32 copy of the state in HBM.
     """
     M = A.cols if trans_a else A.rows
-    K = A.rows if trans_a else A.cols
-    Kb = B.cols if trans_b else B.rows
     N = B.rows if trans_b else B.cols
-    assert K == Kb and A.batch == B.batch and M == N and (A.mid is None) == (B.mid is None)
+    assert M == N and A.batch == B.batch and (A.mid is None) == (B.mid is None) and A.f16 == B.f16
     b = A.batch
     var, absmax, diag = out
     assert var.dtype == torch.uint8 and var.dim() == 2 and var.shape[0] == b and var.stride(1) == 1
@@ -191,29 +250,19 @@ def matmul_q4(A, B, code, out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0
         ovar, oabs, odiag = old
         assert ovar.stride(0) == var.stride(0) and oabs.stride(0) == absmax.stride(0)
         assert odiag is None or diag is None or odiag.stride(0) == diag.stride(0)
-    tail = (N, K, b, float(alpha), float(beta), _ptr(code),
-            _ptr(ovar), _ptr(oabs), _ptr(odiag), _ptr(var), _ptr(absmax), _ptr(diag),
-            var.stride(0), absmax.stride(0),
-            (diag if diag is not None else odiag).stride(0) if (diag is not None or odiag is not None) else 0,
-            F._stream(var))
-    with torch.cuda.device(var.device):
-        if A.mid is not None:
-            rc = F.lib.qt_gemm_bf16x6_q4(
-                A.ptr_hi(), _ptr(A.mid), A.ptr_lo(), A.ld, A.stride, 1 if trans_a else 0,
-                B.ptr_hi(), _ptr(B.mid), B.ptr_lo(), B.ld, B.stride, 0 if trans_b else 1, *tail)
-        else:
-            rc = F.lib.qt_gemm_bf16x3_q4(
-                A.ptr_hi(), A.ptr_lo(), A.ld, A.stride, 1 if trans_a else 0,
-                B.ptr_hi(), B.ptr_lo(), B.ld, B.stride, 0 if trans_b else 1, *tail)
-    F._check(rc, "gemm_q4")
+    sd = (diag if diag is not None else odiag).stride(0) if (diag is not None or odiag is not None) else 0
+    gemm_ex(A, B, trans_a=trans_a, trans_b=trans_b, alpha=alpha, beta=beta,
+            q=dict(code=code, q_in=ovar, absmax_in=oabs, diag_in=odiag, q_out=var, absmax_out=absmax, diag_out=diag,
+                   stride_codes=var.stride(0), stride_absmax=absmax.stride(0), stride_diag=sd))
 
 
 def gemm_ex(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, D=None, P=None, T=None, t_c0=0.0, t_c1=0.0,
-            maxdev=None, a_slot=None, b_slot=None, d_slot=None, active=None, batch=None):
-    """General product (qt_gemm_ex): A, B are Planes (two- or three-plane, possibly holding more
-    entries than `batch` when slot arrays select among them); results go to the fp32 tensor D and / or
-    the Planes P, and optionally T = t_c0 * I + t_c1 * result (three planes, indexed by matrix number).
-    maxdev: fp32 (batch,) combined with max |result - I|; *_slot, active: int32 (batch,) device tensors."""
+            maxdev=None, a_slot=None, b_slot=None, d_slot=None, active=None, batch=None,
+            out_exp=None, out_exp0=0, out_rel=0, out_exp_w=None, q=None):
+    """General product (qt_gemm_ex): A, B are Planes (possibly holding more entries than `batch` when slot
+    arrays select among them); results go to the fp32 tensor D and / or the Planes P, optionally
+    T = t_c0 * I + t_c1 * result (three bf16 planes, indexed by matrix number), or - with `q` - into
+    4-bit state.  maxdev: fp32 (batch,) combined with max |result - I|; *_slot, active: int32 device tensors."""
     from qtensor.cextension import GemmDesc
     M = A.cols if trans_a else A.rows
     K = A.rows if trans_a else A.cols
@@ -237,6 +286,15 @@ def gemm_ex(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, D=N
             d.ldp, d.strideP = X.ld, X.stride
     d.t_c0, d.t_c1 = float(t_c0), float(t_c1)
     d.maxdev, d.a_slot, d.b_slot, d.d_slot, d.active = ip(maxdev), ip(a_slot), ip(b_slot), ip(d_slot), ip(active)
+    if A.f16 or B.f16:
+        assert A.f16 and B.f16
+        d.f16, d.kc = 1, CHAIN_K
+        d.a_exp, d.b_exp, d.ab_exp0 = ip(A.exp), ip(B.exp), int(A.exp0 + B.exp0)
+        d.out_exp, d.out_exp0, d.out_rel, d.out_exp_w = ip(out_exp), int(out_exp0), int(out_rel), ip(out_exp_w)
+    if q is not None:
+        d.q_code, d.q_in, d.q_absmax_in, d.q_diag_in = ip(q["code"]), ip(q["q_in"]), ip(q["absmax_in"]), ip(q["diag_in"])
+        d.q_out, d.q_absmax_out, d.q_diag_out = ip(q["q_out"]), ip(q["absmax_out"]), ip(q["diag_out"])
+        d.q_stride_codes, d.q_stride_absmax, d.q_stride_diag = q["stride_codes"], q["stride_absmax"], q["stride_diag"]
     with torch.cuda.device(A.hi.device):
         rc = F.lib.qt_gemm_ex(ct.byref(d), F._stream(A.hi))
     F._check(rc, "gemm_ex")

@@ -36,12 +36,12 @@ def _reflect(Vk, Tk, target, target_planes, transpose_t, Pv=None):
         W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
         target.baddbmm_(Vk, W, alpha=-1.0)
         return
-    split = _gemm.split3 if target_planes.mid is not None else _gemm.split
+    split = _gemm.split
     if Pv is None:
         Pv = split(Vk)
     W, _ = _gemm.matmul(Pv, target_planes, trans_a=True)                   # Vk^T target, (w x t)
     W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
-    _gemm.matmul(Pv, split(W), alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes, want_planes=True)
+    _gemm.matmul(Pv, split(W), alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
 
 
 def _merge_t(Vo, Tp, widths, Pv=None):
@@ -78,11 +78,12 @@ def _merge_t(Vo, Tp, widths, Pv=None):
     return T
 
 
-def householder_q(X, tensor_cores=True, precise=False):
+def householder_q(X, tensor_cores=True):
     """Q of the QR factorisation of each X[b] (X: (B, n, n) fp32 CUDA, overwritten).
-    `tensor_cores=False` keeps every product in fp32 library products; `precise` runs the
-    tensor-core products on three bf16 planes per operand (fp32-level accuracy, twice the MMAs)
-    instead of two (operands rounded to 16 significant bits)."""
+    `tensor_cores=False` keeps every product in fp32 library products.  The planes of X carry one
+    exponent per matrix, fixed when X is first split: Householder reflections preserve column
+    norms, so no entry of the trailing matrix outgrows sqrt(n) times the largest entry of X, which
+    the split's headroom (largest entry below 2^9 of fp16's 2^16) covers up to n = 16384."""
     B, n, _ = X.shape
     if (not X.is_cuda) or n > MAX_ORDER or n < 2:
         return torch.linalg.qr(X).Q
@@ -96,7 +97,7 @@ def householder_q(X, tensor_cores=True, precise=False):
     T = torch.empty(B, npan, PANEL, PANEL, dtype=torch.float32, device=X.device)
     stream = F._stream(X)
     blocks = []                                           # (J0, wo, T_big)
-    split = _gemm.split3 if precise else _gemm.split
+    split = _gemm.split
     with torch.cuda.device(X.device):
         Xp = split(X) if tc else None
         for J0 in range(0, n, OUTER):

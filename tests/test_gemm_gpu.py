@@ -37,7 +37,7 @@ def test_alpha_beta_c_and_plane_output(native_lib):
     A = torch.randn(b, M, K, device="cuda", generator=g)
     B = torch.randn(b, K, N, device="cuda", generator=g)
     C = torch.randn(b, M, N, device="cuda", generator=g)
-    D, P = _gemm.matmul(_gemm.split(A), _gemm.split(B), alpha=-0.5, beta=1.5, C=C, want_planes=True)
+    D, P = _gemm.matmul(_gemm.split(A), _gemm.split(B), alpha=-0.5, beta=1.5, C=C, want_planes=True, out_bound=100.0)
     assert device_ok(native_lib)
     ref = -0.5 * (A.double() @ B.double()) + 1.5 * C.double()
     assert rel(D, ref) < TOL
@@ -50,12 +50,23 @@ def test_alpha_beta_c_and_plane_output(native_lib):
     assert rel(big[:, :, :N], A.double() @ B.double()) < TOL
 
 
-def test_split_planes_are_exact_to_16_bits(native_lib):
+def test_split_planes_precision(native_lib):
+    """bf16 planes: every element to 16 significant bits.  Scaled fp16 planes: 22 significant bits
+    for every element within 2^12 of the matrix's largest one, and an absolute error below
+    2^-33 of the largest element for the rest (columns here span six decades)."""
     from optimizers import _gemm
     X = torch.randn(2, 77, 130, device="cuda") * torch.logspace(-3, 3, 130, device="cuda")
-    P = _gemm.split(X)
+    P = _gemm.split_bf16(X)
     err = (P.to_float() - X).abs() / X.abs().clamp_min(1e-30)
     assert float(err.max()) < 2.0 ** -15
+    H = _gemm.split(X)
+    assert H.f16 and H.exp is not None
+    amax = X.abs().amax(dim=(1, 2), keepdim=True)
+    scaled_max = amax.squeeze() * torch.exp2(H.exp.float())
+    assert bool((scaled_max < 2.0 ** _gemm.SPLIT_TARGET).all()) and bool((scaled_max >= 2.0 ** (_gemm.SPLIT_TARGET - 1)).all())
+    err = (H.to_float() - X).abs()
+    assert bool((err <= torch.maximum(X.abs() * 2.0 ** -21, amax * 2.0 ** -32)).all())
+    assert device_ok(native_lib)
 
 
 @pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True)])
@@ -136,14 +147,16 @@ def _dequantize_batch(lib, st, code, n):
     return out
 
 
+@pytest.mark.parametrize("encoding", ["f16x2", "bf16x3"])
 @pytest.mark.parametrize("n,k,axis,diagreal,with_old", [
     (128, 64, 0, True, True), (512, 384, 1, True, True), (1200, 768, 0, True, True), (1200, 3072, 1, False, True),
     (672, 768, 0, True, False), (1104, 200, 1, False, True), (2048, 2048, 0, True, True), (16, 40, 0, True, True),
     (48, 48, 1, False, True)])
-def test_quantizing_epilogue_equals_unfused_sequence(native_lib, n, k, axis, diagreal, with_old):
+def test_quantizing_epilogue_equals_unfused_sequence(native_lib, n, k, axis, diagreal, with_old, encoding):
     """state <- quantize(w2 * G G^T + w1 * dequantize(state)) inside the GEMM epilogue: the code
-    bytes, block scales and diagonal must equal dequantize -> six-product GEMM -> quantize bit for
-    bit, and the dequantized result must be within 4-bit quantization error of the float64 value."""
+    bytes, block scales and diagonal must equal dequantize -> product -> quantize bit for bit (same
+    operand planes: scaled fp16 pairs as the optimizers use them, or three bf16 planes), and the
+    dequantized result must be within 4-bit quantization error of the float64 value."""
     import qtensor.functional as F
     from optimizers import _gemm
     dev = "cuda"
@@ -160,7 +173,7 @@ def test_quantizing_epilogue_equals_unfused_sequence(native_lib, n, k, axis, dia
     old = _state(b, n, dev, diagreal)
     _quantize_batch(native_lib, L0.contiguous(), code, old)
     w1, w2 = 0.95, 0.05
-    P = _gemm.split3(G)
+    P = _gemm.split(G) if encoding == "f16x2" else _gemm.split3(G)
     ta, tb = (False, True) if axis == 0 else (True, False)
     # unfused sequence
     Lold = _dequantize_batch(native_lib, old, code, n) if with_old else None
@@ -186,7 +199,36 @@ def test_quantizing_epilogue_equals_unfused_sequence(native_lib, n, k, axis, dia
     ref = w2 * (Gd @ Gd.transpose(1, 2) if axis == 0 else Gd.transpose(1, 2) @ Gd)
     if with_old:
         ref = ref + w1 * Lold.double()
-    assert rel(D, ref) < TOL
+    assert rel(D, ref) < 2e-6, rel(D, ref)                # both encodings are fp32-grade
+
+
+def test_fp16_plane_products_reach_fp32_accuracy(native_lib):
+    """Scaled fp16 planes (22 bits) with 128-k accumulation chains against float64, next to the
+    same product from bf16 planes (16 bits, one chain) and from an fp32 library product: chained
+    plane outputs (explicit bound, worst-case exponent) and a large common scale included."""
+    from optimizers import _gemm
+    g = torch.Generator(device="cuda").manual_seed(41)
+    b, M, N, K = 2, 300, 520, 1200
+    A = torch.randn(b, M, K, device="cuda", generator=g) * 3e4          # scales far from 1 on purpose
+    B = torch.randn(b, K, N, device="cuda", generator=g) * 2e-5
+    ref = A.double() @ B.double()
+    D16, _ = _gemm.matmul(_gemm.split(A), _gemm.split(B))
+    Dbf, _ = _gemm.matmul(_gemm.split_bf16(A), _gemm.split_bf16(B))
+    assert device_ok(native_lib)
+    e16, ebf, e32 = rel(D16, ref), rel(Dbf, ref), rel(torch.bmm(A, B), ref)
+    print(f"fp16x2 {e16:.2e}  bf16x2 {ebf:.2e}  fp32 library {e32:.2e}")
+    assert e16 < 2e-6 and e16 < 4 * e32 + 1e-6 and ebf < 1e-4
+    # plane outputs: worst-case exponent, then consumed by a second product
+    _, P = _gemm.matmul(_gemm.split(A), _gemm.split(B), want_float=False, want_planes=True)
+    assert rel(P.to_float(), ref) < 2e-6
+    C = torch.randn(b, N, 200, device="cuda", generator=g)
+    D2, _ = _gemm.matmul(P, _gemm.split(C))
+    assert device_ok(native_lib)
+    assert rel(D2, ref @ C.double()) < 3e-6
+    # explicit bound that is too small: the planes clamp and the sticky error word reports it
+    _gemm.matmul(_gemm.split(A), _gemm.split(B), want_float=False, want_planes=True, out_bound=1e-3)
+    torch.cuda.synchronize()
+    assert native_lib.qt_device_error(1) == 9
 
 
 def test_split_rows_gathers_and_scales(native_lib):

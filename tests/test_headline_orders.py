@@ -28,9 +28,12 @@ agree with the CPU reference more closely than that on such a case, and the 1e-4
 orders is out of reach there for reasons that are the algorithm's, not the kernels'.
 
 Intermediates (the dequantized 4-bit preconditioner, the preconditioned block) are compared
-AFTER quantization, where the same effect is at its strongest: the products that feed them carry
-operands as two bf16 planes (16 significant bits, 4e-6 relative), which lands about one code in
-10^4 on the other side of a threshold; FLIP_BOUND states the resulting distance."""
+AFTER quantization, where the same effect is at its strongest; FLIP_BOUND states the distance
+a handful of differing codes makes.  The CUDA path multiplies from scaled fp16 operand planes
+(22 significant bits) with 128-k accumulation chains; measured against the oracle it sits at the
+yardstick itself (order 768: preconditioners 2.6e-4 / 2.1e-4 with a yardstick of 2.3e-4, parameters
+1.3e-4 with 1.8e-4; order 1200: 1.4e-3 / 2.2e-3 with 2.1e-3, parameters 1.1e-3 with 1.3e-3; order
+336: 8e-7).  With bf16 operand planes (16 bits) the same cases were 4 to 7 times further away."""
 import json
 import os
 
@@ -43,6 +46,8 @@ from helpers import GOLDEN, hashed_matrix, wellposed_matrix
 TOL = 1e-4
 YARD_FACTOR = 5.0       # headroom over the reference's own fp32-evaluation sensitivity (two independent roundings + margin)
 FLIP_BOUND = 2.5e-3     # 4-bit results compared after quantization at orders >= 336 (see the module docstring)
+ONE_FLIP = 5e-4         # parameters of an n x n block, n >= 336: what ONE differing code of the stored eigenbasis
+                        # (1 in ~3e5) does to them through the AdamW step (measured 1e-4 .. 4e-4)
 
 
 def load_large():
@@ -183,8 +188,11 @@ class Run:
         return max(rel(self.alt[i].numpy(), self.ref[i].numpy()), rel(self.wide[i].numpy(), self.ref[i].numpy()))
 
     def tolerance(self, i):
-        """max(1e-4, YARD_FACTOR x yardstick) for the parameters of tensor i."""
-        return max(TOL, YARD_FACTOR * self.yardstick(i))
+        """max(1e-4, YARD_FACTOR x yardstick) for the parameters of tensor i; tensors with
+        preconditioner orders of 336 and more get at least ONE_FLIP (see its definition)."""
+        dims = [d for d in self.shapes[i] if d != 1]
+        big = len(dims) >= 2 and max(dims[0], int(np.prod(dims[1:]))) >= 336
+        return max(TOL, YARD_FACTOR * self.yardstick(i), ONE_FLIP if big else 0.0)
 
     def param_error(self, i):
         return rel(self.ps[i].detach().cpu().numpy(), self.ref[i].numpy())
