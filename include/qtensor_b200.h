@@ -168,6 +168,20 @@ int qt_householder_panel(const float *A, long long strideA, int order, int count
                          float *V, long long strideV, float *T, long long strideT, void *stream);
 
 /*
+ * qt_householder_panel preceded, in the same launch, by the rank-32 update the previous panel of
+ * the same outer block leaves to do (right-looking blocked QR inside a block of up to four
+ * panels ending at column block_end): with prev_width > 0 the block reflector of the panel at
+ * columns j0-prev_width .. j0-1 (its vectors in V, its factor in Tprev + m*strideT) is applied
+ * to columns j0 .. block_end-1, rows j0-prev_width .. order-1 of A IN PLACE (one CTA per matrix and
+ * 32-column chunk), and the CTA of the first chunk then factors the panel at j0 as above.
+ * prev_width == 0 is qt_householder_panel.  Replaces three library products per panel
+ * (V^T C, T^T (.), C - V (.)) of a separately launched update.
+ */
+int qt_householder_panel_fused(float *A, long long strideA, int order, int count, int j0, int width,
+                               float *V, long long strideV, float *T, long long strideT,
+                               int prev_width, const float *Tprev, int block_end, void *stream);
+
+/*
  * Triangular factor T (width x width, width <= 128) of a block of up to four consecutive panels,
  * H_1 .. H_width = I - Vo T Vo^T, from the panels' factors (Tp + m*strideTp: consecutive 32 x 32
  * row-major factors as written by qt_householder_panel) and the Gram matrix G = Vo^T Vo
@@ -318,15 +332,17 @@ int qt_inverse_root_newton(float *G, long long strideG, int n, int batch, int p,
  * fp32 matrices -> scaled fp16 planes (the operand format of qt_gemm_ex with f16 != 0), with the
  * optional row gather and row scale of qt_split_bf16_rows.  Plane entry = x * 2^e[b] as
  * hi = fp16(.), lo = fp16(. - hi).  Exponents:
- *   amax_scratch != NULL: e[b] is chosen from the largest magnitude of matrix b so that it lands
- *     just below 2^target_or_exp0 (amax_scratch: `batch` floats of device scratch, overwritten);
- *   amax_scratch == NULL: e[b] = exp_in[b] (NULL: 0) + target_or_exp0.
+ *   amax != NULL: e[b] is chosen from amax[b] so that a magnitude of amax[b] lands just below
+ *     2^target_or_exp0.  compute_amax != 0: amax is `batch` floats of scratch and is filled here
+ *     with each matrix's largest magnitude (one extra pass over X); compute_amax == 0: amax holds
+ *     upper bounds the caller already knows (a value above its bound is clamped in the planes);
+ *   amax == NULL: e[b] = exp_in[b] (NULL: 0) + target_or_exp0.
  * exp_out (may be NULL) receives e[b].  Additive; the reference multiplies fp32 tensors with
  * torch.matmul (e.g. optimizers/shampoo2.py:188-190).
  */
 int qt_split_f16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
                  const long long *index, long long stride_index, const float *scale, long long stride_scale,
-                 float *amax_scratch, const int *exp_in, int target_or_exp0, int *exp_out,
+                 float *amax, int compute_amax, const int *exp_in, int target_or_exp0, int *exp_out,
                  void *hi, void *lo, long long ldp, long long strideP, void *stream);
 
 /* Test hook: 128 or 256 forces the output-tile width of two-plane products, -1 restores the

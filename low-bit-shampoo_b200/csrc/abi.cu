@@ -143,8 +143,15 @@ int qt_merge_t(const float *G, long long ldg, long long strideG, const float *Tp
 
 int qt_householder_panel(const float *A, long long strideA, int order, int count, int j0, int width,
                          float *V, long long strideV, float *T, long long strideT, void *stream) {
-    return launch_householder_panel(A, strideA, order, count, j0, width, V, strideV, T, strideT,
+    return launch_householder_panel(const_cast<float *>(A), strideA, order, count, j0, width, V, strideV, T, strideT,
                                     static_cast<cudaStream_t>(stream));
+}
+
+int qt_householder_panel_fused(float *A, long long strideA, int order, int count, int j0, int width,
+                               float *V, long long strideV, float *T, long long strideT,
+                               int prev_width, const float *Tprev, int block_end, void *stream) {
+    return launch_householder_panel(A, strideA, order, count, j0, width, V, strideV, T, strideT,
+                                    static_cast<cudaStream_t>(stream), prev_width, Tprev, block_end);
 }
 
 }  // extern "C"

@@ -40,11 +40,14 @@ static constexpr unsigned WAIT_LIMIT = 1u << 18;
 //                      128x256x16 MMA instead of 8 KiB per 128x128x16 one: 25 % less shared-memory
 //                      traffic per flop, which is what bounds the 128 x 128 tile)
 //   NP = 3, BN_ = 128: 96 KiB per stage, 2 stages
-template <int NP, int BN_> struct TileCfg {
+template <int NP, int BN_, int EC> struct TileCfg {
     static constexpr int B_TILES = BN_ / 128;
     static constexpr int STAGE_BYTES = NP * (1 + B_TILES) * PLANE_TILE_BYTES;
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
-    static constexpr int EPI_WARPS = BN_ / 32;                       // 4 or 8 epilogue warps (128 columns each per row quarter)
+    // Epilogue warp e reads TMEM lanes 32 (e & 3) .. +31 and EC accumulator columns starting at
+    // EC (e >> 2).  EC = 64 halves the partial sums a thread holds (no register spills with
+    // 8 + 2 warps) and doubles the loads in flight for epilogues that stream C, D and planes.
+    static constexpr int EPI_WARPS = 4 * (BN_ / EC);
     static constexpr int THREADS = (EPI_WARPS + 2) * 32;
     static constexpr int TMEM_COLS = 2 * BN_;                        // two accumulators
 };
@@ -365,10 +368,10 @@ __device__ __forceinline__ void store_planes_f16(__half *hi, __half *lo, const f
     }
 }
 
-template <bool A_MN, bool B_MN, int NP, int BN_, bool QOUT = false>
-__global__ void __launch_bounds__((BN_ / 32 + 2) * 32, 1)
+template <bool A_MN, bool B_MN, int NP, int BN_, int EC, bool QOUT = false>
+__global__ void __launch_bounds__(TileCfg<NP, BN_, EC>::THREADS, 1)
 k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
-    using Cfg = TileCfg<NP, BN_>;
+    using Cfg = TileCfg<NP, BN_, EC>;
     __shared__ QuantTablesHolder<QOUT> qtab;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
@@ -528,13 +531,13 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 }
             }
         }
-    } else {
+    } else if (warp < EPI_WARPS) {
         // ---------------- epilogue: warp e reads TMEM lanes 32 (e & 3) .. +31 (lane = output row) and
         // the 128 accumulator columns [128 (e >> 2), +128) of the tile.  Partial sums of the chunks
         // are added in registers; the final combine / conversion / store works on 16 columns at a
         // time with 256-bit accesses straight from registers (no shared-memory staging: the tensor
         // core's operand fetch already uses the shared-memory bandwidth).
-        const int quad = warp & 3, half = warp >> 2;
+        const int quad = warp & 3, seg = warp >> 2;
         const bool has_c = p.C != nullptr && p.beta != 0.0f;
         const bool wide_d = ((p.ldc | p.ldd | p.strideC | p.strideD) & 7) == 0 &&
                             ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(p.D)) & 31) == 0;
@@ -546,23 +549,23 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             int tm, tn, b;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
             if (skipped(b)) continue;
-            const int m0 = tm * BM, n0 = tn * BN_ + half * 128;
+            const int m0 = tm * BM, n0 = tn * BN_ + seg * EC;
             const int row = m0 + quad * 32 + lane;
             const bool row_ok = row < p.M;
-            const int valid = min(128, p.N - n0);              // columns of this warp's half that exist (may be <= 0)
-            float sum[128];
+            const int valid = min(EC, p.N - n0);               // columns of this warp's segment that exist (may be <= 0)
+            float sum[EC];
 #pragma unroll
-            for (int q = 0; q < 128; ++q) sum[q] = 0.0f;
+            for (int q = 0; q < EC; ++q) sum[q] = 0.0f;
             bool ok = true;
             for (int ch = 0; ch < nchunks; ++ch, ++j) {
                 const int acc = j & 1;
                 ok = mbar_wait_warp(acc_full(acc), (j >> 1) & 1, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN_ + half * 128);
+                const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN_ + seg * EC);
                 if (valid > 0) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < EC / 32; ++c) {
                         float v[32];
                         tmem_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), v);
 #pragma unroll
@@ -582,7 +585,7 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             }
             const float alpha_eff = p.f16 ? p.alpha * exp2f((float)-e_in) : p.alpha;
             if constexpr (QOUT) {
-                if (row_ok && valid > 0) quantizing_epilogue<128>(qtab.t, p, sum, b, row, n0, alpha_eff);
+                if (row_ok && valid > 0) quantizing_epilogue<EC>(qtab.t, p, sum, b, row, n0, alpha_eff);
             } else {
                 const int bo = p.d_slot ? __ldg(p.d_slot + b) : b;
                 float dev = 0.0f;                               // max |result - I| over this thread's elements
@@ -590,7 +593,7 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 if (p.f16 && p.Dhi) {
                     const int e_out = p.out_exp ? __ldg(p.out_exp + bo) + p.out_exp0 : (p.out_rel ? e_in + p.out_exp0 : p.out_exp0);
                     pscale = exp2f((float)e_out);
-                    if (p.out_exp_w && tm == 0 && tn == 0 && half == 0 && quad == 0 && lane == 0) p.out_exp_w[bo] = e_out;
+                    if (p.out_exp_w && tm == 0 && tn == 0 && seg == 0 && quad == 0 && lane == 0) p.out_exp_w[bo] = e_out;
                 }
                 if (row_ok && valid > 0) {
                     const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
@@ -609,14 +612,14 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                     };
                     fetch_c(0, cnext);
 #pragma unroll
-                    for (int q = 0; q < 128; q += 16) {
+                    for (int q = 0; q < EC; q += 16) {
                         if (q >= valid) continue;
                         const bool full16 = q + 16 <= valid;
                         float o[16];
                         if (has_c) {
 #pragma unroll
                             for (int t = 0; t < 16; ++t) o[t] = cnext[t];
-                            if (q + 16 < 128) fetch_c(q + 16, cnext);
+                            if (q + 16 < EC) fetch_c(q + 16, cnext);
 #pragma unroll
                             for (int t = 0; t < 16; ++t) o[t] = fmaf(p.beta, o[t], alpha_eff * sum[q + t]);
                         } else {
@@ -839,6 +842,7 @@ k_split_f16_rows(const float *__restrict__ X, long long ldx, long long strideX, 
     constexpr int E = WIDE ? 16 : 1;
     const int per_row = cols / E;
     const long long total = (long long)rows * per_row;
+    float worst = 0.0f;                                      // a bound the caller vouched for may be violated
     for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(t / per_row), c = (int)(t - (long long)r * per_row) * E;
         const long long src = idx ? idx[r] : (long long)r;
@@ -850,7 +854,8 @@ k_split_f16_rows(const float *__restrict__ X, long long ldx, long long strideX, 
             unsigned H[8], L[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float a0 = v[2 * j] * f, a1 = v[2 * j + 1] * f;
+                const float a0 = fminf(fmaxf(v[2 * j] * f, -65000.0f), 65000.0f), a1 = fminf(fmaxf(v[2 * j + 1] * f, -65000.0f), 65000.0f);
+                worst = fmaxf(worst, fmaxf(fabsf(a0), fabsf(a1)));
                 const __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
                 const __half l0 = __float2half_rn(a0 - __half2float(h0)), l1 = __float2half_rn(a1 - __half2float(h1));
                 H[j] = (unsigned)__half_as_ushort(h0) | ((unsigned)__half_as_ushort(h1) << 16);
@@ -859,18 +864,21 @@ k_split_f16_rows(const float *__restrict__ X, long long ldx, long long strideX, 
             stg256u(h + (long long)r * ldp + c, H);
             stg256u(l + (long long)r * ldp + c, L);
         } else {
-            const float a = x[src * ldx + c] * f;
+            const float a = fminf(fmaxf(x[src * ldx + c] * f, -65000.0f), 65000.0f);
+            worst = fmaxf(worst, fabsf(a));
             const __half vh = __float2half_rn(a);
             h[(long long)r * ldp + c] = vh;
             l[(long long)r * ldp + c] = __float2half_rn(a - __half2float(vh));
         }
     }
+    if (worst >= 65000.0f) atomicCAS(&g_gemm_error, 0, QT_ERR_RANGE);
 }
 
-// amax (float, batch entries) is scratch the caller provides; exp_out receives the exponents.
+// amax (float, batch entries): scratch that receives each matrix's largest magnitude (compute_amax)
+// or per-matrix upper bounds the caller already knows; exp_out receives the exponents.
 int launch_split_f16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
                      const long long *index, long long stride_index, const float *scale, long long stride_scale,
-                     float *amax, const int *exp_in, int target_or_exp0, int *exp_out,
+                     float *amax, int compute_amax, const int *exp_in, int target_or_exp0, int *exp_out,
                      void *hi, void *lo, long long ldp, long long strideP, cudaStream_t s) {
     if (rows < 0 || cols < 0 || batch < 0 || batch > 65535) return record(QT_ERR_ARG);
     if (rows == 0 || cols == 0 || batch == 0) return record(QT_OK);
@@ -883,7 +891,7 @@ int launch_split_f16(const float *X, long long ldx, long long strideX, int rows,
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;
     dim3 grid((unsigned)ctas, batch);
-    if (amax) {
+    if (amax && compute_amax) {
         if (cudaMemsetAsync(amax, 0, sizeof(float) * batch, s) != cudaSuccess) return record(QT_ERR_LAUNCH);
         k_amax_rows<<<grid, 256, 0, s>>>(X, ldx, strideX, rows, cols, index, stride_index, scale, stride_scale, amax);
         count_launch(1);
@@ -1106,23 +1114,24 @@ struct QuantStateArgs {
 typedef void (*GemmKern)(const GemmMaps, const GemmParams);
 
 // Kernel table: [tile configuration][A major][B major][quantizing epilogue].
-// Configurations: 0 = two planes, 128 x 128; 1 = two planes, 128 x 256; 2 = three planes, 128 x 128.
-template <int NP, int BN_> static void fill_kernels(GemmKern (&t)[2][2][2]) {
-    t[0][0][0] = k_gemm_bf16x3<false, false, NP, BN_, false>; t[0][0][1] = k_gemm_bf16x3<false, false, NP, BN_, true>;
-    t[0][1][0] = k_gemm_bf16x3<false, true, NP, BN_, false>;  t[0][1][1] = k_gemm_bf16x3<false, true, NP, BN_, true>;
-    t[1][0][0] = k_gemm_bf16x3<true, false, NP, BN_, false>;  t[1][0][1] = k_gemm_bf16x3<true, false, NP, BN_, true>;
-    t[1][1][0] = k_gemm_bf16x3<true, true, NP, BN_, false>;   t[1][1][1] = k_gemm_bf16x3<true, true, NP, BN_, true>;
+// Configurations: 0 = two planes, 128 x 128 tile, eight epilogue warps of 64 columns; 1 = two planes, 128 x 256,
+// eight epilogue warps of 128 columns; 2 = three planes, 128 x 128, four epilogue warps.
+template <int NP, int BN_, int EC> static void fill_kernels(GemmKern (&t)[2][2][2]) {
+    t[0][0][0] = k_gemm_bf16x3<false, false, NP, BN_, EC, false>; t[0][0][1] = k_gemm_bf16x3<false, false, NP, BN_, EC, true>;
+    t[0][1][0] = k_gemm_bf16x3<false, true, NP, BN_, EC, false>;  t[0][1][1] = k_gemm_bf16x3<false, true, NP, BN_, EC, true>;
+    t[1][0][0] = k_gemm_bf16x3<true, false, NP, BN_, EC, false>;  t[1][0][1] = k_gemm_bf16x3<true, false, NP, BN_, EC, true>;
+    t[1][1][0] = k_gemm_bf16x3<true, true, NP, BN_, EC, false>;   t[1][1][1] = k_gemm_bf16x3<true, true, NP, BN_, EC, true>;
 }
 static GemmKern g_kernels[3][2][2][2];
-static const int g_cfg_threads[3] = {TileCfg<2, 128>::THREADS, TileCfg<2, 256>::THREADS, TileCfg<3, 128>::THREADS};
+static const int g_cfg_threads[3] = {TileCfg<2, 128, 64>::THREADS, TileCfg<2, 256, 128>::THREADS, TileCfg<3, 128, 128>::THREADS};
 static const int g_cfg_bn[3] = {128, 256, 128};
 
 static bool prepare_kernels() {
     static bool filled = false;
     if (!filled) {
-        fill_kernels<2, 128>(g_kernels[0]);
-        fill_kernels<2, 256>(g_kernels[1]);
-        fill_kernels<3, 128>(g_kernels[2]);
+        fill_kernels<2, 128, 64>(g_kernels[0]);
+        fill_kernels<2, 256, 128>(g_kernels[1]);
+        fill_kernels<3, 128, 128>(g_kernels[2]);
         filled = true;
     }
     static PerDeviceOnce attr_done;                      // function attributes are per device
@@ -1139,6 +1148,8 @@ static bool prepare_kernels() {
 
 // Test hook: force a tile configuration for two-plane products (-1: choose by problem size).
 static int g_force_bn = -1;
+static int g_wide_min_k = 0;
+static int g_heavy_narrow = 1;
 
 // a.Ahi/Alo (+ Amid/Bmid for three planes: order hi, mid, lo).  With `qs` the result (and the C
 // operand, if qs->q_in) is 4-bit state instead of a.C / a.D.
@@ -1178,8 +1189,12 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     // tile configuration: the wide tile when it still leaves every SM at least two tiles
     int cfg = np == 3 ? 2 : 0;
     if (np == 2 && a.N > 128) {
+        // the wide tile pays where the product is bound by operand delivery (long K); a short-K
+        // product is bound by its epilogue, which the narrow tile's four warps with all their
+        // registers do better
         const long long wide_tiles = (long long)tiles_m * ((a.N + 255) / 256) * a.batch;
-        if (wide_tiles >= 2LL * sms) cfg = 1;
+        const bool heavy_epilogue = a.C != nullptr && a.beta != 0.0f && a.Dhi != nullptr;   // streams C, D and planes
+        if (wide_tiles >= 2LL * sms && a.K >= g_wide_min_k && !(heavy_epilogue && g_heavy_narrow)) cfg = 1;
         if (g_force_bn == 128) cfg = 0;
         if (g_force_bn == 256) cfg = 1;
     }
@@ -1462,13 +1477,13 @@ int qt_matmul_f32_static(const float *A, long long lda, long long strideA, int t
 
 int qt_device_error(int clear) { return read_gemm_error(clear != 0); }
 
-void qt_gemm_force_tile(int bn) { g_force_bn = bn; }
+void qt_gemm_force_tile(int bn) { if (bn >= 1000) g_wide_min_k = bn - 1000; else if (bn == 1 || bn == 0) g_heavy_narrow = bn; else g_force_bn = bn; }
 
 int qt_split_f16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
                  const long long *index, long long stride_index, const float *scale, long long stride_scale,
-                 float *amax_scratch, const int *exp_in, int target_or_exp0, int *exp_out,
+                 float *amax, int compute_amax, const int *exp_in, int target_or_exp0, int *exp_out,
                  void *hi, void *lo, long long ldp, long long strideP, void *stream) {
-    return launch_split_f16(X, ldx, strideX, rows, cols, batch, index, stride_index, scale, stride_scale, amax_scratch, exp_in,
+    return launch_split_f16(X, ldx, strideX, rows, cols, batch, index, stride_index, scale, stride_scale, amax, compute_amax, exp_in,
                             target_or_exp0, exp_out, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream));
 }
 

@@ -34,22 +34,124 @@ __device__ __forceinline__ float warp_sum(float v) {
 // take the dot product v_i . v_c needed for the triangular factor T, and warp 0 fills in
 // column c-1 of T meanwhile (slarft recurrence), off the critical path.  One barrier per step;
 // every reduction chain is split over four accumulators.
+//
+// Fused form (prev_w > 0): before anything is factored, the block reflector of the PREVIOUS panel
+// of the same outer block (Householder vectors in V's columns j0-prev_w .. j0-1, rows j0-prev_w ..
+// n-1; its triangular factor Tprev) is applied to 32-column chunks of the rest of the outer block:
+//     C <- (I - Vp Tp^T Vp^T) C,   C = A[j0-prev_w : n, j0 + 32 chunk : ...]
+// CTA (matrix, chunk) updates chunk `chunk` (written back to A); chunk 0 is the new panel, which
+// its CTA goes on to factor from shared memory.  This replaces the three library products per
+// panel that a separate rank-32 update needs, and the CTAs of chunks 1.. fill otherwise idle SMs.
 template <int RPL, int RS>
 __global__ void __launch_bounds__(kQrThreads, 1)
-k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, int j0, int w,
-                    float *__restrict__ Vbase, long long strideV, float *__restrict__ Tbase, long long strideT) {
+k_householder_panel(float *__restrict__ Abase, long long strideA, int n, int j0, int w,
+                    float *__restrict__ Vbase, long long strideV, float *__restrict__ Tbase, long long strideT,
+                    int prev_w, const float *__restrict__ Tprev_base, int block_end) {
     constexpr int RT = RPL + RS;
     extern __shared__ float sm[];
     const int m = n - j0;
-    float *P = sm;                                         // [m][33] staging for coalesced global access
-    float *vb = P + ((m * 33 + 31) & ~31);                 // [2][RT * 32] published Householder vector
+    float *Pall = sm;                                      // [kPanel + m][33]: rows of the update window, then of the panel
+    float *P = Pall + kPanel * 33;                         // [m][33] staging of the panel rows (coalesced global access)
+    float *vb = Pall + (((kPanel + m) * 33 + 31) & ~31);   // [2][RT * 32] published Householder vector
     float *G = vb + 2 * RT * 32;                           // [32][33]  v_i . v_j, i < j
     float *Ts = G + kPanel * (kPanel + 1);                 // [32][33]
     float *tau = Ts + kPanel * (kPanel + 1);               // [32]
+    float *Vs = tau + kPanel;                              // [256][33] slab of the previous panel's vectors (fused form)
+    float *Tp = Vs + 256 * 33;                             // [32][33]  previous panel's triangular factor
+    float *zs = Tp + kPanel * (kPanel + 1);                // [32 warps][32]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float *A = Abase + (long long)blockIdx.x * strideA + (long long)j0 * n + j0;
+    const int chunk = blockIdx.y;
+    float *Amat = Abase + (long long)blockIdx.x * strideA;
+    const float *A = Amat + (long long)j0 * n + j0;
 
-    for (int r = warp; r < m; r += 32) P[r * 33 + lane] = (lane < w) ? A[(long long)r * n + lane] : 0.0f;
+    if (prev_w > 0) {
+        // ---- apply the previous panel's block reflector to this CTA's column chunk
+        const int r0 = j0 - prev_w;                        // first row of the update window
+        const int mu = n - r0;                             // rows of the window
+        const int c0 = j0 + kPanel * chunk;                // first column of the chunk
+        const int wc = min(kPanel, block_end - c0);        // columns of the chunk
+        float *C = Pall + (kPanel - prev_w) * 33;          // window rows so that row prev_w of it is P's row 0
+        float *Cg = Amat + (long long)r0 * n + c0;
+        const float *Vg = Vbase + (long long)blockIdx.x * strideV + (long long)r0 * n + r0;
+        for (int r = warp; r < mu; r += 32) C[r * 33 + lane] = (lane < wc) ? Cg[(long long)r * n + lane] : 0.0f;
+        for (int i = tid; i < kPanel * kPanel; i += kQrThreads) {
+            const int a = i / kPanel, b = i - a * kPanel;
+            Tp[a * (kPanel + 1) + b] = (a < prev_w && b < prev_w) ? Tprev_base[(long long)blockIdx.x * strideT + i] : 0.0f;
+        }
+        // Vp is streamed through shared memory in slabs of kSlab window rows; the next slab is
+        // fetched into registers while the current one is being used, so the global-memory latency
+        // of the 2 * ceil(mu / kSlab) dependent slab loads is hidden behind the arithmetic.
+        constexpr int kSlab = 256, kPer = kSlab * kPanel / kQrThreads;    // 8 elements per thread per slab
+        float pre[kPer];
+        auto fetch = [&](int rb) {
+#pragma unroll
+            for (int q = 0; q < kPer; ++q) {
+                const int i = tid + q * kQrThreads, rr = i >> 5, j = i & 31;
+                pre[q] = (rb + rr < mu && j < prev_w) ? Vg[(long long)(rb + rr) * n + j] : 0.0f;
+            }
+        };
+        auto stash = [&]() {
+#pragma unroll
+            for (int q = 0; q < kPer; ++q) {
+                const int i = tid + q * kQrThreads;
+                Vs[(i >> 5) * 33 + (i & 31)] = pre[q];
+            }
+        };
+        float wacc[kPanel];
+#pragma unroll
+        for (int j = 0; j < kPanel; ++j) wacc[j] = 0.0f;
+        fetch(0);
+        for (int rb = 0; rb < mu; rb += kSlab) {           // W = Vp^T C
+            __syncthreads();
+            stash();
+            __syncthreads();
+            fetch(rb + kSlab < mu ? rb + kSlab : 0);       // after the last slab: the first slab of the second pass
+#pragma unroll
+            for (int k = 0; k < kSlab / 32; ++k) {
+                const int rr = lane + 32 * k;
+                const float cv = (rb + rr < mu) ? C[(rb + rr) * 33 + warp] : 0.0f;
+#pragma unroll
+                for (int j = 0; j < kPanel; ++j) wacc[j] = fmaf(Vs[rr * 33 + j], cv, wacc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kPanel; ++j) wacc[j] = warp_sum(wacc[j]);
+        // z = Tp^T w for this warp's column (lane i computes z_i), shared through zs
+        {
+            float z = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kPanel; ++j) z = fmaf(Tp[j * (kPanel + 1) + lane], wacc[j], z);
+            zs[warp * kPanel + lane] = z;
+        }
+        for (int rb = 0; rb < mu; rb += kSlab) {           // C -= Vp z
+            __syncthreads();
+            stash();
+            __syncthreads();
+            if (rb + kSlab < mu) fetch(rb + kSlab);
+            const float *zw = zs + warp * kPanel;          // read by every lane at the same address: a broadcast
+#pragma unroll
+            for (int k = 0; k < kSlab / 32; ++k) {
+                const int rr = lane + 32 * k;
+                if (rb + rr < mu) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < kPanel; ++j) acc = fmaf(Vs[rr * 33 + j], zw[j], acc);
+                    C[(rb + rr) * 33 + warp] -= acc;
+                }
+            }
+        }
+        __syncthreads();
+        if (chunk > 0) {                                   // not the new panel: write the updated chunk back and leave
+            for (int r = warp; r < mu; r += 32)
+                if (lane < wc) Cg[(long long)r * n + lane] = C[r * 33 + lane];
+            return;
+        }
+        // chunk 0: rows prev_w.. of the window are the new panel, already in P
+        for (int r = warp; r < m; r += 32)
+            if (lane >= w) P[r * 33 + lane] = 0.0f;
+    } else {
+        for (int r = warp; r < m; r += 32) P[r * 33 + lane] = (lane < w) ? A[(long long)r * n + lane] : 0.0f;
+    }
     for (int i = tid; i < 2 * kPanel * (kPanel + 1); i += kQrThreads) G[i] = 0.0f;   // G and Ts are adjacent
     __syncthreads();
     float col[RPL];
@@ -144,10 +246,12 @@ k_householder_panel(const float *__restrict__ Abase, long long strideA, int n, i
 }
 
 template <int RPL, int RS>
-static int launch_panel_rpl(const float *A, long long strideA, int n, int count, int j0, int w,
-                            float *V, long long strideV, float *T, long long strideT, cudaStream_t s) {
+static int launch_panel_rpl(float *A, long long strideA, int n, int count, int j0, int w,
+                            float *V, long long strideV, float *T, long long strideT, cudaStream_t s,
+                            int prev_w, const float *Tprev, int block_end) {
     const int m = n - j0;
-    const size_t smem = sizeof(float) * ((size_t)((m * 33 + 31) & ~31) + 2 * (RPL + RS) * 32 + 2 * kPanel * (kPanel + 1) + kPanel);
+    const size_t smem = sizeof(float) * ((size_t)(((kPanel + m) * 33 + 31) & ~31) + 2 * (RPL + RS) * 32 + 2 * kPanel * (kPanel + 1) + kPanel +
+                                         256 * 33 + kPanel * (kPanel + 1) + 32 * kPanel);
     static PerDeviceOnce attr_set;                         // function attributes are per device
     const int dev = current_device();
     if (attr_set.pending(dev)) {
@@ -156,19 +260,25 @@ static int launch_panel_rpl(const float *A, long long strideA, int n, int count,
         attr_set.mark(dev);
     }
     if (smem > 227 * 1024) return record(QT_ERR_UNSUPPORTED);
-    k_householder_panel<RPL, RS><<<count, kQrThreads, smem, s>>>(A, strideA, n, j0, w, V, strideV, T, strideT);
+    const int chunks = prev_w > 0 ? (block_end - j0 + kPanel - 1) / kPanel : 1;
+    dim3 grid(count, chunks);
+    k_householder_panel<RPL, RS><<<grid, kQrThreads, smem, s>>>(A, strideA, n, j0, w, V, strideV, T, strideT, prev_w, Tprev, block_end);
     count_launch(1);
     return check_launch();
 }
 
-int launch_householder_panel(const float *A, long long strideA, int n, int count, int j0, int w,
-                             float *V, long long strideV, float *T, long long strideT, cudaStream_t s) {
+int launch_householder_panel(float *A, long long strideA, int n, int count, int j0, int w,
+                             float *V, long long strideV, float *T, long long strideT, cudaStream_t s,
+                             int prev_w, const float *Tprev, int block_end) {
     if (n <= 0 || count < 0 || j0 < 0 || j0 >= n || w <= 0 || w > kPanel || j0 + w > n) return record(QT_ERR_ARG);
     if (!A || !V || !T) return record(QT_ERR_ARG);
+    if (prev_w < 0 || prev_w > kPanel || prev_w > j0) return record(QT_ERR_ARG);
+    if (prev_w > 0 && (!Tprev || block_end < j0 + w || block_end > n || block_end - j0 > 4 * kPanel)) return record(QT_ERR_ARG);
     if (count == 0) return record(QT_OK);
+    if (count > 65535) return record(QT_ERR_UNSUPPORTED);
     const int rows_per_lane = (n - j0 + 31) / 32;
     if (rows_per_lane > kMaxRowsPerLane) return record(QT_ERR_UNSUPPORTED);
-#define QT_PANEL(R, S) return launch_panel_rpl<R, S>(A, strideA, n, count, j0, w, V, strideV, T, strideT, s)
+#define QT_PANEL(R, S) return launch_panel_rpl<R, S>(A, strideA, n, count, j0, w, V, strideV, T, strideT, s, prev_w, Tprev, block_end)
     if (rows_per_lane <= 6) QT_PANEL(6, 0);
     if (rows_per_lane <= 12) QT_PANEL(12, 0);
     if (rows_per_lane <= 20) QT_PANEL(20, 0);

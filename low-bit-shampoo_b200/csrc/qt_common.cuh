@@ -61,7 +61,8 @@ int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, v
                              cudaStream_t stream, float *amax_scratch = nullptr, int target = 0, int *exp_out = nullptr);
 int launch_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches_dev,
                              cudaStream_t stream);
-int launch_householder_panel(const float *A, long long strideA, int n, int count, int j0, int w,
-                             float *V, long long strideV, float *T, long long strideT, cudaStream_t stream);
+int launch_householder_panel(float *A, long long strideA, int n, int count, int j0, int w,
+                             float *V, long long strideV, float *T, long long strideT, cudaStream_t stream,
+                             int prev_w = 0, const float *Tprev = nullptr, int block_end = 0);
 
 }  // namespace qt

@@ -230,10 +230,12 @@ class _exact:
 
 
 class Mat:
-    """A batch of matrices available as an fp32 tensor, as bf16 hi/lo planes, or both."""
+    """A batch of matrices available as an fp32 tensor, as operand planes, or both.  `bound`: an
+    a-priori bound on the entries (float, or per-matrix fp32 tensor) that spares the split its pass
+    for the largest magnitude; a violated bound trips QT_ERR_RANGE instead of passing silently."""
 
-    def __init__(self, f32=None, planes=None):
-        self.f32, self._planes = f32, planes
+    def __init__(self, f32=None, planes=None, bound=None):
+        self.f32, self._planes, self.bound = f32, planes, bound
 
     @property
     def planes3(self):
@@ -246,7 +248,7 @@ class Mat:
     def planes(self):
         if self._planes is None:
             x = self.f32 if self.f32.stride(2) == 1 else self.f32.contiguous()
-            self._planes = _gemm.split(x)
+            self._planes = _gemm.split(x, bound=self.bound)
         return self._planes
 
 
@@ -278,6 +280,7 @@ def mm(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, want_flo
 # silently.
 _BASIS_BOUND = 8.0
 _GRAM_BOUND = 16.0
+_UNIT_BOUND = 2.0             # entries of orthonormal rows / columns and of Householder vectors (<= 1) with margin
 
 
 def op_bjorck(V, want_planes=False):
@@ -298,8 +301,8 @@ def op_scaled_gram_gathered(Vt, idx, weights):
     (b, k), weights fp32 (b, k).  On the tensor-core path the gather and the scaling happen while
     the operands are split into planes, so neither rows nor the scaled copy is materialised."""
     if _tc(Vt) and Vt.stride(2) == 1:
-        A = _gemm.split_rows(Vt, idx)
-        B = _gemm.split_rows(Vt, idx, weights.contiguous())
+        A = _gemm.split_rows(Vt, idx, bound=_BASIS_BOUND)
+        B = _gemm.split_rows(Vt, idx, weights.contiguous(), bound=(weights.abs().amax(dim=1) * _BASIS_BOUND).contiguous())
         D, _ = _gemm.matmul(A, B, trans_a=True)
         return Mat(D)
     return op_scaled_gram(Mat(_gather_rows(Vt, idx)), weights)
@@ -321,7 +324,7 @@ def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
     quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
     V = householder_q(mm(L, Vt, trans_b=True).f32, tensor_cores=_tc(L.f32))
-    LV = mm(L, Mat(V)).f32
+    LV = mm(L, Mat(V, bound=_UNIT_BOUND)).f32
     eigs = (LV * V).sum(dim=1)
     return V, eigs
 
@@ -514,7 +517,7 @@ def _class_statistics(cls, entries, w1, w2, eps, exact):
                     L = cls.stat.dequantize(a, b)
                 cls.stat.quantize(a, b, _ema_update(L, ga, w1, w2))
                 continue
-            Vt = Mat(cls.stat.dequantize(a, b))
+            Vt = Mat(cls.stat.dequantize(a, b), bound=_UNIT_BOUND if cls.stat.lowbit else None)
             if cls.stat.lowbit:
                 for _ in range(cls.rect_t1):
                     Vt = op_bjorck(Vt, want_planes=True)
@@ -582,7 +585,7 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent, starts=None):
                 P = MF.ComputePower(L, exponent, ridge_epsilon=eps, v0=v0_of(a, b))
             elif inv_root_mode == 0:
                 Vt = cls.stat.dequantize(a, b)
-                rows = Mat(_gather_rows(Vt, cls.keep_idx[a:b]))
+                rows = Mat(_gather_rows(Vt, cls.keep_idx[a:b]), bound=_UNIT_BOUND if cls.stat.lowbit else None)
                 if cls.stat.lowbit:
                     for _ in range(cls.rect_t2):
                         rows = op_bjorck(rows, want_planes=True)
@@ -590,7 +593,8 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent, starts=None):
                 weights = 1 / (cls.S[a:b] + rho.unsqueeze(1)).pow(1 / exponent)
                 if cls.prec.fusable() and _tc(rows.f32 if rows.f32 is not None else rows._planes.hi):
                     # rows^T diag(w) rows straight into the 4-bit preconditioner (quantized in the epilogue)
-                    scaled = _gemm.split_rows(rows.f32, None, weights.contiguous())
+                    scaled = _gemm.split_rows(rows.f32, None, weights.contiguous(),
+                                              bound=(weights.abs().amax(dim=1) * _BASIS_BOUND).contiguous())
                     _gemm.matmul_q4(rows.planes, scaled, cls.prec.code, cls.prec.state(a, b), trans_a=True)
                     continue
                 P = op_scaled_gram(rows, weights).f32

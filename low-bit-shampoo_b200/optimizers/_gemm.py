@@ -33,6 +33,10 @@ def _ptr(t):
     return None if t is None else ct.c_void_p(t.data_ptr())
 
 
+def _ceil_log2(x):
+    return int(math.ceil(math.log2(max(float(x), 1e-30))))
+
+
 def _pitch(cols):
     return (cols + 15) // 16 * 16       # 32-byte rows: TMA needs 16, the 256-bit epilogue stores 32
 
@@ -116,32 +120,46 @@ def split_bf16(X):
     return P
 
 
-def _split_f16(X, index, scale, target):
+def _split_f16(X, index, scale, target, bound):
+    """`bound`: None - each matrix's largest magnitude is measured (one extra pass over X);
+    a float - an a-priori bound on every entry (one exponent for the whole batch, no pass);
+    an fp32 tensor (batch,) - per-matrix bounds known on the device (no pass)."""
     b, R, c = X.shape
     rows = index.shape[1] if index is not None else R
-    scratch = torch.empty(2, b, dtype=torch.int32, device=X.device)      # [0]: amax (as float bits), [1]: exponents
-    P = Planes(b, rows, c, X.device, f16=True, exp=scratch[1], exp0=0, tmax=target)
+    amax = exp = None
+    compute, exp0 = 0, target
+    if bound is None:
+        scratch = torch.empty(2, b, dtype=torch.int32, device=X.device)  # [0]: amax (as float bits), [1]: exponents
+        amax, exp, compute = scratch[0], scratch[1], 1
+    elif torch.is_tensor(bound):
+        assert bound.dtype == torch.float32 and bound.shape == (b,) and bound.is_contiguous()
+        amax, exp = bound, torch.empty(b, dtype=torch.int32, device=X.device)
+    else:
+        exp0 = target - _ceil_log2(bound)
+    P = Planes(b, rows, c, X.device, f16=True, exp=exp, exp0=0 if exp is not None else exp0, tmax=target)
     with torch.cuda.device(X.device):
         rc = F.lib.qt_split_f16(_ptr(X), X.stride(1), X.stride(0), rows, c, b,
                                 _ptr(index), index.stride(0) if index is not None else 0,
                                 _ptr(scale), scale.stride(0) if scale is not None else 0,
-                                _ptr(scratch[0]), None, target, _ptr(scratch[1]),
+                                _ptr(amax), compute, None, exp0, _ptr(exp),
                                 P.ptr_hi(), P.ptr_lo(), P.ld, P.stride, F._stream(X))
     F._check(rc, "split_f16")
     return P
 
 
-def split(X, target=None):
-    """fp32 (batch, rows, cols) tensor (last dim contiguous) -> Planes (scaled fp16 unless FP16_PLANES is off)."""
+def split(X, target=None, bound=None):
+    """fp32 (batch, rows, cols) tensor (last dim contiguous) -> Planes (scaled fp16 unless FP16_PLANES is off).
+    `bound`: see _split_f16."""
     assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
     if not FP16_PLANES:
         return split_bf16(X)
-    return _split_f16(X, None, None, SPLIT_TARGET if target is None else target)
+    return _split_f16(X, None, None, SPLIT_TARGET if target is None else target, bound)
 
 
-def split_rows(X, index=None, scale=None, target=None):
+def split_rows(X, index=None, scale=None, target=None, bound=None):
     """Planes of the matrices whose row i is scale[b, i] * X[b, index[b, i], :].
-    X: fp32 (batch, R, cols); index: int64 (batch, rows) or None; scale: fp32 (batch, rows) or None."""
+    X: fp32 (batch, R, cols); index: int64 (batch, rows) or None; scale: fp32 (batch, rows) or None;
+    `bound` on the SCALED rows: see _split_f16."""
     assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
     b, R, c = X.shape
     rows = index.shape[1] if index is not None else R
@@ -150,7 +168,7 @@ def split_rows(X, index=None, scale=None, target=None):
     if scale is not None:
         assert scale.dtype == torch.float32 and scale.shape == (b, rows) and scale.stride(1) == 1
     if FP16_PLANES:
-        return _split_f16(X, index, scale, SPLIT_TARGET if target is None else target)
+        return _split_f16(X, index, scale, SPLIT_TARGET if target is None else target, bound)
     P = Planes(b, rows, c, X.device)
     with torch.cuda.device(X.device):
         rc = F.lib.qt_split_bf16_rows(_ptr(X), X.stride(1), X.stride(0), rows, c, b,
@@ -159,10 +177,6 @@ def split_rows(X, index=None, scale=None, target=None):
                                       P.ptr_hi(), P.ptr_lo(), P.ld, P.stride, F._stream(X))
     F._check(rc, "split_bf16_rows")
     return P
-
-
-def _ceil_log2(x):
-    return int(math.ceil(math.log2(max(float(x), 1e-30))))
 
 
 def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=None, want_planes=False,

@@ -22,26 +22,25 @@ def _ptr(t):
 
 
 OUTER = 128                 # columns per outer block (four panels): trailing updates are rank-128
-USE_TENSOR_CORES = True     # rank-128 far updates on the tcgen05 kernel (panel-local rank-32 ones stay fp32)
+USE_TENSOR_CORES = True     # rank-128 far updates on the tcgen05 kernel (rank-32 ones inside a block: fused into the panel kernel)
 
 
 def _reflect(Vk, Tk, target, target_planes, transpose_t, Pv=None):
-    """target <- (I - Vk T Vk^T) target (or with T^T), fp32 in place; when `target_planes` (the
-    bf16 planes of `target`) is given the two large products run on the tensor cores and the
-    planes are kept in step with the fp32 values.  `Pv`: planes of Vk if the caller has them.
-    Two-plane or three-plane operands alike (the planes decide the kernel)."""
+    """target <- (I - Vk T' Vk^T) target with T' = T^T (transpose_t) or T, fp32 in place.
+    With `target_planes` (the operand planes of `target`) everything runs on the tensor cores:
+    Y = Vk T' and W = Vk^T target are produced directly as operand planes, then
+    target <- target - Y W with the planes of `target` kept in step.  `Pv`: planes of Vk."""
     from optimizers import _gemm
     if target_planes is None:
         W = torch.bmm(Vk.transpose(1, 2), target)
         W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
         target.baddbmm_(Vk, W, alpha=-1.0)
         return
-    split = _gemm.split
     if Pv is None:
-        Pv = split(Vk)
-    W, _ = _gemm.matmul(Pv, target_planes, trans_a=True)                   # Vk^T target, (w x t)
-    W = torch.bmm(Tk.transpose(1, 2) if transpose_t else Tk, W)
-    _gemm.matmul(Pv, split(W), alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
+        Pv = _gemm.split(Vk, bound=2.0)
+    _, Yp = _gemm.matmul(Pv, _gemm.split(Tk), trans_b=transpose_t, want_float=False, want_planes=True)
+    _, Wp = _gemm.matmul(Pv, target_planes, trans_a=True, want_float=False, want_planes=True)
+    _gemm.matmul(Yp, Wp, alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
 
 
 def _merge_t(Vo, Tp, widths, Pv=None):
@@ -106,21 +105,23 @@ def householder_q(X, tensor_cores=True):
             for j0 in range(J0, J0 + wo, PANEL):
                 w = min(PANEL, n - j0)
                 k = j0 // PANEL
-                rc = lib.qt_householder_panel(_ptr(X), n * n, n, B, j0, w, _ptr(V), n * n,
-                                              _ptr(T[:, k]), npan * PANEL * PANEL, stream)
+                # each launch first applies the previous panel's reflector to the rest of the outer
+                # block (32-column chunks on separate CTAs), then factors its own panel
+                prev = PANEL if j0 > J0 else 0
+                rc = lib.qt_householder_panel_fused(_ptr(X), n * n, n, B, j0, w, _ptr(V), n * n,
+                                                    _ptr(T[:, k]), npan * PANEL * PANEL, prev,
+                                                    _ptr(T[:, k - 1]) if prev else None, J0 + wo, stream)
                 F._check(rc, "householder panel")
                 widths.append(w)
-                if j0 + w < J0 + wo:                      # rest of this outer block: rank-32 update in fp32
-                    _reflect(V[:, j0:, j0:j0 + w], T[:, k, :w, :w], X[:, j0:, j0 + w:J0 + wo], None, True)
             Vo = V[:, J0:, J0:J0 + wo]
-            Pv = split(Vo) if tc else None                # shared by the merge, the far update and the accumulation of Q
+            Pv = split(Vo, bound=2.0) if tc else None     # Householder vectors: entries <= 1; shared by the merge, the far update and the accumulation of Q
             Tb = _merge_t(Vo, T[:, J0 // PANEL:], widths, Pv)
             blocks.append((J0, wo, Tb, Pv))
             if J0 + wo < n:
                 m, t = n - J0, n - J0 - wo
                 _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True, Pv)
         Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
-        Qp = split(Q) if tc else None
+        Qp = split(Q, bound=2.0) if tc else None         # Q stays orthonormal: entries <= 1
         for J0, wo, Tb, Pv in reversed(blocks):
             m = n - J0
             _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False, Pv)

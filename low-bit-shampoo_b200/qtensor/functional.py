@@ -199,8 +199,18 @@ def compute_power(Vt, S, p, iter_count=4, ridge_epsilon=1e-6, indices=None, max_
     `iter_count` Bjorck steps, then  rows^T diag((S + ridge * lambda_max)^(-1/p)) rows
     (reference functional.py:749-762; lambda_max defaults to max(S))."""
     rows = Vt[indices] if indices is not None else Vt
-    for _ in range(iter_count):
-        rows = torch.addmm(rows, rows @ rows.T, rows, beta=1.5, alpha=-0.5)
     top = max_eigen if max_eigen is not None else S.max()
     weights = 1 / (S + ridge_epsilon * top).pow(1 / p)
+    if rows.is_cuda and rows.dtype == torch.float32 and lib is not None:
+        # the same products on the tensor cores (batch of one; fp32 results re-split between
+        # products, so any input is accepted - the optimizers' batched engine chains planes instead)
+        from optimizers import _engine as E
+        R = E.Mat(rows.contiguous().unsqueeze(0))
+        for _ in range(iter_count):
+            W = E.mm(R, R, trans_b=True)
+            R = E.mm(W, R, alpha=-0.5, beta=1.5, C=R.f32)
+        scaled = E.Mat((weights.to(rows.device).unsqueeze(1) * R.f32[0]).unsqueeze(0))
+        return E.mm(R, scaled, trans_a=True).f32[0]
+    for _ in range(iter_count):
+        rows = torch.addmm(rows, rows @ rows.T, rows, beta=1.5, alpha=-0.5)
     return rows.T @ (weights.unsqueeze(1) * rows)

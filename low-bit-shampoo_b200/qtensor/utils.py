@@ -142,6 +142,10 @@ class QTensorDiagReal(_LowBitBase):
 
 def bjorck_step(M):
     """One Bjorck orthonormalisation step on the rows of M: 1.5 M - 0.5 (M M^T) M."""
+    if M.is_cuda and M.dtype == torch.float32 and F.lib is not None:
+        from optimizers import _engine as E
+        R = E.Mat(M.contiguous().unsqueeze(0))
+        return E.mm(E.mm(R, R, trans_b=True), R, alpha=-0.5, beta=1.5, C=R.f32).f32[0]
     return torch.addmm(M, M @ M.T, M, beta=1.5, alpha=-0.5)
 
 
@@ -198,8 +202,15 @@ class QTensorSVDFast(_LowBitBase):
 
     def quantize(self, var, Vt=None):
         L = var.float()
-        V, _ = torch.linalg.qr(L @ Vt.T.float())
-        eigs = ((L @ V) * V).sum(dim=0)                       # diag(V^T L V)
+        if L.is_cuda and F.lib is not None and L.shape[0] >= 2:
+            # batch of one through the optimizers' engine: L V^T and L V on the tensor cores, the QR
+            # on the library's Householder kernels (no cuSOLVER / cuBLAS call)
+            from optimizers import _engine as E
+            Vb, eb = E.op_subspace_step(E.Mat(L.contiguous().unsqueeze(0)), E.Mat(Vt.float().contiguous().unsqueeze(0)))
+            V, eigs = Vb[0], eb[0]
+        else:
+            V, _ = torch.linalg.qr(L @ Vt.T.float())
+            eigs = ((L @ V) * V).sum(dim=0)                   # diag(V^T L V)
         keep = max(1, eigs.numel() // 2)
         order_vals, order_idx = torch.sort(eigs)
         self._assign("keep_indices", order_idx[:keep].to(torch.int64))
@@ -240,6 +251,10 @@ class QTensorSVDFast(_LowBitBase):
         Vt = self._basis(self.rect_t1)
         rows = Vt[self.keep_indices.to(Vt.device)]
         S = self.Svalue.to(device=Vt.device, dtype=Vt.dtype)
+        if rows.is_cuda and rows.dtype == torch.float32 and F.lib is not None:
+            from optimizers import _engine as E
+            R = E.Mat(rows.contiguous().unsqueeze(0))
+            return E.mm(R, E.Mat((S.unsqueeze(1) * rows).unsqueeze(0)), trans_a=True).f32[0], Vt
         return rows.T @ (S.unsqueeze(1) * rows), Vt
 
     def computepower(self, exp, ridge_epsilon=1e-6):
