@@ -144,6 +144,16 @@ int qt_dequantize_planes_f16(const unsigned char *A, long long strideA, const fl
                              void *hi, void *lo, long long ldp, long long strideP, int blocksize, int bits, void *stream);
 
 /*
+ * Plane exponents of `count` matrices held as 4-bit state, without dequantizing them: e[j] puts
+ * the largest magnitude matrix j (state slot slots[j], or j when slots is NULL) can hold - the
+ * maximum over its block scales (n_absmax floats per slot) and, if diag is given, its fp32
+ * diagonal (n_diag floats) - just below 2^target.  For qt_gemm_ex with aq_codes / bq_codes.
+ */
+int qt_state_exponents(const float *absmax, long long stride_absmax, int n_absmax,
+                       const float *diag, long long stride_diag, int n_diag,
+                       const int *slots, int count, int target, int *exp_out, void *stream);
+
+/*
  * Self-test of the quantizer's division: the kernels replace x / absmax by an exact
  * reciprocal plus two fused corrections; this entry point compares that sequence with the
  * IEEE division on `pairs` pseudo-random operand pairs (seeded) and ADDS the number of
@@ -276,7 +286,17 @@ int qt_gemm_bf16x6(const void *Ahi, const void *Amid, const void *Alo, long long
  *     tensor memory, partial sums added in fp32 registers (0: one chain; the tensor core's
  *     accumulation truncates, so long chains lose about 6.5e-9 * K);
  *   - q_out != NULL: the result is written as 4-bit state exactly as qt_gemm_bf16x3_q4 does
- *     (q_* fields as that function's arguments), instead of D / P.
+ *     (q_* fields as that function's arguments), instead of D / P;
+ *   - aq_codes / bq_codes != NULL (f16 products with row-major operands: a_mn == 0, b_mn == 1):
+ *     that operand is not read from planes but DEQUANTIZED INSIDE THE KERNEL from 4-bit block-64
+ *     state (square, order M for A and N for B, K equal to it): converter warps turn each
+ *     128-byte line of the operand tile from codes and block scales (diagonal from *_diag, may be
+ *     NULL) into the swizzled fp16 hi / lo tile the tensor core reads, so neither the fp32
+ *     matrix nor its operand planes exist in device memory.  Matrix m of the product is state
+ *     slot *_slots[m] (NULL: m) of storage laid out with the *_stride_* strides (bytes / floats /
+ *     floats per slot); its plane exponent is a_exp[m] / b_exp[m] (see qt_state_exponents);
+ *     oq_code is the 16-entry codebook.  The tile bytes equal those qt_dequantize_planes_f16
+ *     writes.  This is the operand side of preconditioned_grad (optimizers/shampoo2.py:255-268).
  * All index, exponent and flag arrays are device int32 arrays read when the kernel runs.
  */
 typedef struct qt_gemm_desc {
@@ -294,6 +314,11 @@ typedef struct qt_gemm_desc {
     const float *q_code; const unsigned char *q_in; const float *q_absmax_in, *q_diag_in;
     unsigned char *q_out; float *q_absmax_out, *q_diag_out;
     long long q_stride_codes, q_stride_absmax, q_stride_diag;
+    const float *oq_code;
+    const unsigned char *aq_codes; const float *aq_absmax, *aq_diag; const int *aq_slots;
+    long long aq_stride_codes, aq_stride_absmax, aq_stride_diag;
+    const unsigned char *bq_codes; const float *bq_absmax, *bq_diag; const int *bq_slots;
+    long long bq_stride_codes, bq_stride_absmax, bq_stride_diag;
 } qt_gemm_desc;
 int qt_gemm_ex(const qt_gemm_desc *desc, void *stream);
 
@@ -345,8 +370,8 @@ int qt_split_f16(const float *X, long long ldx, long long strideX, int rows, int
                  float *amax, int compute_amax, const int *exp_in, int target_or_exp0, int *exp_out,
                  void *hi, void *lo, long long ldp, long long strideP, void *stream);
 
-/* Test hook: 128 or 256 forces the output-tile width of two-plane products, -1 restores the
- * choice by problem size.  Additive; no counterpart in the reference. */
+/* Measurement hook: 256 selects the 128 x 256 output tile for two-plane products wider than 128
+ * columns, anything else the default 128 x 128 tile.  Additive; no counterpart in the reference. */
 void qt_gemm_force_tile(int bn);
 
 /*

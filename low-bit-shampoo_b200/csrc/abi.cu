@@ -132,6 +132,13 @@ int qt_dequantize_planes_f16(const unsigned char *A, long long strideA, const fl
     return launch_dequantize_planes(a, slots, hi, lo, ldp, strideP, static_cast<cudaStream_t>(stream), amax_scratch, target, exp_out);
 }
 
+int qt_state_exponents(const float *absmax, long long stride_absmax, int n_absmax,
+                       const float *diag, long long stride_diag, int n_diag,
+                       const int *slots, int count, int target, int *exp_out, void *stream) {
+    return launch_state_exponents(absmax, stride_absmax, n_absmax, diag, stride_diag, n_diag, slots, count, target, exp_out,
+                                  static_cast<cudaStream_t>(stream));
+}
+
 int qt_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches, void *stream) {
     return launch_selftest_division(seed, pairs, mismatches, static_cast<cudaStream_t>(stream));
 }

@@ -25,6 +25,7 @@
 #include "quant_device.cuh"
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <cstring>
 
 namespace qt {
 
@@ -40,7 +41,7 @@ static constexpr unsigned WAIT_LIMIT = 1u << 18;
 //                      128x256x16 MMA instead of 8 KiB per 128x128x16 one: 25 % less shared-memory
 //                      traffic per flop, which is what bounds the 128 x 128 tile)
 //   NP = 3, BN_ = 128: 96 KiB per stage, 2 stages
-template <int NP, int BN_, int EC> struct TileCfg {
+template <int NP, int BN_, int EC, bool CONV = false> struct TileCfg {
     static constexpr int B_TILES = BN_ / 128;
     static constexpr int STAGE_BYTES = NP * (1 + B_TILES) * PLANE_TILE_BYTES;
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
@@ -48,11 +49,21 @@ template <int NP, int BN_, int EC> struct TileCfg {
     // EC (e >> 2).  EC = 64 halves the partial sums a thread holds (no register spills with
     // 8 + 2 warps) and doubles the loads in flight for epilogues that stream C, D and planes.
     static constexpr int EPI_WARPS = 4 * (BN_ / EC);
-    static constexpr int THREADS = (EPI_WARPS + 2) * 32;
+    // CONV: four more warps that build an operand's tiles in shared memory from 4-bit state
+    static constexpr int CONV_WARPS = CONV ? 4 : 0;
+    static constexpr int THREADS = (EPI_WARPS + 2 + CONV_WARPS) * 32;
     static constexpr int TMEM_COLS = 2 * BN_;                        // two accumulators
 };
 
 __device__ int g_gemm_error = 0;
+
+// A product operand that lives as 4-bit blockwise state: matrix b of the product is state slot
+// slots[b] (null: b); its plane exponent is a_exp[b] / b_exp[b] of GemmParams.
+struct QOperand {
+    const unsigned char *codes; const float *absmax, *diag; const int *slots;
+    long long stride_codes, stride_absmax, stride_diag;                   // per slot: bytes, floats, floats
+    int n, nb;                                                            // order of the state matrices, blocks per row
+};
 
 struct GemmParams {
     int M, N, K, batch;
@@ -70,6 +81,10 @@ struct GemmParams {
     const int *out_exp; int *out_exp_w; int out_exp0, out_rel;            // exponent of the plane output: given per entry, or
                                                                           // (out_rel) operand exponents + out_exp0; written to out_exp_w
     int kc;                                                               // k-blocks per accumulation chain (two-plane kernels)
+    // Operands taken straight from 4-bit state (CONV kernels; block size 64, square order qn):
+    // codes == nullptr: the operand comes from its planes through TMA as usual.
+    QOperand aq, bq;
+    const float *oq_code;                                                 // the 16-entry codebook of those operands
     int tiles_m, tiles_n;
     // 4-bit state as C operand and as result (QOUT kernels only): block size 64, order N == M
     const unsigned char *q_in; const float *q_absmax_in, *q_diag_in;      // q_in == nullptr: no C operand
@@ -368,10 +383,56 @@ __device__ __forceinline__ void store_planes_f16(__half *hi, __half *lo, const f
     }
 }
 
-template <bool A_MN, bool B_MN, int NP, int BN_, int EC, bool QOUT = false>
-__global__ void __launch_bounds__(TileCfg<NP, BN_, EC>::THREADS, 1)
+// 64 consecutive elements of row `row` of a 4-bit state matrix, starting at column `col` (a
+// multiple of 64: exactly one quantization block), dequantized exactly as k_dequantize_planes
+// does (code * scale, fp32 diagonal restored), scaled by two_e and split into fp16 hi / lo;
+// written as eight 16-byte pieces per plane to `dst_hi` / `dst_lo` (shared-memory addresses of
+// this row's 128-byte line) with the 128-byte swizzle pattern of line `line` of its 8-line group.
+// nvalid: leading elements that exist (a multiple of 16, or 0); the rest is written as zeros.
+__device__ __forceinline__ void convert_q4_row(const QOperand &q, const float *code_s, int slot, int row, int col, int nvalid,
+                                               float two_e, unsigned dst_hi, unsigned dst_lo, int line) {
+    const unsigned char *cp = q.codes + (long long)slot * q.stride_codes + (((long long)row * q.n + col) >> 1);
+    float am = 0.0f, dg = 0.0f;
+    bool has_d = false;
+    if (nvalid > 0) {
+        am = __ldg(q.absmax + (long long)slot * q.stride_absmax + (long long)row * q.nb + (col >> 6));
+        has_d = q.diag != nullptr && (unsigned)(row - col) < 64u;
+        if (has_d) dg = __ldg(q.diag + (long long)slot * q.stride_diag + row);
+    }
+    const float z = (am == 0.0f) ? 0.0f : -0.0f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {                            // 16 elements (8 code bytes) per step
+        uint2 w = make_uint2(0u, 0u);
+        const bool live = g * 16 < nvalid;
+        if (live) w = __ldg(reinterpret_cast<const uint2 *>(cp + 8 * g));
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {                     // 8 elements -> one 16-byte piece per plane
+            unsigned H[4], L[4];
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                const unsigned byte = ((hh ? w.y : w.x) >> (8 * (i >> 1))) & 255u;
+                float v0 = fmaf(code_s[byte >> 4], am, z), v1 = fmaf(code_s[byte & 15u], am, z);
+                const int c = col + g * 16 + hh * 8 + i;
+                if (has_d) { if (c == row) v0 = dg; if (c + 1 == row) v1 = dg; }
+                const float a0 = live ? v0 * two_e : 0.0f, a1 = live ? v1 * two_e : 0.0f;
+                const __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
+                const __half l0 = __float2half_rn(a0 - __half2float(h0)), l1 = __float2half_rn(a1 - __half2float(h1));
+                H[i >> 1] = (unsigned)__half_as_ushort(h0) | ((unsigned)__half_as_ushort(h1) << 16);
+                L[i >> 1] = (unsigned)__half_as_ushort(l0) | ((unsigned)__half_as_ushort(l1) << 16);
+            }
+            const unsigned off = (unsigned)(((g * 2 + hh) ^ (line & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_hi + off), "r"(H[0]), "r"(H[1]), "r"(H[2]), "r"(H[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst_lo + off), "r"(L[0]), "r"(L[1]), "r"(L[2]), "r"(L[3]) : "memory");
+        }
+    }
+}
+
+template <bool A_MN, bool B_MN, int NP, int BN_, int EC, bool QOUT = false, bool CONV = false>
+__global__ void __launch_bounds__(TileCfg<NP, BN_, EC, CONV>::THREADS, 1)
 k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
-    using Cfg = TileCfg<NP, BN_, EC>;
+    using Cfg = TileCfg<NP, BN_, EC, CONV>;
+    static_assert(!CONV || (NP == 2 && !A_MN && B_MN && BN_ == 128), "operands from 4-bit state: A row-major, B row-major, two planes");
+    __shared__ float conv_code[CONV ? 16 : 1];
     __shared__ QuantTablesHolder<QOUT> qtab;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
@@ -406,8 +467,12 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
     const int nchunks = (num_kb + KC - 1) / KC;
 
+    const bool conv_a = CONV && p.aq.codes != nullptr, conv_b = CONV && p.bq.codes != nullptr;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        // a stage is full when the TMA bytes have landed and, for an operand built from 4-bit
+        // state, when each of the four converter warps has arrived
+        const unsigned full_count = 1u + ((conv_a || conv_b) ? (unsigned)Cfg::CONV_WARPS : 0u);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), full_count); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -421,6 +486,10 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
     if constexpr (QOUT) build_tables<16>(qtab.t, p.q_code);    // all threads; ends with a barrier
+    if constexpr (CONV) {
+        if (threadIdx.x < 16 && p.oq_code) conv_code[threadIdx.x] = p.oq_code[threadIdx.x];
+        __syncthreads();
+    }
 
     // A matrix whose entry of `active` is zero is skipped by all three roles alike (the array
     // does not change while the kernel runs), so their ring and accumulator counters stay in step.
@@ -443,19 +512,21 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                     ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     const unsigned stage = base + s * STAGE_BYTES;
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES - (conv_a ? NP * PLANE_TILE_BYTES : 0) - (conv_b ? NP * B_PLANE_BYTES : 0));
                     const int k0 = kb * BK;
 #pragma unroll
                     for (int pl = 0; pl < NP; ++pl) {
                         const unsigned ta = stage + pl * PLANE_TILE_BYTES;
                         const unsigned tb = stage + NP * PLANE_TILE_BYTES + pl * B_PLANE_BYTES;
-                        if (!A_MN) {
+                        if (conv_a) {
+                        } else if (!A_MN) {
                             tma_load_3d(ta, &maps.a[pl], full_bar(s), k0, m0, za);
                         } else {
                             tma_load_3d(ta, &maps.a[pl], full_bar(s), m0, k0, za);
                             tma_load_3d(ta + PLANE_TILE_BYTES / 2, &maps.a[pl], full_bar(s), m0 + 64, k0, za);
                         }
-                        if (!B_MN) {
+                        if (conv_b) {
+                        } else if (!B_MN) {
                             tma_load_3d(tb, &maps.b[pl], full_bar(s), k0, n0, zb);
                         } else {
 #pragma unroll
@@ -670,6 +741,49 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    } else if (CONV && (conv_a || conv_b)) {
+        // ---------------- converter warps: the operand that lives as 4-bit state is dequantized
+        // here, straight into the swizzled tile the tensor core reads - the state's fp32 form and
+        // its operand planes never exist in device memory.  Thread t builds one 128-byte line:
+        // A (row-major, K contiguous): tile row t, the quantization block at columns k0 .. k0+63;
+        // B (row-major, N contiguous): k-row t & 63 of the 64-column chunk t >> 6.
+        const int t = threadIdx.x - (EPI_WARPS + 2) * 32;
+        unsigned it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int tm, tn, b;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
+            if (skipped(b)) continue;
+            const int m0 = tm * BM, n0 = tn * BN_;
+            const int sa = conv_a ? (p.aq.slots ? __ldg(p.aq.slots + b) : b) : 0;
+            const int sb = conv_b ? (p.bq.slots ? __ldg(p.bq.slots + b) : b) : 0;
+            const float ea = conv_a ? exp2f((float)(p.a_exp ? __ldg(p.a_exp + b) : 0)) : 1.0f;
+            const float eb = conv_b ? exp2f((float)(p.b_exp ? __ldg(p.b_exp + b) : 0)) : 1.0f;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                ok = mbar_wait_warp(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
+                if (!ok) break;
+                const unsigned stage = base + s * STAGE_BYTES;
+                const int k0 = kb * BK;
+                if (conv_a) {
+                    const int row = m0 + t;
+                    const int nvalid = row < p.M ? max(0, min(64, p.K - k0)) : 0;
+                    const unsigned line = stage + (unsigned)t * 128u;
+                    convert_q4_row(p.aq, conv_code, sa, row, k0, nvalid, ea, line, line + PLANE_TILE_BYTES, t);
+                }
+                if (conv_b) {
+                    const int kr = t & 63, chunk = t >> 6;
+                    const int krow = k0 + kr, col = n0 + 64 * chunk;
+                    const int nvalid = krow < p.K ? max(0, min(64, p.N - col)) : 0;
+                    const unsigned line = stage + NP * PLANE_TILE_BYTES + (unsigned)chunk * (PLANE_TILE_BYTES / 2) + (unsigned)kr * 128u;
+                    convert_q4_row(p.bq, conv_code, sb, krow, col, nvalid, eb, line, line + B_PLANE_BYTES, kr);
+                }
+                // make the generic-proxy writes visible to the tensor core's (async-proxy) reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_bar(s)) : "memory");
+            }
+        }
     }
     __syncthreads();
     if (warp == EPI_WARPS + 1) {
@@ -1099,6 +1213,9 @@ struct GemmExtras {
     const int *a_exp = nullptr, *b_exp = nullptr; int ab_exp0 = 0;
     const int *out_exp = nullptr; int *out_exp_w = nullptr; int out_exp0 = 0, out_rel = 0;
     int kc = 0;                                             // k-blocks per accumulation chain (0: one chain)
+    // operands straight from 4-bit state (see QOperand); codes == nullptr: from planes
+    QOperand aq = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0}, bq = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
+    const float *oq_code = nullptr;
 };
 
 static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -1122,9 +1239,10 @@ template <int NP, int BN_, int EC> static void fill_kernels(GemmKern (&t)[2][2][
     t[1][0][0] = k_gemm_bf16x3<true, false, NP, BN_, EC, false>;  t[1][0][1] = k_gemm_bf16x3<true, false, NP, BN_, EC, true>;
     t[1][1][0] = k_gemm_bf16x3<true, true, NP, BN_, EC, false>;   t[1][1][1] = k_gemm_bf16x3<true, true, NP, BN_, EC, true>;
 }
-static GemmKern g_kernels[3][2][2][2];
-static const int g_cfg_threads[3] = {TileCfg<2, 128, 64>::THREADS, TileCfg<2, 256, 128>::THREADS, TileCfg<3, 128, 128>::THREADS};
-static const int g_cfg_bn[3] = {128, 256, 128};
+static GemmKern g_kernels[4][2][2][2];
+static const int g_cfg_threads[4] = {TileCfg<2, 128, 64>::THREADS, TileCfg<2, 256, 128>::THREADS, TileCfg<3, 128, 128>::THREADS,
+                                     TileCfg<2, 128, 64, true>::THREADS};
+static const int g_cfg_bn[4] = {128, 256, 128, 128};
 
 static bool prepare_kernels() {
     static bool filled = false;
@@ -1132,15 +1250,19 @@ static bool prepare_kernels() {
         fill_kernels<2, 128, 64>(g_kernels[0]);
         fill_kernels<2, 256, 128>(g_kernels[1]);
         fill_kernels<3, 128, 128>(g_kernels[2]);
+        // configuration 3: operands from 4-bit state (row-major A and B only)
+        for (int i = 0; i < 8; ++i) g_kernels[3][(i >> 2) & 1][(i >> 1) & 1][i & 1] = nullptr;
+        g_kernels[3][0][1][0] = k_gemm_bf16x3<false, true, 2, 128, 64, false, true>;
         filled = true;
     }
     static PerDeviceOnce attr_done;                      // function attributes are per device
     const int dev = current_device();
     if (attr_done.pending(dev)) {
-        for (int i = 0; i < 24; ++i)
-            if (cudaFuncSetAttribute(reinterpret_cast<const void *>(g_kernels[i / 8][(i >> 2) & 1][(i >> 1) & 1][i & 1]),
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
+        for (int i = 0; i < 32; ++i) {
+            GemmKern k = g_kernels[i / 8][(i >> 2) & 1][(i >> 1) & 1][i & 1];
+            if (k && cudaFuncSetAttribute(reinterpret_cast<const void *>(k), cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
                 return false;
+        }
         attr_done.mark(dev);
     }
     return true;
@@ -1148,8 +1270,6 @@ static bool prepare_kernels() {
 
 // Test hook: force a tile configuration for two-plane products (-1: choose by problem size).
 static int g_force_bn = -1;
-static int g_wide_min_k = 0;
-static int g_heavy_narrow = 1;
 
 // a.Ahi/Alo (+ Amid/Bmid for three planes: order hi, mid, lo).  With `qs` the result (and the C
 // operand, if qs->q_in) is 4-bit state instead of a.C / a.D.
@@ -1169,7 +1289,16 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     if (a.M < 0 || a.N < 0 || a.K < 0 || a.batch < 0) return record(QT_ERR_ARG);
     if (a.M == 0 || a.N == 0 || a.batch == 0) return record(QT_OK);
     if (a.K == 0) return record(QT_ERR_UNSUPPORTED);
-    if (!a.Ahi || !a.Alo || !a.Bhi || !a.Blo || (!qs && !a.D && !a.Dhi && !x.Thi && !x.maxdev)) return record(QT_ERR_ARG);
+    const bool qa = x.aq.codes != nullptr, qb = x.bq.codes != nullptr;
+    if (qa || qb) {
+        // operands from 4-bit state: scaled fp16 two-plane products with row-major operands only
+        if (np != 2 || !x.f16 || a.a_mn || !a.b_mn || qs || !x.oq_code) return record(QT_ERR_UNSUPPORTED);
+        if (qa && (x.aq.n != a.M || a.K != a.M || x.aq.n % 16 || !x.aq.absmax || !x.a_exp)) return record(QT_ERR_ARG);
+        if (qb && (x.bq.n != a.N || a.K != a.N || x.bq.n % 16 || !x.bq.absmax || !x.b_exp)) return record(QT_ERR_ARG);
+        if ((qa && ((reinterpret_cast<uintptr_t>(x.aq.codes) & 7) || (x.aq.stride_codes & 7))) ||
+            (qb && ((reinterpret_cast<uintptr_t>(x.bq.codes) & 7) || (x.bq.stride_codes & 7)))) return record(QT_ERR_ARG);
+    }
+    if ((!qa && (!a.Ahi || !a.Alo)) || (!qb && (!a.Bhi || !a.Blo)) || (!qs && !a.D && !a.Dhi && !x.Thi && !x.maxdev)) return record(QT_ERR_ARG);
     if ((a.Dhi == nullptr) != (a.Dlo == nullptr) || (Amid == nullptr) != (Bmid == nullptr)) return record(QT_ERR_ARG);
     if (a.Dhi && np == 3 && !x.Dmid) return record(QT_ERR_ARG);                  // three-plane result needs all three planes
     if (x.Thi && (!x.Tmid || !x.Tlo || np != 3 || a.ldp <= 0)) return record(QT_ERR_ARG);
@@ -1181,33 +1310,34 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     const void *Bp[3] = {a.Bhi, np == 3 ? Bmid : a.Blo, a.Blo};
     // TMA: 16-byte aligned bases, row pitches and batch strides
     for (int i = 0; i < np; ++i)
-        if (!al16(Ap[i]) || !al16(Bp[i])) return record(QT_ERR_ARG);
-    if (a.lda % 8 || a.ldb % 8 || a.strideA % 8 || a.strideB % 8) return record(QT_ERR_ARG);
+        if ((!qa && !al16(Ap[i])) || (!qb && !al16(Bp[i]))) return record(QT_ERR_ARG);
+    if ((!qa && (a.lda % 8 || a.strideA % 8)) || (!qb && (a.ldb % 8 || a.strideB % 8))) return record(QT_ERR_ARG);
     if (!prepare_kernels()) return record(QT_ERR_LAUNCH);
     const int sms = device_sm_count();
     const int tiles_m = (a.M + BM - 1) / BM;
-    // tile configuration: the wide tile when it still leaves every SM at least two tiles
+    // Tile configuration.  The narrow tile with eight epilogue warps is the default: it holds a
+    // thread's 64 partial sums without spilling and keeps twice the loads in flight for epilogues that
+    // stream C, D and planes.  The wide tile needs 25 % less operand traffic per flop (the 128 x 128
+    // tile is bound by operand delivery from L2) and is faster on a plain long-K product (280 vs
+    // 289 us on 125 x 768^3), but its epilogue threads hold 128 partial sums and spill at the 168
+    // registers a 320-thread CTA leaves them; over the whole optimizer step it loses 0.6 ms.  It
+    // stays selectable (qt_gemm_force_tile) for measurements.
     int cfg = np == 3 ? 2 : 0;
-    if (np == 2 && a.N > 128) {
-        // the wide tile pays where the product is bound by operand delivery (long K); a short-K
-        // product is bound by its epilogue, which the narrow tile's four warps with all their
-        // registers do better
-        const long long wide_tiles = (long long)tiles_m * ((a.N + 255) / 256) * a.batch;
-        const bool heavy_epilogue = a.C != nullptr && a.beta != 0.0f && a.Dhi != nullptr;   // streams C, D and planes
-        if (wide_tiles >= 2LL * sms && a.K >= g_wide_min_k && !(heavy_epilogue && g_heavy_narrow)) cfg = 1;
-        if (g_force_bn == 128) cfg = 0;
-        if (g_force_bn == 256) cfg = 1;
-    }
+    if (np == 2 && a.N > 128 && g_force_bn == 256) cfg = 1;
+    if (qa || qb) cfg = 3;
     const int bn = g_cfg_bn[cfg];
     GemmMaps maps;
+    memset(&maps, 0, sizeof(maps));
     bool ok = true;
     for (int i = 0; i < 3; ++i) {
         const void *pa = Ap[i < np ? i : 0], *pb = Bp[i < np ? i : 0];
         const bool h = x.f16 != 0;
-        if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a_entries, a.lda, a.strideA, BK, BM, h);   // stored [M][K]
-        else         ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a_entries, a.lda, a.strideA, 64, BK, h);   // stored [K][M]
-        if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, b_entries, a.ldb, a.strideB, BK, bn, h);   // stored [N][K]
-        else         ok = ok && make_map(&maps.b[i], pb, a.N, a.K, b_entries, a.ldb, a.strideB, 64, BK, h);   // stored [K][N]
+        if (qa) {}
+        else if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a_entries, a.lda, a.strideA, BK, BM, h);   // stored [M][K]
+        else              ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a_entries, a.lda, a.strideA, 64, BK, h);   // stored [K][M]
+        if (qb) {}
+        else if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, b_entries, a.ldb, a.strideB, BK, bn, h);   // stored [N][K]
+        else              ok = ok && make_map(&maps.b[i], pb, a.N, a.K, b_entries, a.ldb, a.strideB, 64, BK, h);   // stored [K][N]
     }
     if (!ok) return record(QT_ERR_LAUNCH);
     GemmParams p;
@@ -1221,6 +1351,7 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     p.a_slot = x.a_slot; p.b_slot = x.b_slot; p.d_slot = x.d_slot; p.active = x.active;
     p.f16 = x.f16; p.a_exp = x.a_exp; p.b_exp = x.b_exp; p.ab_exp0 = x.ab_exp0;
     p.out_exp = x.out_exp; p.out_exp_w = x.out_exp_w; p.out_exp0 = x.out_exp0; p.out_rel = x.out_rel; p.kc = x.kc;
+    p.aq = x.aq; p.bq = x.bq; p.oq_code = x.oq_code;
     p.tiles_m = tiles_m; p.tiles_n = (a.N + bn - 1) / bn;
     p.q_in = nullptr; p.q_absmax_in = p.q_diag_in = nullptr; p.q_out = nullptr; p.q_absmax_out = p.q_diag_out = nullptr;
     p.q_stride_codes = p.q_stride_absmax = p.q_stride_diag = 0; p.q_code = nullptr; p.q_nb = 0;
@@ -1477,7 +1608,7 @@ int qt_matmul_f32_static(const float *A, long long lda, long long strideA, int t
 
 int qt_device_error(int clear) { return read_gemm_error(clear != 0); }
 
-void qt_gemm_force_tile(int bn) { if (bn >= 1000) g_wide_min_k = bn - 1000; else if (bn == 1 || bn == 0) g_heavy_narrow = bn; else g_force_bn = bn; }
+void qt_gemm_force_tile(int bn) { g_force_bn = bn; }
 
 int qt_split_f16(const float *X, long long ldx, long long strideX, int rows, int cols, int batch,
                  const long long *index, long long stride_index, const float *scale, long long stride_scale,
@@ -1500,6 +1631,11 @@ int qt_gemm_ex(const qt_gemm_desc *d, void *stream) {
     x.a_entries = d->a_entries; x.b_entries = d->b_entries;
     x.f16 = d->f16; x.a_exp = d->a_exp; x.b_exp = d->b_exp; x.ab_exp0 = d->ab_exp0;
     x.out_exp = d->out_exp; x.out_exp_w = d->out_exp_w; x.out_exp0 = d->out_exp0; x.out_rel = d->out_rel; x.kc = d->kc;
+    if (d->aq_codes) x.aq = QOperand{d->aq_codes, d->aq_absmax, d->aq_diag, d->aq_slots, d->aq_stride_codes, d->aq_stride_absmax,
+                                     d->aq_stride_diag, d->M, (d->M + 63) / 64};
+    if (d->bq_codes) x.bq = QOperand{d->bq_codes, d->bq_absmax, d->bq_diag, d->bq_slots, d->bq_stride_codes, d->bq_stride_absmax,
+                                     d->bq_stride_diag, d->N, (d->N + 63) / 64};
+    x.oq_code = d->oq_code;
     if (three && (!d->A[1] || !d->B[1])) return record(QT_ERR_ARG);
     QuantStateArgs qs{d->q_code, d->q_in, d->q_absmax_in, d->q_diag_in, d->q_out, d->q_absmax_out, d->q_diag_out,
                       d->q_stride_codes, d->q_stride_absmax, d->q_stride_diag};

@@ -59,6 +59,8 @@ int launch_dequantize(const DequantArgs &a, cudaStream_t stream);
 // `target`, written to exp_out); nullptr: plain bf16 planes.
 int launch_dequantize_planes(const DequantArgs &a, const int *slots, void *hi, void *lo, long long ldp, long long strideP,
                              cudaStream_t stream, float *amax_scratch = nullptr, int target = 0, int *exp_out = nullptr);
+int launch_state_exponents(const float *absmax, long long stride_absmax, int n_absmax, const float *diag, long long stride_diag,
+                           int n_diag, const int *slots, int count, int target, int *exp_out, cudaStream_t stream);
 int launch_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches_dev,
                              cudaStream_t stream);
 int launch_householder_panel(float *A, long long strideA, int n, int count, int j0, int w,

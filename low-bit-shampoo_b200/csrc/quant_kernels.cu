@@ -439,7 +439,7 @@ __device__ __forceinline__ void stg256u(void *p, const unsigned (&v)[8]) {
 __global__ void __launch_bounds__(256)
 k_state_amax(const float *__restrict__ absmax_base, long long stride_absmax, int n_absmax,
              const float *__restrict__ diag_base, long long stride_diag, int n_diag,
-             const int *__restrict__ slots, float *__restrict__ amax) {
+             const int *__restrict__ slots, float *__restrict__ amax, int *__restrict__ exp_out = nullptr, int target = 0) {
     const int m = blockIdx.x;
     const long long src = slots ? (long long)slots[m] : (long long)m;
     float v = 0.0f;
@@ -453,7 +453,8 @@ k_state_amax(const float *__restrict__ absmax_base, long long stride_absmax, int
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int i = 1; i < 8; ++i) v = fmaxf(v, red[i]);
-        amax[m] = v;
+        if (amax) amax[m] = v;
+        if (exp_out) exp_out[m] = exponent_for(v, target);
     }
 }
 
@@ -791,6 +792,15 @@ int launch_dequantize(const DequantArgs &a, cudaStream_t s) {
     } else {
         if (a.bits == 4) launch_dequantize_typed<__nv_bfloat16, 4>(a, s); else launch_dequantize_typed<__nv_bfloat16, 8>(a, s);
     }
+    return check_launch();
+}
+
+int launch_state_exponents(const float *absmax, long long stride_absmax, int n_absmax, const float *diag, long long stride_diag,
+                           int n_diag, const int *slots, int count, int target, int *exp_out, cudaStream_t s) {
+    if (count < 0 || n_absmax < 0 || !absmax || !exp_out) return record(QT_ERR_ARG);
+    if (count == 0) return record(QT_OK);
+    k_state_amax<<<count, 256, 0, s>>>(absmax, stride_absmax, n_absmax, diag, stride_diag, n_diag, slots, nullptr, exp_out, target);
+    count_launch(1);
     return check_launch();
 }
 

@@ -301,8 +301,9 @@ class _ShampooBase(optim.Optimizer):
                    "normalisation": "ieee division", "ties": "lower code"}
 
     def _check_device_error(self):
-        """Raises if a bounded wait inside one of the library's kernels ran out since the last
-        check (its results are then garbage).  Synchronises; called where the caller does anyway."""
+        """Raises if one of the library's kernels set the device status word since the last check
+        (a bounded wait ran out, or a value left the range of a scaled operand plane: the results
+        are then garbage).  Synchronises; called where the caller does anyway."""
         lib = F.lib
         if lib is None:
             return
@@ -311,8 +312,9 @@ class _ShampooBase(optim.Optimizer):
             with torch.cuda.device(dev):
                 rc = lib.qt_device_error(1)
             if rc != 0:
-                raise RuntimeError(f"a device-side wait of libqtensor_b200 timed out on {dev} (status {rc}): "
-                                   "optimizer state written since the previous check is not valid")
+                raise RuntimeError(f"a kernel of libqtensor_b200 reported status {rc} on {dev} "
+                                   f"({lib.qt_error_string(rc).decode()}): optimizer state written since the "
+                                   "previous check is not valid")
 
     def state_dict(self):
         self._check_device_error()

@@ -100,6 +100,12 @@ class QuantArena:
         """(codes, absmax, diag or None) views of matrices a..b-1, the operand form of _gemm.matmul_q4."""
         return self.var[a:b], self.absmax[a:b], (self.diag[a:b] if self.diagreal else None)
 
+    def operand(self, slots):
+        """Matrices `slots` as a product operand that stays 4-bit: dequantized tile by tile inside
+        the product kernel (no fp32 copy, no operand planes in device memory)."""
+        idx = _index_tensor(list(slots), self.device, torch.int32)
+        return _gemm.StateOperand(self.var, self.absmax, self.diag if self.diagreal else None, self.code, self.n, idx)
+
     def dequantize_planes(self, slots):
         """Matrices `slots` (any order, repeats allowed) as bf16 hi/lo Planes, written by the
         dequantize kernel itself: no fp32 copy, no gather, no split pass (qt_dequantize_planes)."""
@@ -209,7 +215,14 @@ class OrderClass:
 # ---------------------------------------------------------------------------------------
 USE_TENSOR_CORES = True
 FUSE_STATE_EPILOGUE = True     # products that end in 4-bit state quantize inside the GEMM epilogue
-DEQUANTIZE_TO_PLANES = True    # preconditioners are dequantized straight into bf16 operand planes
+DEQUANTIZE_TO_PLANES = True    # preconditioners are dequantized straight into operand planes, never to fp32
+# ... or inside the product itself (converter warps of the product kernel).  A tile of the 4-bit
+# operand is converted once per output tile that uses it, so this pays while few output tiles share
+# an operand tile (measured on the ViT-B/32 apply products, where 6 to 24 column tiles share each
+# tile of P: 5.9 ms per steady-state step against 4.1 ms through planes written once); with
+# DEQUANTIZE_IN_PRODUCT_MAX_SHARE = None every eligible product takes this path.
+DEQUANTIZE_IN_PRODUCT = True
+DEQUANTIZE_IN_PRODUCT_MAX_SHARE = 2
 # Set while an order class with plain 16/32-bit state, or a Schur-Newton inverse root, is
 # processed: those paths have no quantisation noise to hide the ~1e-5 relative error of the
 # split-bf16 products (and the Newton iteration amplifies it), so they stay on fp32 products.
@@ -632,8 +645,14 @@ def preconditioned_blocks(items):
         for s in range(0, len(ks), cap):
             part = ks[s: s + cap]
             G = torch.stack([items[k][4] for k in part])
-            P0 = Mat(planes=c0.prec.dequantize_planes([items[k][1] for k in part]))
-            P1 = Mat(planes=c1.prec.dequantize_planes([items[k][3] for k in part]))
+            def operand(c, sl, sharing_tiles):
+                ok = (DEQUANTIZE_IN_PRODUCT and _gemm.FP16_PLANES and c.prec.bits == 4 and c.prec.blocksize == 64 and c.n % 16 == 0
+                      and (DEQUANTIZE_IN_PRODUCT_MAX_SHARE is None or sharing_tiles <= DEQUANTIZE_IN_PRODUCT_MAX_SHARE))
+                return c.prec.operand(sl) if ok else c.prec.dequantize_planes(sl)
+            # P0 (m x m) is the left operand of P0 G: each of its tiles serves ceil(k / 128) output tiles;
+            # P1 (k x k) is the right operand of (P0 G) P1: each tile serves ceil(m / 128) output tiles
+            P0 = Mat(planes=operand(c0, [items[k][1] for k in part], (shape[1] + 127) // 128))
+            P1 = Mat(planes=operand(c1, [items[k][3] for k in part], (shape[0] + 127) // 128))
             T = mm(P0, Mat(G), want_float=False, want_planes=True)
             R = mm(T, P1).f32
             for j, k in enumerate(part):

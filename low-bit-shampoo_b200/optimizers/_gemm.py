@@ -96,6 +96,29 @@ class Planes:
         return full.view(self.batch, self.rows, self.ld)[:, :, : self.cols]
 
 
+class StateOperand:
+    """A product operand that stays 4-bit state: `batch` square matrices of order n, matrix m being
+    slot slots[m] of an arena (codes uint8 (count, row_bytes), absmax fp32 (count, n*nb), diag fp32
+    (count, n) or None).  The product kernel's converter warps dequantize it tile by tile in
+    shared memory (qt_gemm_ex, aq_* / bq_*); only the per-matrix plane exponents are computed
+    beforehand, from the block scales and the diagonal (qt_state_exponents)."""
+
+    f16, mid, exp0, offset = True, None, 0, 0
+
+    def __init__(self, var, absmax, diag, code, n, slots, target=None):
+        self.var, self.absmax, self.diag, self.code, self.slots = var, absmax, diag, code, slots
+        self.rows = self.cols = n
+        self.batch = slots.numel()
+        self.tmax = SPLIT_TARGET if target is None else target
+        self.hi = var                                       # device / stream anchor
+        self.exp = torch.empty(self.batch, dtype=torch.int32, device=var.device)
+        with torch.cuda.device(var.device):
+            rc = F.lib.qt_state_exponents(_ptr(absmax), absmax.stride(0), absmax.shape[1],
+                                          _ptr(diag), diag.stride(0) if diag is not None else 0, n,
+                                          _ptr(slots), self.batch, self.tmax, _ptr(self.exp), F._stream(var))
+        F._check(rc, "state exponents")
+
+
 def split3(X):
     """fp32 (batch, rows, cols) tensor -> three-plane bf16 Planes (hi, mid, lo; 24 significant bits)."""
     assert X.dim() == 3 and X.dtype == torch.float32 and X.stride(2) == 1
@@ -143,7 +166,7 @@ def _split_f16(X, index, scale, target, bound):
                                 _ptr(scale), scale.stride(0) if scale is not None else 0,
                                 _ptr(amax), compute, None, exp0, _ptr(exp),
                                 P.ptr_hi(), P.ptr_lo(), P.ld, P.stride, F._stream(X))
-    F._check(rc, "split_f16")
+    F._check(rc, f"split_f16 ({b} x {rows}x{c})")
     return P
 
 
@@ -202,6 +225,8 @@ def matmul(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, out=
         assert D.stride(2) == 1
     if C is not None:
         assert C.stride(2) == 1
+    if isinstance(A, StateOperand) or isinstance(B, StateOperand):
+        assert not trans_a and not trans_b, "an operand from 4-bit state is used as stored (row-major)"
     three = A.mid is not None or B.mid is not None
     f16 = A.f16 or B.f16
     if three:
@@ -285,10 +310,19 @@ def gemm_ex(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, D=N
     d = GemmDesc()
     ip = lambda t: None if t is None else t.data_ptr()
     po = lambda X, t: None if t is None else t.data_ptr() + 2 * X.offset
-    d.A[0], d.A[1], d.A[2] = po(A, A.hi), po(A, A.mid), po(A, A.lo)
-    d.B[0], d.B[1], d.B[2] = po(B, B.hi), po(B, B.mid), po(B, B.lo)
-    d.lda, d.strideA, d.a_mn, d.a_entries = A.ld, A.stride, 1 if trans_a else 0, A.batch
-    d.ldb, d.strideB, d.b_mn, d.b_entries = B.ld, B.stride, 0 if trans_b else 1, B.batch
+    d.a_mn, d.b_mn = 1 if trans_a else 0, 0 if trans_b else 1
+    for X, side in ((A, "a"), (B, "b")):
+        if isinstance(X, StateOperand):
+            setattr(d, side + "q_codes", ip(X.var)); setattr(d, side + "q_absmax", ip(X.absmax)); setattr(d, side + "q_diag", ip(X.diag))
+            setattr(d, side + "q_slots", ip(X.slots)); setattr(d, side + "q_stride_codes", X.var.stride(0))
+            setattr(d, side + "q_stride_absmax", X.absmax.stride(0)); setattr(d, side + "q_stride_diag", X.diag.stride(0) if X.diag is not None else 0)
+            d.oq_code = ip(X.code)
+    if not isinstance(A, StateOperand):
+        d.A[0], d.A[1], d.A[2] = po(A, A.hi), po(A, A.mid), po(A, A.lo)
+        d.lda, d.strideA, d.a_entries = A.ld, A.stride, A.batch
+    if not isinstance(B, StateOperand):
+        d.B[0], d.B[1], d.B[2] = po(B, B.hi), po(B, B.mid), po(B, B.lo)
+        d.ldb, d.strideB, d.b_entries = B.ld, B.stride, B.batch
     d.M, d.N, d.K, d.batch, d.alpha, d.beta = M, N, K, b, float(alpha), float(beta)
     if C is not None:
         d.C, d.ldc, d.strideC = C.data_ptr(), C.stride(1), C.stride(0)
@@ -311,4 +345,4 @@ def gemm_ex(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, D=N
         d.q_stride_codes, d.q_stride_absmax, d.q_stride_diag = q["stride_codes"], q["stride_absmax"], q["stride_diag"]
     with torch.cuda.device(A.hi.device):
         rc = F.lib.qt_gemm_ex(ct.byref(d), F._stream(A.hi))
-    F._check(rc, "gemm_ex")
+    F._check(rc, f"gemm_ex ({b} x {M}x{N}x{K})")

@@ -22,7 +22,7 @@ LEGACY_SYMBOLS = tuple(
 EXTRA_SYMBOLS = (
     "qt_version", "qt_launch_count", "qt_note_graph_replay", "qt_last_error", "qt_error_string", "qt_set_stream",
     "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_dequantize_planes", "qt_householder_panel", "qt_merge_t", "qt_selftest_division", "qt_split_bf16", "qt_split_bf16_rows", "qt_gemm_bf16x3", "qt_split_bf16_3", "qt_gemm_bf16x6", "qt_gemm_bf16x3_q4", "qt_gemm_bf16x6_q4", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error", "qt_adamw_tail", "qt_selftest_wait_timeout", "qt_gemm_ex", "qt_gemm_force_tile", "qt_power_iter",
-    "qt_inverse_root_newton", "qt_inverse_root_newton_workspace_bytes", "qt_split_f16", "qt_dequantize_planes_f16", "qt_householder_panel_fused",
+    "qt_inverse_root_newton", "qt_inverse_root_newton_workspace_bytes", "qt_split_f16", "qt_dequantize_planes_f16", "qt_householder_panel_fused", "qt_state_exponents",
 )
 
 _lib = None
@@ -43,7 +43,12 @@ class GemmDesc(ct.Structure):
                 ("a_exp", ct.c_void_p), ("b_exp", ct.c_void_p), ("out_exp", ct.c_void_p), ("out_exp_w", ct.c_void_p),
                 ("q_code", ct.c_void_p), ("q_in", ct.c_void_p), ("q_absmax_in", ct.c_void_p), ("q_diag_in", ct.c_void_p),
                 ("q_out", ct.c_void_p), ("q_absmax_out", ct.c_void_p), ("q_diag_out", ct.c_void_p),
-                ("q_stride_codes", ct.c_longlong), ("q_stride_absmax", ct.c_longlong), ("q_stride_diag", ct.c_longlong)]
+                ("q_stride_codes", ct.c_longlong), ("q_stride_absmax", ct.c_longlong), ("q_stride_diag", ct.c_longlong),
+                ("oq_code", ct.c_void_p),
+                ("aq_codes", ct.c_void_p), ("aq_absmax", ct.c_void_p), ("aq_diag", ct.c_void_p), ("aq_slots", ct.c_void_p),
+                ("aq_stride_codes", ct.c_longlong), ("aq_stride_absmax", ct.c_longlong), ("aq_stride_diag", ct.c_longlong),
+                ("bq_codes", ct.c_void_p), ("bq_absmax", ct.c_void_p), ("bq_diag", ct.c_void_p), ("bq_slots", ct.c_void_p),
+                ("bq_stride_codes", ct.c_longlong), ("bq_stride_absmax", ct.c_longlong), ("bq_stride_diag", ct.c_longlong)]
 
 
 def library_path() -> Path:
@@ -110,6 +115,8 @@ def _declare(lib):
     lib.qt_split_f16.argtypes = [vp, i64, i64, i32, i32, i32, vp, i64, vp, i64, vp, i32, vp, i32, vp, vp, vp, i64, i64, vp]
     lib.qt_dequantize_planes_f16.restype = i32
     lib.qt_dequantize_planes_f16.argtypes = [vp, i64, vp, i32, i32, vp, i64, vp, i64, vp, vp, i32, vp, vp, vp, i64, i64, i32, i32, vp]
+    lib.qt_state_exponents.restype = i32
+    lib.qt_state_exponents.argtypes = [vp, i64, i32, vp, i64, i32, vp, i32, i32, vp, vp]
     lib.qt_householder_panel_fused.restype = i32
     lib.qt_householder_panel_fused.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, i64, i32, vp, i32, vp]
     lib.qt_gemm_force_tile.restype = None

@@ -16,6 +16,7 @@ Same names, argument order and return values as the reference's qtensor/function
   without a return statement (:312-368) although every branch fills `out`.
 """
 import ctypes as ct
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -89,9 +90,21 @@ def _packed_numel(order: int, bits: int) -> int:
     return (order * order + per_byte - 1) // per_byte
 
 
+# QT_CHECK_EACH_CALL=1: synchronise after every library call and read the device status word, so
+# that a kernel-side error (a bounded wait that ran out, a value outside an operand plane's range)
+# is reported by the call that caused it instead of at the next periodic check.  Debugging aid:
+# it serialises the step and cannot be used while a CUDA graph is being captured.
+CHECK_EACH_CALL = os.environ.get("QT_CHECK_EACH_CALL", "0") == "1"
+
+
 def _check(status: int, what: str):
     if status != 0:
         raise RuntimeError(f"{what} failed: {lib.qt_error_string(status).decode()} (status {status})")
+    if CHECK_EACH_CALL and not torch.cuda.is_current_stream_capturing():
+        torch.cuda.synchronize()
+        rc = lib.qt_device_error(1)
+        if rc != 0:
+            raise RuntimeError(f"{what}: device status {rc} ({lib.qt_error_string(rc).decode()})")
 
 
 def _stream(t: Tensor) -> ct.c_void_p:

@@ -247,3 +247,44 @@ def test_split_rows_gathers_and_scales(native_lib):
             W = _gemm.split(ref.contiguous())
             assert device_ok(native_lib)
             assert torch.equal(P.to_float(), W.to_float())
+
+
+@pytest.mark.parametrize("n,other", [(128, 64), (768, 3072), (1200, 768), (672, 100), (1104, 1200), (48, 48)])
+@pytest.mark.parametrize("diagreal", [True, False])
+def test_operand_dequantized_inside_the_product(native_lib, n, other, diagreal):
+    """P G and G P with P taken straight from 4-bit state by the kernel's converter warps: the
+    same bytes as dequantizing P into operand planes first (qt_dequantize_planes_f16) and
+    multiplying those, for scattered, repeated slots, zero blocks and a tail block included."""
+    import qtensor.functional as F
+    from optimizers import _gemm
+    from optimizers import _engine as E
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(n * 7 + other)
+    code = F.create_linear_map(True, 4, 2).to(dev)
+    count = 5
+    arena = E.QuantArena(n, count, dev, 4, 64, code, 0, diagreal=diagreal)
+    X = torch.randn(count, n, n, device=dev, generator=gen) * torch.logspace(-2, 1, count, device=dev).view(-1, 1, 1)
+    X[1, :, : min(n, 64)] = 0.0                               # all-zero quantization blocks
+    arena.quantize(0, count, X.contiguous())
+    slots = [3, 0, 3, 4, 1, 2]
+    b = len(slots)
+    G_left = torch.randn(b, n, other, device=dev, generator=gen)
+    G_right = torch.randn(b, other, n, device=dev, generator=gen)
+    planes = arena.dequantize_planes(slots)
+    state = arena.operand(slots)
+    assert torch.equal(state.exp, planes.exp)
+    # P @ G: the 4-bit operand on the A side
+    want, _ = _gemm.matmul(planes, _gemm.split(G_left))
+    got, _ = _gemm.matmul(state, _gemm.split(G_left))
+    assert device_ok(native_lib)
+    assert torch.equal(got, want)
+    ref = arena.dequantize(0, count)[slots].double() @ G_left.double()
+    assert rel(got, ref) < 2e-6
+    # G @ P: on the B side, result also handed on as planes
+    Gp = _gemm.split(G_right)
+    want, wantP = _gemm.matmul(Gp, planes, want_planes=True)
+    got, gotP = _gemm.matmul(Gp, state, want_planes=True)
+    assert device_ok(native_lib)
+    assert torch.equal(got, want) and torch.equal(gotP.to_float(), wantP.to_float())
+    ref = G_right.double() @ arena.dequantize(0, count)[slots].double()
+    assert rel(got, ref) < 2e-6

@@ -265,3 +265,34 @@ def test_adamw_tail_entry_point_handles_unaligned_and_ragged_tensors(native_lib)
     # a chunk size that is not a multiple of four is refused, nothing is launched
     assert native_lib.qt_adamw_tail(vp(tabs[0]), vp(tabs[1]), vp(tabs[2]), vp(tabs[3]), vp(numels), vp(tct), vp(tci), len(ct_), 6,
                                     vp(scal), beta1, beta2, 1 - beta1, 1 - beta2, eps, None) != 0
+
+
+def test_step_with_preconditioners_dequantized_inside_the_products(native_lib):
+    """The apply products P_L G P_R with the 4-bit preconditioners dequantized by the product
+    kernel's converter warps (every eligible product) give the same parameters as the default
+    mix (through operand planes where many output tiles share an operand tile)."""
+    from optimizers import _engine
+    from optimizers.shampoo2 import ShampooAdamW
+    shapes = [(256, 192), (192,), (128, 320), (64, 64), (96, 1216)]
+    hyper = dict(lr=1e-2, weight_decay=0.05, prec_bits=4, stat_compute_steps=1, prec_compute_steps=1)
+
+    def run(max_share):
+        keep = _engine.DEQUANTIZE_IN_PRODUCT_MAX_SHARE
+        _engine.DEQUANTIZE_IN_PRODUCT_MAX_SHARE = max_share
+        try:
+            g = torch.Generator().manual_seed(13)
+            ps = [torch.nn.Parameter((torch.randn(s, generator=g) * 0.3).cuda()) for s in shapes]
+            opt = ShampooAdamW(ps, **hyper)
+            for _ in range(3):
+                for p in ps:
+                    p.grad = (torch.randn(p.shape, generator=g) * 0.1).cuda()
+                opt.step()
+            torch.cuda.synchronize()
+            return [p.detach().cpu() for p in ps]
+        finally:
+            _engine.DEQUANTIZE_IN_PRODUCT_MAX_SHARE = keep
+
+    everywhere, nowhere, mixed = run(None), run(0), run(2)
+    assert native_lib.qt_device_error(1) == 0
+    for a, b, c in zip(everywhere, nowhere, mixed):
+        assert torch.equal(a, b) and torch.equal(c, b)
