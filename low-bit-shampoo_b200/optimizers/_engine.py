@@ -603,7 +603,7 @@ def _class_roots(cls, slots, eps, inv_root_mode, exponent, starts=None):
                     for _ in range(cls.rect_t2):
                         rows = op_bjorck(rows, want_planes=True)
                 rho = eps * cls.max_eig[a:b]
-                weights = 1 / (cls.S[a:b] + rho.unsqueeze(1)).pow(1 / exponent)
+                weights = F.ridged_inverse_root(cls.S[a:b], rho.unsqueeze(1), exponent)
                 if cls.prec.fusable() and _tc(rows.f32 if rows.f32 is not None else rows._planes.hi):
                     # rows^T diag(w) rows straight into the 4-bit preconditioner (quantized in the epilogue)
                     scaled = _gemm.split_rows(rows.f32, None, weights.contiguous(),

@@ -207,13 +207,25 @@ def dequantize_blockwise_diagreal(
 
 
 @torch.no_grad()
+def ridged_inverse_root(S, rho, p):
+    """(S + rho)^(-1/p) as in the reference (functional.py:760-762) wherever S + rho > 0.  The S are
+    Rayleigh quotients of a positive semi-definite statistic computed in fp32: rounding can
+    leave one at or below -rho (seen after ten identical gradients on a 768 x 384 block, where the
+    kept half of the spectrum is pure ridge), which the reference turns into inf or NaN that then
+    spreads over the parameter.  Such an entry is treated as the zero it stands for:
+    rho^(-1/p).  `rho` broadcasts against the last dimension of S."""
+    t = S + rho
+    return 1 / torch.where(t > 0, t, rho.expand_as(t) if torch.is_tensor(rho) else torch.full_like(t, rho)).pow(1 / p)
+
+
+@torch.no_grad()
 def compute_power(Vt, S, p, iter_count=4, ridge_epsilon=1e-6, indices=None, max_eigen=None):
     """Inverse p-th root from an eigen-factor form: rows `indices` of Vt are rectified by
     `iter_count` Bjorck steps, then  rows^T diag((S + ridge * lambda_max)^(-1/p)) rows
     (reference functional.py:749-762; lambda_max defaults to max(S))."""
     rows = Vt[indices] if indices is not None else Vt
     top = max_eigen if max_eigen is not None else S.max()
-    weights = 1 / (S + ridge_epsilon * top).pow(1 / p)
+    weights = ridged_inverse_root(S, ridge_epsilon * top, p)
     if rows.is_cuda and rows.dtype == torch.float32 and lib is not None:
         # the same products on the tensor cores (batch of one; fp32 results re-split between
         # products, so any input is accepted - the optimizers' batched engine chains planes instead)

@@ -72,3 +72,21 @@ def test_block_partitioner_roundtrip():
     assert bp.num_splits() == 2
     # a dimension that is an exact multiple makes no empty block (reference: (d-1)//block_size)
     assert [tuple(p.shape) for p in BlockPartitioner(torch.zeros(8, 3), 4).partition(torch.zeros(8, 3))] == [(4, 3), (4, 3)]
+
+
+def test_ridged_inverse_root_equals_reference_where_it_is_finite():
+    """(S + rho)^(-1/p) of the reference (functional.py:760-762) wherever S + rho > 0; a Rayleigh
+    quotient that rounding pushed to or below -rho (the reference returns inf / NaN there) counts
+    as the zero it stands for."""
+    import qtensor.functional as F
+    S = torch.tensor([[2.0, 0.5, 0.0, -5e-7, -1e-6, -1.0025e-6, -3e-6]])
+    rho = torch.tensor([[1e-6]])
+    got = F.ridged_inverse_root(S, rho, 4)
+    want = 1 / (S + rho).pow(0.25)
+    finite = torch.isfinite(want)
+    assert finite.tolist() == [[True, True, True, True, False, False, False]]
+    assert torch.equal(got[finite], want[finite])
+    assert torch.equal(got[~finite], (1 / rho.pow(0.25)).expand_as(S)[~finite])
+    assert torch.isfinite(got).all()
+    # scalar ridge, as the single-matrix form passes it
+    assert torch.equal(F.ridged_inverse_root(S[0], 1e-6 * torch.tensor(1.0), 4), got[0])
