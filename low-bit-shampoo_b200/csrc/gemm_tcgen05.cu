@@ -9,12 +9,12 @@
 // hi*hi + hi*lo + lo*hi (the lo*lo term, below 2^-16 relative, is dropped).  Three
 // tcgen05.mma.kind::f16 instructions per k-slice share one TMEM accumulator.
 //
-// Kernel structure (persistent: one CTA per SM walks over 128 x 128 output tiles; two TMEM
+// Kernel structure (persistent: one CTA per SM walks over 128 x 128 output tiles; a ring of TMEM
 // accumulators so the epilogue of tile i overlaps the main loop of tile i+1):
 //   warp 4      TMA producer: cp.async.bulk.tensor 3-D loads (batch is the third
 //               coordinate) of the four operand planes into a 3-stage shared-memory ring,
 //               128-byte swizzle, completion on mbarriers;
-//   warp 5      allocates 256 TMEM columns and issues the MMAs (one elected lane);
+//   warp 5      allocates the SM's 512 TMEM columns and issues the MMAs (one elected lane);
 //               tcgen05.commit releases ring slots and signals the epilogue;
 //   warps 0-3   epilogue: tcgen05.ld (32 lanes x 32 columns per instruction), then
 //               D = alpha * acc + beta * C in fp32, written as fp32 and/or as bf16 hi/lo
@@ -41,9 +41,15 @@ static constexpr unsigned WAIT_LIMIT = 1u << 18;
 //                      128x256x16 MMA instead of 8 KiB per 128x128x16 one: 25 % less shared-memory
 //                      traffic per flop, which is what bounds the 128 x 128 tile)
 //   NP = 3, BN_ = 128: 96 KiB per stage, 2 stages
-template <int NP, int BN_, int EC, bool CONV = false> struct TileCfg {
+//   PAIR (NP = 2, BN_ = 128): two CTAs of a cluster (an SM pair) share one 256 x 128 tile through
+//                      tcgen05 cta_group::2: each CTA stages its own 128 rows of A and only HALF of B
+//                      (64 of the 128 columns), 48 KiB per stage instead of 64, 4 stages; the tensor
+//                      cores of the pair exchange the B halves between themselves.  25 % less operand
+//                      traffic from L2 and from shared memory per flop.
+template <int NP, int BN_, int EC, bool CONV = false, bool PAIR = false> struct TileCfg {
     static constexpr int B_TILES = BN_ / 128;
-    static constexpr int STAGE_BYTES = NP * (1 + B_TILES) * PLANE_TILE_BYTES;
+    static constexpr int B_PLANE_BYTES = PAIR ? PLANE_TILE_BYTES / 2 : B_TILES * PLANE_TILE_BYTES;
+    static constexpr int STAGE_BYTES = NP * (PLANE_TILE_BYTES + B_PLANE_BYTES);
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
     // Epilogue warp e reads TMEM lanes 32 (e & 3) .. +31 and EC accumulator columns starting at
     // EC (e >> 2).  EC = 64 halves the partial sums a thread holds (no register spills with
@@ -52,7 +58,12 @@ template <int NP, int BN_, int EC, bool CONV = false> struct TileCfg {
     // CONV: four more warps that build an operand's tiles in shared memory from 4-bit state
     static constexpr int CONV_WARPS = CONV ? 4 : 0;
     static constexpr int THREADS = (EPI_WARPS + 2 + CONV_WARPS) * 32;
-    static constexpr int TMEM_COLS = 2 * BN_;                        // two accumulators
+    // The whole tensor memory of the SM (one CTA per SM) as a ring of accumulators: four of 128
+    // columns, two of 256.  With accumulation chains of 128 k an accumulator is busy for 0.8 us of
+    // MMAs only, and the epilogue warps are away for microseconds while they store a finished tile;
+    // a ring of two let the MMA issuer run just two chains ahead before it stalled on them.
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int NACC = TMEM_COLS / BN_;
 };
 
 __device__ int g_gemm_error = 0;
@@ -98,14 +109,15 @@ struct GemmParams {
 // roughly square patch: both operands' k-panels are then shared by a dozen CTAs through L2
 // instead of one operand by all and the other by two (matters once a matrix exceeds L2).
 static constexpr int RASTER_M = 12;
+template <int RASTER = RASTER_M>
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int &tm, int &tn, int &b) {
     const int per_matrix = tiles_m * tiles_n;
     b = tile / per_matrix;
     const int t = tile - b * per_matrix;
-    const int group = t / (RASTER_M * tiles_n);
-    const int first_m = group * RASTER_M;
-    const int gsize = min(tiles_m - first_m, RASTER_M);
-    const int r = t - group * RASTER_M * tiles_n;
+    const int group = t / (RASTER * tiles_n);
+    const int first_m = group * RASTER;
+    const int gsize = min(tiles_m - first_m, RASTER);
+    const int r = t - group * RASTER * tiles_n;
     tn = r / gsize;
     tm = first_m + (r - tn * gsize);
 }
@@ -121,12 +133,24 @@ __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded parity wait; also gives up when another role raised the CTA's abort flag.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag) {
-    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
-        unsigned ok;
+// One poll of a barrier's phase.  CLUSTER: acquire at cluster scope (the arrival may come from the
+// other CTA of a pair).
+template <bool CLUSTER>
+__device__ __forceinline__ unsigned mbar_try(unsigned bar, unsigned parity) {
+    unsigned ok;
+    if constexpr (CLUSTER)
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    else
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded parity wait; also gives up when another role raised the CTA's abort flag.
+template <bool CLUSTER = false>
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag) {
+    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+        const unsigned ok = mbar_try<CLUSTER>(bar, parity);
         if (ok) return true;
         if ((it & 1023u) == 1023u && *abort_flag) return false;
     }
@@ -136,12 +160,12 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
 }
 // Warp-collective wait: lane 0 polls with a short sleep between polls (the other 31 lanes and
 // the other warps' issue slots stay free for the MMA and TMA threads), result broadcast.
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity, volatile int *abort_flag) {
     unsigned ok = 0;
     if ((threadIdx.x & 31) == 0) {
         for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
-            asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            ok = mbar_try<CLUSTER>(bar, parity);
             if (ok) break;
             if ((it & 255u) == 255u && *abort_flag) break;
             // try_wait already suspends the thread for a while; an extra sleep only pays once the
@@ -160,6 +184,43 @@ __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
+// ---- CTA pairs (cta_group::2) -------------------------------------------------------------
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ unsigned map_to_cta(unsigned addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Load into this CTA's shared memory; the bytes are counted on a barrier that may belong to the
+// other CTA of the pair (`bar`: a shared::cluster address).  No multicast: every CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_3d_pair(unsigned dst, const CUtensorMap *map, unsigned bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// One MMA over both SMs of the pair: 256 x N x 16, rows 0..127 accumulate in this CTA's tensor
+// memory, rows 128..255 in the peer's; each CTA's shared memory holds its rows of A and its half of B
+// at the offsets the descriptors name.
+__device__ __forceinline__ void umma_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrival on `bar` (a shared::cluster address, either CTA's) once the pair's MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 __device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
                                           unsigned idesc, unsigned accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
@@ -427,17 +488,33 @@ __device__ __forceinline__ void convert_q4_row(const QOperand &q, const float *c
     }
 }
 
-template <bool A_MN, bool B_MN, int NP, int BN_, int EC, bool QOUT = false, bool CONV = false>
-__global__ void __launch_bounds__(TileCfg<NP, BN_, EC, CONV>::THREADS, 1)
+template <bool A_MN, bool B_MN, int NP, int BN_, int EC, bool QOUT = false, bool CONV = false, bool PAIR = false>
+__global__ void __launch_bounds__(TileCfg<NP, BN_, EC, CONV, PAIR>::THREADS, 1)
 k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
-    using Cfg = TileCfg<NP, BN_, EC, CONV>;
+    using Cfg = TileCfg<NP, BN_, EC, CONV, PAIR>;
     static_assert(!CONV || (NP == 2 && !A_MN && B_MN && BN_ == 128), "operands from 4-bit state: A row-major, B row-major, two planes");
+    static_assert(!PAIR || (NP == 2 && BN_ == 128 && !CONV && !QOUT), "CTA pairs: plain two-plane products with 128-column tiles");
+    // PAIR: launched as clusters of two CTAs.  CTA rank r of a pair owns rows [128 r, +128) of the
+    // pair's 256 x 128 tile and columns [64 r, +64) of its B operand.  Rank 0 (the leader) issues
+    // the MMAs for both; every CTA runs its own TMA producer and epilogue.  p.tiles_m counts
+    // 256-row bands.  Barrier traffic between the two CTAs:
+    //   full[s]      leader's only: counts the TMA bytes of BOTH CTAs;
+    //   empty[s]     one per CTA, both signalled by the leader's tcgen05.commit;
+    //   acc_full[a]  one per CTA, both signalled by the leader's tcgen05.commit;
+    //   acc_empty[a] leader's only: the epilogue warps of both CTAs arrive on it.
+    // Waits stay bounded; a CTA never returns before the final cluster barrier, so its peer never
+    // touches shared or tensor memory of a CTA that is gone.
+    const unsigned rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0u;
+    const int cta_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;     // first tile of this CTA (pair)
+    const int cta_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    constexpr int TILE_M = PAIR ? 2 * BM : BM;
     __shared__ float conv_code[CONV ? 16 : 1];
     __shared__ QuantTablesHolder<QOUT> qtab;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
     constexpr int EPI_WARPS = Cfg::EPI_WARPS;
-    constexpr int B_PLANE_BYTES = Cfg::B_TILES * PLANE_TILE_BYTES;
+    constexpr int B_PLANE_BYTES = Cfg::B_PLANE_BYTES;
     // The tensor core's fp32 accumulation truncates: the error of one accumulation chain grows
     // linearly with its length (measured 6.5e-9 * K relative, biased).  The three-plane variant
     // therefore accumulates at most KC k-blocks (128 k) per TMEM accumulator and the epilogue
@@ -451,18 +528,20 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *aligned = smem_raw + (base - smem_u32(smem_raw));
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(aligned + RING_BYTES);
-    // bars[0..S): full, [S..2S): empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
-    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 2 * STAGES + 4);
+    // bars[0..S): full, [S..2S): empty, [2S..2S+NACC): accumulator full, [2S+NACC..2S+2 NACC): accumulator empty
+    constexpr int NACC = Cfg::NACC;
+    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 2 * STAGES + 2 * NACC);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const unsigned bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
     auto acc_full = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
-    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+    auto acc_empty = [&](int a) { return bar0 + 8u * (2 * STAGES + NACC + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // a wait that expired in an earlier CTA (or launch) poisons the rest of the grid: drain fast
-    if (*reinterpret_cast<volatile int *>(&g_gemm_error) != 0) return;
+    // (not in a pair: the two CTAs could decide differently, and one would wait for the other)
+    if (!PAIR && *reinterpret_cast<volatile int *>(&g_gemm_error) != 0) return;
     const int num_kb = (p.K + BK - 1) / BK;
     const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
     const int nchunks = (num_kb + KC - 1) / KC;
@@ -473,16 +552,23 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         // state, when each of the four converter warps has arrived
         const unsigned full_count = 1u + ((conv_a || conv_b) ? (unsigned)Cfg::CONV_WARPS : 0u);
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), full_count); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), EPI_WARPS); }
+        for (int a = 0; a < NACC; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), PAIR ? 2 * EPI_WARPS : EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == EPI_WARPS + 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            // the same warp of both CTAs allocates the same columns in both tensor memories
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();                   // the peer's barriers are initialised, its tensor memory allocated
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
     if constexpr (QOUT) build_tables<16>(qtab.t, p.q_code);    // all threads; ends with a barrier
@@ -500,20 +586,41 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         if (lane == 0) {
             unsigned it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = cta_first; tile < num_tiles && ok; tile += cta_step) {
                 int tm, tn, b;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
+                tile_coords<PAIR ? RASTER_M / 2 : RASTER_M>(tile, p.tiles_m, p.tiles_n, tm, tn, b);
                 if (skipped(b)) continue;
                 const int za = p.a_slot ? __ldg(p.a_slot + b) : b;
                 const int zb = p.b_slot ? __ldg(p.b_slot + b) : b;
-                const int m0 = tm * BM, n0 = tn * BN_;
+                const int m0 = tm * TILE_M + (int)rank * BM, n0 = tn * BN_;
+                // pair: this CTA stages the columns [n0 + rank * ncur / 2, + ncur / 2) of B (ncur: the
+                // tile's existing columns rounded up to 16, as the MMA issuer computes it)
+                const int nhalf = min(BN_, (p.N - n0 + 15) & ~15) >> 1;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
-                    ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
+                    ok = mbar_wait<PAIR>(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     const unsigned stage = base + s * STAGE_BYTES;
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES - (conv_a ? NP * PLANE_TILE_BYTES : 0) - (conv_b ? NP * B_PLANE_BYTES : 0));
                     const int k0 = kb * BK;
+                    if constexpr (PAIR) {
+                        const unsigned lead_full = map_to_cta(full_bar(s), 0u);
+                        if (leader) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+#pragma unroll
+                        for (int pl = 0; pl < NP; ++pl) {
+                            const unsigned ta = stage + pl * PLANE_TILE_BYTES;
+                            const unsigned tb = stage + NP * PLANE_TILE_BYTES + pl * B_PLANE_BYTES;
+                            if (!A_MN) {
+                                tma_load_3d_pair(ta, &maps.a[pl], lead_full, k0, m0, za);
+                            } else {
+                                tma_load_3d_pair(ta, &maps.a[pl], lead_full, m0, k0, za);
+                                tma_load_3d_pair(ta + PLANE_TILE_BYTES / 2, &maps.a[pl], lead_full, m0 + 64, k0, za);
+                            }
+                            if (!B_MN) tma_load_3d_pair(tb, &maps.b[pl], lead_full, k0, n0 + (int)rank * nhalf, zb);
+                            else       tma_load_3d_pair(tb, &maps.b[pl], lead_full, n0 + (int)rank * nhalf, k0, zb);
+                        }
+                        continue;
+                    }
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES - (conv_a ? NP * PLANE_TILE_BYTES : 0) - (conv_b ? NP * B_PLANE_BYTES : 0));
 #pragma unroll
                     for (int pl = 0; pl < NP; ++pl) {
                         const unsigned ta = stage + pl * PLANE_TILE_BYTES;
@@ -538,12 +645,12 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             }
         }
     } else if (warp == EPI_WARPS + 1) {
-        // ---------------- MMA issuer: accumulator j&1 in TMEM columns [ (j&1)*BN_, +BN_ )
-        if (lane == 0) {
-            // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N, M
+        // ---------------- MMA issuer: accumulator j % NACC in TMEM columns [ (j % NACC) * BN_, +BN_ )
+        if (lane == 0 && leader) {
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, majors, N, M (256 for a CTA pair)
             const unsigned fmt = p.f16 ? 0u : ((1u << 7) | (1u << 10));          // operand format: 0 = fp16, 1 = bf16
             const unsigned idesc = (1u << 4) | fmt | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-                                   ((unsigned)(BN_ >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+                                   ((unsigned)(BN_ >> 3) << 17) | ((unsigned)(TILE_M >> 4) << 24);
             // descriptors differ only in their 14-bit start-address field: build one per operand
             // plane for stage 0, k-slice 0 and add (byte offset >> 4) afterwards
             const unsigned a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
@@ -557,25 +664,25 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             unsigned it = 0;
             bool ok = true;
             int j = 0;                                      // accumulator hand-offs so far
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = cta_first; tile < num_tiles && ok; tile += cta_step) {
                 // a ragged last column band needs only its own columns (N is any multiple of 16):
                 // the tensor core's time per MMA scales with N
                 int tm_, tn_, b_;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm_, tn_, b_);
+                tile_coords<PAIR ? RASTER_M / 2 : RASTER_M>(tile, p.tiles_m, p.tiles_n, tm_, tn_, b_);
                 if (skipped(b_)) continue;
                 const int ncur = min(BN_, (p.N - tn_ * BN_ + 15) & ~15);
                 const unsigned idesc_tile = (idesc & ~(0x3Fu << 17)) | ((unsigned)(ncur >> 3) << 17);
                 int kb = 0;
                 for (int ch = 0; ch < nchunks && ok; ++ch, ++j) {
-                    const int acc = j & 1;
-                    ok = mbar_wait(acc_empty(acc), ((j >> 1) & 1) ^ 1, abort_flag);
+                    const int acc = j % NACC;
+                    ok = mbar_wait<PAIR>(acc_empty(acc), ((j / NACC) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN_);
                     const int kend = min(num_kb, kb + KC);
                     for (bool fresh = true; kb < kend; ++kb, ++it, fresh = false) {
                         const int s = it % STAGES;
-                        ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
+                        ok = mbar_wait<PAIR>(full_bar(s), (it / STAGES) & 1, abort_flag);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         // K-major: 8-row groups 1024 B apart, a 16-element k-slice is 32 B further along the row.
@@ -591,14 +698,27 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                             for (int sum = NP - 1; sum >= 0; --sum) {
 #pragma unroll
                                 for (int ia = 0; ia <= sum; ++ia) {
-                                    umma_bf16(tmem_acc, dA[ia] + ao, dB[sum - ia] + bo, idesc_tile, first ? 0u : 1u);
+                                    if constexpr (PAIR) umma_pair(tmem_acc, dA[ia] + ao, dB[sum - ia] + bo, idesc_tile, first ? 0u : 1u);
+                                    else                umma_bf16(tmem_acc, dA[ia] + ao, dB[sum - ia] + bo, idesc_tile, first ? 0u : 1u);
                                     first = false;
                                 }
                             }
                         }
-                        umma_commit(empty_bar(s));
+                        if constexpr (PAIR) {                      // the slot is free in both CTAs
+                            umma_commit_pair(empty_bar(s));
+                            umma_commit_pair(map_to_cta(empty_bar(s), 1u));
+                        } else {
+                            umma_commit(empty_bar(s));
+                        }
                     }
-                    if (ok) umma_commit(acc_full(acc));
+                    if (ok) {
+                        if constexpr (PAIR) {                      // both CTAs' epilogues read their half of the rows
+                            umma_commit_pair(acc_full(acc));
+                            umma_commit_pair(map_to_cta(acc_full(acc), 1u));
+                        } else {
+                            umma_commit(acc_full(acc));
+                        }
+                    }
                 }
             }
         }
@@ -616,10 +736,12 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                             ((reinterpret_cast<uintptr_t>(p.Dhi) | reinterpret_cast<uintptr_t>(p.Dmid) | reinterpret_cast<uintptr_t>(p.Dlo) |
                               reinterpret_cast<uintptr_t>(p.Thi) | reinterpret_cast<uintptr_t>(p.Tmid) | reinterpret_cast<uintptr_t>(p.Tlo)) & 31) == 0;
         int j = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const unsigned lead_acc_empty0 = PAIR ? map_to_cta(acc_empty(0), 0u) : 0u;
+        for (int tile = cta_first; tile < num_tiles; tile += cta_step) {
             int tm, tn, b;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, b);
+            tile_coords<PAIR ? RASTER_M / 2 : RASTER_M>(tile, p.tiles_m, p.tiles_n, tm, tn, b);
             if (skipped(b)) continue;
+            if constexpr (PAIR) tm = 2 * tm + (int)rank;       // this CTA's 128-row band
             const int m0 = tm * BM, n0 = tn * BN_ + seg * EC;
             const int row = m0 + quad * 32 + lane;
             const bool row_ok = row < p.M;
@@ -629,8 +751,8 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             for (int q = 0; q < EC; ++q) sum[q] = 0.0f;
             bool ok = true;
             for (int ch = 0; ch < nchunks; ++ch, ++j) {
-                const int acc = j & 1;
-                ok = mbar_wait_warp(acc_full(acc), (j >> 1) & 1, abort_flag);
+                const int acc = j % NACC;
+                ok = mbar_wait_warp<PAIR>(acc_full(acc), (j / NACC) & 1, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned tmem_acc = tmem_base + (unsigned)(acc * BN_ + seg * EC);
@@ -645,7 +767,10 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
+                if (lane == 0) {
+                    if constexpr (PAIR) mbar_arrive_cluster(lead_acc_empty0 + 8u * acc);
+                    else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(acc)) : "memory");
+                }
             }
             if (!ok) break;
             // scaled operand planes: the accumulator holds sum(a * 2^ea * b * 2^eb)
@@ -786,9 +911,13 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         }
     }
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();                   // neither CTA frees or leaves while its peer still works
     if (warp == EPI_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
     }
 }
 
@@ -1239,10 +1368,10 @@ template <int NP, int BN_, int EC> static void fill_kernels(GemmKern (&t)[2][2][
     t[1][0][0] = k_gemm_bf16x3<true, false, NP, BN_, EC, false>;  t[1][0][1] = k_gemm_bf16x3<true, false, NP, BN_, EC, true>;
     t[1][1][0] = k_gemm_bf16x3<true, true, NP, BN_, EC, false>;   t[1][1][1] = k_gemm_bf16x3<true, true, NP, BN_, EC, true>;
 }
-static GemmKern g_kernels[4][2][2][2];
-static const int g_cfg_threads[4] = {TileCfg<2, 128, 64>::THREADS, TileCfg<2, 256, 128>::THREADS, TileCfg<3, 128, 128>::THREADS,
-                                     TileCfg<2, 128, 64, true>::THREADS};
-static const int g_cfg_bn[4] = {128, 256, 128, 128};
+static GemmKern g_kernels[5][2][2][2];
+static const int g_cfg_threads[5] = {TileCfg<2, 128, 64>::THREADS, TileCfg<2, 256, 128>::THREADS, TileCfg<3, 128, 128>::THREADS,
+                                     TileCfg<2, 128, 64, true>::THREADS, TileCfg<2, 128, 64, false, true>::THREADS};
+static const int g_cfg_bn[5] = {128, 256, 128, 128, 128};
 
 static bool prepare_kernels() {
     static bool filled = false;
@@ -1253,12 +1382,18 @@ static bool prepare_kernels() {
         // configuration 3: operands from 4-bit state (row-major A and B only)
         for (int i = 0; i < 8; ++i) g_kernels[3][(i >> 2) & 1][(i >> 1) & 1][i & 1] = nullptr;
         g_kernels[3][0][1][0] = k_gemm_bf16x3<false, true, 2, 128, 64, false, true>;
+        // configuration 4: CTA pairs (cta_group::2) on 256 x 128 tiles, plain epilogue only
+        for (int i = 0; i < 8; ++i) g_kernels[4][(i >> 2) & 1][(i >> 1) & 1][i & 1] = nullptr;
+        g_kernels[4][0][0][0] = k_gemm_bf16x3<false, false, 2, 128, 64, false, false, true>;
+        g_kernels[4][0][1][0] = k_gemm_bf16x3<false, true, 2, 128, 64, false, false, true>;
+        g_kernels[4][1][0][0] = k_gemm_bf16x3<true, false, 2, 128, 64, false, false, true>;
+        g_kernels[4][1][1][0] = k_gemm_bf16x3<true, true, 2, 128, 64, false, false, true>;
         filled = true;
     }
     static PerDeviceOnce attr_done;                      // function attributes are per device
     const int dev = current_device();
     if (attr_done.pending(dev)) {
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 40; ++i) {
             GemmKern k = g_kernels[i / 8][(i >> 2) & 1][(i >> 1) & 1][i & 1];
             if (k && cudaFuncSetAttribute(reinterpret_cast<const void *>(k), cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
                 return false;
@@ -1268,7 +1403,8 @@ static bool prepare_kernels() {
     return true;
 }
 
-// Test hook: force a tile configuration for two-plane products (-1: choose by problem size).
+// Test hook: tile configuration of two-plane products.  -1: chosen by problem size; 128: single CTAs,
+// 128 x 128 tiles; 256: single CTAs, 128 x 256 tiles; 512: CTA pairs wherever they are possible.
 static int g_force_bn = -1;
 
 // a.Ahi/Alo (+ Amid/Bmid for three planes: order hi, mid, lo).  With `qs` the result (and the C
@@ -1325,6 +1461,13 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     int cfg = np == 3 ? 2 : 0;
     if (np == 2 && a.N > 128 && g_force_bn == 256) cfg = 1;
     if (qa || qb) cfg = 3;
+    // CTA pairs (256-row bands) only on request: measured on B200 they are no faster than single
+    // CTAs on 128 x 128 tiles (125 x 768^3: 372 vs 364 us; 8 x 4096^3: 3980 vs 3480 us) - halving
+    // the B operand a CTA stages does not pay while each SM still multiplies 128 x 128 x 16 per
+    // instruction; the 128 x 256 single-CTA tile is the one that gains (2900 us on the large case).
+    const bool pair_possible = cfg == 0 && !qs && sms >= 2 && a.M > BM;
+    if (pair_possible && g_force_bn == 512) cfg = 4;
+    const bool pair = cfg == 4;
     const int bn = g_cfg_bn[cfg];
     GemmMaps maps;
     memset(&maps, 0, sizeof(maps));
@@ -1336,7 +1479,7 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
         else if (!a.a_mn) ok = ok && make_map(&maps.a[i], pa, a.K, a.M, a_entries, a.lda, a.strideA, BK, BM, h);   // stored [M][K]
         else              ok = ok && make_map(&maps.a[i], pa, a.M, a.K, a_entries, a.lda, a.strideA, 64, BK, h);   // stored [K][M]
         if (qb) {}
-        else if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, b_entries, a.ldb, a.strideB, BK, bn, h);   // stored [N][K]
+        else if (!a.b_mn) ok = ok && make_map(&maps.b[i], pb, a.K, a.N, b_entries, a.ldb, a.strideB, BK, pair ? 64 : bn, h);   // stored [N][K]
         else              ok = ok && make_map(&maps.b[i], pb, a.N, a.K, b_entries, a.ldb, a.strideB, 64, BK, h);   // stored [K][N]
     }
     if (!ok) return record(QT_ERR_LAUNCH);
@@ -1352,7 +1495,7 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     p.f16 = x.f16; p.a_exp = x.a_exp; p.b_exp = x.b_exp; p.ab_exp0 = x.ab_exp0;
     p.out_exp = x.out_exp; p.out_exp_w = x.out_exp_w; p.out_exp0 = x.out_exp0; p.out_rel = x.out_rel; p.kc = x.kc;
     p.aq = x.aq; p.bq = x.bq; p.oq_code = x.oq_code;
-    p.tiles_m = tiles_m; p.tiles_n = (a.N + bn - 1) / bn;
+    p.tiles_m = pair ? (a.M + 2 * BM - 1) / (2 * BM) : tiles_m; p.tiles_n = (a.N + bn - 1) / bn;
     p.q_in = nullptr; p.q_absmax_in = p.q_diag_in = nullptr; p.q_out = nullptr; p.q_absmax_out = p.q_diag_out = nullptr;
     p.q_stride_codes = p.q_stride_absmax = p.q_stride_diag = 0; p.q_code = nullptr; p.q_nb = 0;
     if (qs) {
@@ -1363,8 +1506,27 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     }
     const long long ctas = (long long)p.tiles_m * p.tiles_n * a.batch;
     if (ctas > 0x7fffffffLL) return record(QT_ERR_UNSUPPORTED);
+    GemmKern kern = g_kernels[cfg][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0][qs ? 1 : 0];
+    if (pair) {
+        // persistent: one CTA pair (a cluster of two, scheduled on an SM pair) per two SMs
+        const long long pairs = ctas < sms / 2 ? ctas : sms / 2;
+        cudaLaunchConfig_t cfgl;
+        memset(&cfgl, 0, sizeof(cfgl));
+        cfgl.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+        cfgl.blockDim = dim3((unsigned)g_cfg_threads[cfg], 1, 1);
+        cfgl.dynamicSmemBytes = GEMM_SMEM;
+        cfgl.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfgl.attrs = attr;
+        cfgl.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfgl, kern, maps, p) != cudaSuccess) { cudaGetLastError(); return record(QT_ERR_LAUNCH); }
+        count_launch(1);
+        return check_launch();
+    }
     const unsigned grid = (unsigned)(ctas < sms ? ctas : sms);                   // persistent: one CTA per SM
-    g_kernels[cfg][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0][qs ? 1 : 0]<<<grid, g_cfg_threads[cfg], GEMM_SMEM, s>>>(maps, p);
+    kern<<<grid, g_cfg_threads[cfg], GEMM_SMEM, s>>>(maps, p);
     count_launch(1);
     return check_launch();
 }

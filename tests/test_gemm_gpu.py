@@ -288,3 +288,37 @@ def test_operand_dequantized_inside_the_product(native_lib, n, other, diagreal):
     assert torch.equal(got, want) and torch.equal(gotP.to_float(), wantP.to_float())
     ref = G_right.double() @ arena.dequantize(0, count)[slots].double()
     assert rel(got, ref) < 2e-6
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K,b", [(256, 128, 64, 1), (768, 768, 768, 3), (1200, 1200, 768, 2), (1104, 672, 200, 2),
+                                     (200, 72, 50, 5), (1000, 1008, 336, 2), (129, 16, 1200, 1)])
+def test_cta_pair_product_equals_single_cta_product(native_lib, trans_a, trans_b, M, N, K, b):
+    """The cta_group::2 kernel (two CTAs on one 256 x 128 tile, each staging half of B) against the
+    single-CTA kernel on the same planes: same accumulation chains, so the results are equal bit
+    for bit - fp32 output, plane output, C operand, ragged rows / columns / k, all operand majors."""
+    from optimizers import _gemm
+    g = torch.Generator(device="cuda").manual_seed(M + 3 * N + 7 * K)
+    A = torch.randn((b, K, M) if trans_a else (b, M, K), device="cuda", generator=g)
+    B = torch.randn((b, N, K) if trans_b else (b, K, N), device="cuda", generator=g)
+    C = torch.randn(b, M, N, device="cuda", generator=g)
+    Ap, Bp = _gemm.split(A), _gemm.split(B)
+    out = {}
+    try:
+        for tile in (128, 512):
+            native_lib.qt_gemm_force_tile(tile)
+            D, P = _gemm.matmul(Ap, Bp, trans_a=trans_a, trans_b=trans_b, alpha=0.75, beta=-1.25, C=C, want_planes=True,
+                                out_bound=4.0 * K)
+            guard = torch.full((b, M + 3, N + 16), 7.0, device="cuda")
+            _gemm.matmul(Ap, Bp, trans_a=trans_a, trans_b=trans_b, out=guard[:, :M, :N])
+            assert device_ok(native_lib)
+            valid = lambda t: t.view(b, M, P.ld)[:, :, :N].clone()      # the pitch padding is never written
+            out[tile] = (D, valid(P.hi), valid(P.lo), guard)
+    finally:
+        native_lib.qt_gemm_force_tile(-1)
+    for x, y in zip(out[128], out[512]):
+        assert torch.equal(x, y)
+    guard = out[512][3]
+    assert bool((guard[:, M:, :] == 7.0).all()) and bool((guard[:, :, N:] == 7.0).all())
+    ref = 0.75 * ((A.transpose(1, 2) if trans_a else A).double() @ (B.transpose(1, 2) if trans_b else B).double()) - 1.25 * C.double()
+    assert rel(out[512][0], ref) < 1e-5, rel(out[512][0], ref)
