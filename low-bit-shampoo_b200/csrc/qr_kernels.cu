@@ -56,9 +56,9 @@ k_householder_panel(float *__restrict__ Abase, long long strideA, int n, int j0,
     float *G = vb + 2 * RT * 32;                           // [32][33]  v_i . v_j, i < j
     float *Ts = G + kPanel * (kPanel + 1);                 // [32][33]
     float *tau = Ts + kPanel * (kPanel + 1);               // [32]
-    float *Vs = tau + kPanel;                              // [256][33] slab of the previous panel's vectors (fused form)
-    float *Tp = Vs + 256 * 33;                             // [32][33]  previous panel's triangular factor
-    float *zs = Tp + kPanel * (kPanel + 1);                // [32 warps][32]
+    float *Vs = tau + kPanel;                              // [256][36] slab of the previous panel's vectors (fused form); later the partial sums of W
+    float *Tp = Vs + 256 * 36;                             // [32][33]  previous panel's triangular factor
+    float *zs = Tp + kPanel * (kPanel + 1);                // [32][33]  z = Tp^T W
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunk = blockIdx.y;
     float *Amat = Abase + (long long)blockIdx.x * strideA;
@@ -81,7 +81,10 @@ k_householder_panel(float *__restrict__ Abase, long long strideA, int n, int j0,
         // Vp is streamed through shared memory in slabs of kSlab window rows; the next slab is
         // fetched into registers while the current one is being used, so the global-memory latency
         // of the 2 * ceil(mu / kSlab) dependent slab loads is hidden behind the arithmetic.
-        constexpr int kSlab = 256, kPer = kSlab * kPanel / kQrThreads;    // 8 elements per thread per slab
+        // In both passes a lane works on COLUMN `lane` of the chunk and a warp on a subset of the rows,
+        // so a row of Vp is read as broadcast 128-bit loads and serves all 32 columns at once (one
+        // warp per column re-read every row 32 times and was bound by shared-memory bandwidth).
+        constexpr int kSlab = 256, kVp = 36, kPer = kSlab * kPanel / kQrThreads;    // row pitch 36: 16-byte aligned rows
         float pre[kPer];
         auto fetch = [&](int rb) {
 #pragma unroll
@@ -94,49 +97,78 @@ k_householder_panel(float *__restrict__ Abase, long long strideA, int n, int j0,
 #pragma unroll
             for (int q = 0; q < kPer; ++q) {
                 const int i = tid + q * kQrThreads;
-                Vs[(i >> 5) * 33 + (i & 31)] = pre[q];
+                Vs[(i >> 5) * kVp + (i & 31)] = pre[q];
             }
         };
-        float wacc[kPanel];
+        // ---- W = Vp^T C.  Warp (g, h): reflector columns 8g .. 8g+7, rows h, h+8, .. of each slab.
+        const int g8 = (warp >> 3) * 8, h = warp & 7;
+        float wacc[8];
 #pragma unroll
-        for (int j = 0; j < kPanel; ++j) wacc[j] = 0.0f;
+        for (int j = 0; j < 8; ++j) wacc[j] = 0.0f;
         fetch(0);
-        for (int rb = 0; rb < mu; rb += kSlab) {           // W = Vp^T C
+        for (int rb = 0; rb < mu; rb += kSlab) {
             __syncthreads();
             stash();
             __syncthreads();
             fetch(rb + kSlab < mu ? rb + kSlab : 0);       // after the last slab: the first slab of the second pass
-#pragma unroll
-            for (int k = 0; k < kSlab / 32; ++k) {
-                const int rr = lane + 32 * k;
-                const float cv = (rb + rr < mu) ? C[(rb + rr) * 33 + warp] : 0.0f;
-#pragma unroll
-                for (int j = 0; j < kPanel; ++j) wacc[j] = fmaf(Vs[rr * 33 + j], cv, wacc[j]);
+#pragma unroll 4
+            for (int k = 0; k < kSlab / 8; ++k) {
+                const int rr = h + 8 * k;
+                if (rb + rr < mu) {
+                    const float cv = C[(rb + rr) * 33 + lane];
+                    const float4 v0 = *reinterpret_cast<const float4 *>(Vs + rr * kVp + g8);
+                    const float4 v1 = *reinterpret_cast<const float4 *>(Vs + rr * kVp + g8 + 4);
+                    wacc[0] = fmaf(v0.x, cv, wacc[0]); wacc[1] = fmaf(v0.y, cv, wacc[1]);
+                    wacc[2] = fmaf(v0.z, cv, wacc[2]); wacc[3] = fmaf(v0.w, cv, wacc[3]);
+                    wacc[4] = fmaf(v1.x, cv, wacc[4]); wacc[5] = fmaf(v1.y, cv, wacc[5]);
+                    wacc[6] = fmaf(v1.z, cv, wacc[6]); wacc[7] = fmaf(v1.w, cv, wacc[7]);
+                }
             }
         }
+        __syncthreads();                                   // the slab buffer is free: it takes the eight partial sums
+        float *Wpart = Vs;                                 // [8 row groups][32][33]
 #pragma unroll
-        for (int j = 0; j < kPanel; ++j) wacc[j] = warp_sum(wacc[j]);
-        // z = Tp^T w for this warp's column (lane i computes z_i), shared through zs
+        for (int j = 0; j < 8; ++j) Wpart[(h * kPanel + g8 + j) * 33 + lane] = wacc[j];
+        __syncthreads();
+        float *Wm = G;                                     // [32][33]; G is cleared again before the factorisation
         {
-            float z = 0.0f;
+            float wsum = 0.0f;                             // W[warp][lane]
 #pragma unroll
-            for (int j = 0; j < kPanel; ++j) z = fmaf(Tp[j * (kPanel + 1) + lane], wacc[j], z);
-            zs[warp * kPanel + lane] = z;
+            for (int q = 0; q < 8; ++q) wsum += Wpart[(q * kPanel + warp) * 33 + lane];
+            Wm[warp * 33 + lane] = wsum;
         }
-        for (int rb = 0; rb < mu; rb += kSlab) {           // C -= Vp z
+        __syncthreads();
+        {
+            float z = 0.0f;                                // z[warp][lane] = (Tp^T W)[warp][lane]
+#pragma unroll
+            for (int j = 0; j < kPanel; ++j) z = fmaf(Tp[j * (kPanel + 1) + warp], Wm[j * 33 + lane], z);
+            zs[warp * 33 + lane] = z;
+        }
+        __syncthreads();
+        float zreg[kPanel];
+#pragma unroll
+        for (int j = 0; j < kPanel; ++j) zreg[j] = zs[j * 33 + lane];
+        // ---- C -= Vp z.  Warp w: rows w, w+32, .. of each slab.
+        for (int rb = 0; rb < mu; rb += kSlab) {
             __syncthreads();
             stash();
             __syncthreads();
             if (rb + kSlab < mu) fetch(rb + kSlab);
-            const float *zw = zs + warp * kPanel;          // read by every lane at the same address: a broadcast
-#pragma unroll
+#pragma unroll 2
             for (int k = 0; k < kSlab / 32; ++k) {
-                const int rr = lane + 32 * k;
+                const int rr = warp + 32 * k;
                 if (rb + rr < mu) {
-                    float acc = 0.0f;
+                    float a0 = 0.0f, a1 = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < kPanel; ++j) acc = fmaf(Vs[rr * 33 + j], zw[j], acc);
-                    C[(rb + rr) * 33 + warp] -= acc;
+                    for (int j = 0; j < kPanel; j += 8) {
+                        const float4 v0 = *reinterpret_cast<const float4 *>(Vs + rr * kVp + j);
+                        const float4 v1 = *reinterpret_cast<const float4 *>(Vs + rr * kVp + j + 4);
+                        a0 = fmaf(v0.x, zreg[j], a0); a0 = fmaf(v0.y, zreg[j + 1], a0);
+                        a0 = fmaf(v0.z, zreg[j + 2], a0); a0 = fmaf(v0.w, zreg[j + 3], a0);
+                        a1 = fmaf(v1.x, zreg[j + 4], a1); a1 = fmaf(v1.y, zreg[j + 5], a1);
+                        a1 = fmaf(v1.z, zreg[j + 6], a1); a1 = fmaf(v1.w, zreg[j + 7], a1);
+                    }
+                    C[(rb + rr) * 33 + lane] -= a0 + a1;
                 }
             }
         }
@@ -251,7 +283,7 @@ static int launch_panel_rpl(float *A, long long strideA, int n, int count, int j
                             int prev_w, const float *Tprev, int block_end) {
     const int m = n - j0;
     const size_t smem = sizeof(float) * ((size_t)(((kPanel + m) * 33 + 31) & ~31) + 2 * (RPL + RS) * 32 + 2 * kPanel * (kPanel + 1) + kPanel +
-                                         256 * 33 + kPanel * (kPanel + 1) + 32 * kPanel);
+                                         256 * 36 + kPanel * (kPanel + 1) + kPanel * (kPanel + 1));
     static PerDeviceOnce attr_set;                         // function attributes are per device
     const int dev = current_device();
     if (attr_set.pending(dev)) {

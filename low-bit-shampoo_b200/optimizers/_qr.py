@@ -77,12 +77,43 @@ def _merge_t(Vo, Tp, widths, Pv=None):
     return T
 
 
+LOOKAHEAD = True            # far update split into the next block's columns (critical path) and the rest (side stream)
+FORWARD_Q_MAX_BATCH = 24    # up to this many matrices Q is accumulated block by block beside the factorisation
+
+_SIDE_STREAMS = {}
+
+
+def _side_streams(device):
+    """Two side streams per (device, calling stream): order classes factor concurrently on
+    streams of their own, and each of them needs its own pair."""
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    pair = _SIDE_STREAMS.get(key)
+    if pair is None:
+        pair = _SIDE_STREAMS[key] = (torch.cuda.Stream(device=device), torch.cuda.Stream(device=device))
+    return pair
+
+
+def _apply_block(Yp, Pv, target, target_planes):
+    """target <- target - Y (V^T target), fp32 and planes in one epilogue."""
+    from optimizers import _gemm
+    _, Wp = _gemm.matmul(Pv, target_planes, trans_a=True, want_float=False, want_planes=True)
+    _gemm.matmul(Yp, Wp, alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
+    return Wp
+
+
 def householder_q(X, tensor_cores=True):
     """Q of the QR factorisation of each X[b] (X: (B, n, n) fp32 CUDA, overwritten).
     `tensor_cores=False` keeps every product in fp32 library products.  The planes of X carry one
     exponent per matrix, fixed when X is first split: Householder reflections preserve column
     norms, so no entry of the trailing matrix outgrows sqrt(n) times the largest entry of X, which
-    the split's headroom (largest entry below 2^9 of fp16's 2^16) covers up to n = 16384."""
+    the split's headroom (largest entry below 2^9 of fp16's 2^16) covers up to n = 16384.
+
+    The chain of 32-column panel launches is the critical path (a panel kernel occupies one SM
+    per matrix for 30-150 us whatever the batch).  With LOOKAHEAD only the update of the NEXT
+    outer block's 128 columns stays on it; the rest of each far update runs on a side stream beside
+    the next block's panels.  For small batches Q is accumulated forwards on a second side stream,
+    Q <- Q (I - V T V^T) per finished block (1.5x the flops of the backward accumulation over
+    shrinking windows, but off the critical path), so that Q is ready when the last panel is."""
     B, n, _ = X.shape
     if (not X.is_cuda) or n > MAX_ORDER or n < 2:
         return torch.linalg.qr(X).Q
@@ -94,11 +125,22 @@ def householder_q(X, tensor_cores=True):
     npan = (n + PANEL - 1) // PANEL
     V = torch.zeros(B, n, n, dtype=torch.float32, device=X.device)
     T = torch.empty(B, npan, PANEL, PANEL, dtype=torch.float32, device=X.device)
-    stream = F._stream(X)
-    blocks = []                                           # (J0, wo, T_big)
+    blocks = []                                           # (J0, wo, T_big, planes of V)
     split = _gemm.split
+    lookahead = tc and LOOKAHEAD and n > 2 * OUTER
+    forward_q = lookahead and B <= FORWARD_Q_MAX_BATCH
+    keep = []                                             # tensors used on side streams stay alive until the join
     with torch.cuda.device(X.device):
+        main = torch.cuda.current_stream(X.device)
+        stream = F._stream(X)
+        rest_stream, q_stream = _side_streams(X.device) if lookahead else (None, None)
+        rest_done = None                                  # event: the previous block's remainder update
         Xp = split(X) if tc else None
+        Q = Qp = None
+        if forward_q:
+            Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
+            Qp = split(Q, bound=2.0)                      # Q stays orthonormal: entries <= 1
+            q_stream.wait_stream(main)
         for J0 in range(0, n, OUTER):
             wo = min(OUTER, n - J0)
             widths = []
@@ -117,9 +159,40 @@ def householder_q(X, tensor_cores=True):
             Pv = split(Vo, bound=2.0) if tc else None     # Householder vectors: entries <= 1; shared by the merge, the far update and the accumulation of Q
             Tb = _merge_t(Vo, T[:, J0 // PANEL:], widths, Pv)
             blocks.append((J0, wo, Tb, Pv))
-            if J0 + wo < n:
-                m, t = n - J0, n - J0 - wo
-                _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True, Pv)
+            m, t = n - J0, n - J0 - wo
+            if not lookahead:
+                if t > 0:
+                    _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True, Pv)
+                continue
+            if t == 0 and not forward_q:
+                continue
+            _, Yp = _gemm.matmul(Pv, split(Tb), trans_b=True, want_float=False, want_planes=True)     # Y = V T^T
+            keep += [Pv, Yp, Tb]
+            y_ready = torch.cuda.Event()
+            y_ready.record(main)
+            if t > 0:
+                nxt = min(OUTER, t)                        # the next outer block's columns: needed by its panels
+                if rest_done is not None:
+                    main.wait_event(rest_done)            # they were last written by the previous block's remainder
+                keep.append(_apply_block(Yp, Pv, X[:, J0:, J0 + wo:J0 + wo + nxt], Xp.window(J0, J0 + wo, m, nxt)))
+                if t > nxt:
+                    rest_stream.wait_event(y_ready)
+                    with torch.cuda.stream(rest_stream):
+                        keep.append(_apply_block(Yp, Pv, X[:, J0:, J0 + wo + nxt:], Xp.window(J0, J0 + wo + nxt, m, t - nxt)))
+                        rest_done = torch.cuda.Event()
+                        rest_done.record(rest_stream)
+            if forward_q:                                 # Q[:, :, J0:] <- Q[:, :, J0:] - (Q[:, :, J0:] V) Y^T
+                q_stream.wait_event(y_ready)
+                with torch.cuda.stream(q_stream):
+                    Qw = Qp.window(0, J0, n, m)
+                    _, Wp = _gemm.matmul(Qw, Pv, want_float=False, want_planes=True)
+                    _gemm.matmul(Wp, Yp, trans_b=True, alpha=-1.0, beta=1.0, C=Q[:, :, J0:], out=Q[:, :, J0:], out_planes=Qw)
+                    keep.append(Wp)
+        if lookahead:
+            main.wait_stream(rest_stream)
+            if forward_q:
+                main.wait_stream(q_stream)
+                return Q
         Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
         Qp = split(Q, bound=2.0) if tc else None         # Q stays orthonormal: entries <= 1
         for J0, wo, Tb, Pv in reversed(blocks):
