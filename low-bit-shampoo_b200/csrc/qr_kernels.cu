@@ -203,7 +203,15 @@ k_householder_panel(float *__restrict__ Abase, long long strideA, int n, int j0,
         const int r = lane + 32 * k;
         if (r < m) P[r * 33 + warp] = v;
     };
-    auto t_column = [&](int i) {                            // LAPACK slarft, forward / columnwise; whole warp
+    // Triangular factor (LAPACK slarft, forward / columnwise): T[:i, i] = -tau_i T[:i, :i] (V^T v_i)[:i].
+    // Warp l owns row l of T, lane k holding T[l][k] in a register; column i is added one step after
+    // its Gram entries G[:i][i] were written, by all finished warps at once (one product and one warp
+    // reduction each), off the critical path of the step.
+    // (The tall variants, which keep part of the panel in shared memory, have no register to spare:
+    // there warp 0 fills in the column from shared memory as before.)
+    constexpr bool T_IN_REGS = RS == 0;
+    float trow = 0.0f;
+    auto t_column_warp0 = [&](int i) {                      // whole warp; lane l computes T[l][i]
         const float ti = tau[i];
         if (lane == i) Ts[i * (kPanel + 1) + i] = ti;
         if (lane < i) {
@@ -217,6 +225,19 @@ k_householder_panel(float *__restrict__ Abase, long long strideA, int n, int j0,
             Ts[lane * (kPanel + 1) + i] = -ti * (a0 + a1);
         }
         __syncwarp();
+    };
+    auto t_column = [&](int i) {
+        if constexpr (!T_IN_REGS) {
+            if (warp == 0) t_column_warp0(i);
+            return;
+        }
+        if (warp < i) {
+            const float part = (lane >= warp && lane < i) ? trow * G[lane * (kPanel + 1) + i] : 0.0f;
+            const float sum = warp_sum(part);
+            if (lane == i) trow = -tau[i] * sum;
+        } else if (warp == i && lane == i) {
+            trow = tau[i];
+        }
     };
 
     for (int c = 0; c < w; ++c) {
@@ -260,10 +281,11 @@ k_householder_panel(float *__restrict__ Abase, long long strideA, int n, int j0,
             }
         }
         // column c-1 of T: its dot products were completed before this step's barrier
-        if (warp == 0 && c >= 1) t_column(c - 1);
+        if (c >= 1) t_column(c - 1);
     }
     __syncthreads();
-    if (warp == 0) t_column(w - 1);
+    t_column(w - 1);
+    if constexpr (T_IN_REGS) Ts[warp * (kPanel + 1) + lane] = (lane >= warp && lane < w && warp < w) ? trow : 0.0f;
 #pragma unroll
     for (int k = 0; k < RPL; ++k) {
         const int r = lane + 32 * k;
