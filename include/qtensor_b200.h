@@ -319,6 +319,9 @@ typedef struct qt_gemm_desc {
     long long aq_stride_codes, aq_stride_absmax, aq_stride_diag;
     const unsigned char *bq_codes; const float *bq_absmax, *bq_diag; const int *bq_slots;
     long long bq_stride_codes, bq_stride_absmax, bq_stride_diag;
+    int max_ctas;   /* > 0: at most this many CTAs (the kernel is persistent and otherwise takes every SM until
+                     * it is done, so a latency-critical kernel launched beside it on another stream would wait for
+                     * the whole product); 0: one CTA per SM */
 } qt_gemm_desc;
 int qt_gemm_ex(const qt_gemm_desc *desc, void *stream);
 

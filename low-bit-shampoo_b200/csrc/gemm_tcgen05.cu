@@ -1345,6 +1345,7 @@ struct GemmExtras {
     // operands straight from 4-bit state (see QOperand); codes == nullptr: from planes
     QOperand aq = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0}, bq = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
     const float *oq_code = nullptr;
+    int max_ctas = 0;                                       // > 0: cap of the persistent grid (SMs left to kernels on other streams)
 };
 
 static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -1509,7 +1510,8 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     GemmKern kern = g_kernels[cfg][a.a_mn ? 1 : 0][a.b_mn ? 1 : 0][qs ? 1 : 0];
     if (pair) {
         // persistent: one CTA pair (a cluster of two, scheduled on an SM pair) per two SMs
-        const long long pairs = ctas < sms / 2 ? ctas : sms / 2;
+        long long pairs = ctas < sms / 2 ? ctas : sms / 2;
+        if (x.max_ctas > 1 && pairs > x.max_ctas / 2) pairs = x.max_ctas / 2;
         cudaLaunchConfig_t cfgl;
         memset(&cfgl, 0, sizeof(cfgl));
         cfgl.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
@@ -1525,7 +1527,8 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
         count_launch(1);
         return check_launch();
     }
-    const unsigned grid = (unsigned)(ctas < sms ? ctas : sms);                   // persistent: one CTA per SM
+    unsigned grid = (unsigned)(ctas < sms ? ctas : sms);                         // persistent: one CTA per SM
+    if (x.max_ctas > 0 && grid > (unsigned)x.max_ctas) grid = (unsigned)x.max_ctas;
     kern<<<grid, g_cfg_threads[cfg], GEMM_SMEM, s>>>(maps, p);
     count_launch(1);
     return check_launch();
@@ -1792,7 +1795,7 @@ int qt_gemm_ex(const qt_gemm_desc *d, void *stream) {
     x.maxdev = d->maxdev; x.a_slot = d->a_slot; x.b_slot = d->b_slot; x.d_slot = d->d_slot; x.active = d->active;
     x.a_entries = d->a_entries; x.b_entries = d->b_entries;
     x.f16 = d->f16; x.a_exp = d->a_exp; x.b_exp = d->b_exp; x.ab_exp0 = d->ab_exp0;
-    x.out_exp = d->out_exp; x.out_exp_w = d->out_exp_w; x.out_exp0 = d->out_exp0; x.out_rel = d->out_rel; x.kc = d->kc;
+    x.out_exp = d->out_exp; x.out_exp_w = d->out_exp_w; x.out_exp0 = d->out_exp0; x.out_rel = d->out_rel; x.kc = d->kc; x.max_ctas = d->max_ctas;
     if (d->aq_codes) x.aq = QOperand{d->aq_codes, d->aq_absmax, d->aq_diag, d->aq_slots, d->aq_stride_codes, d->aq_stride_absmax,
                                      d->aq_stride_diag, d->M, (d->M + 63) / 64};
     if (d->bq_codes) x.bq = QOperand{d->bq_codes, d->bq_absmax, d->bq_diag, d->bq_slots, d->bq_stride_codes, d->bq_stride_absmax,

@@ -77,8 +77,9 @@ def _merge_t(Vo, Tp, widths, Pv=None):
     return T
 
 
-LOOKAHEAD = True            # far update split into the next block's columns (critical path) and the rest (side stream)
-FORWARD_Q_MAX_BATCH = 24    # up to this many matrices Q is accumulated block by block beside the factorisation
+LOOKAHEAD = False           # far update split into the next block's columns (critical path) and the rest (side stream);
+                            # measured: 5 % faster for 8 matrices of order 1200, 5-15 % slower from 16 matrices up - off
+FORWARD_Q = True            # Q accumulated block by block beside the factorisation (with LOOKAHEAD), else backwards afterwards
 
 _SIDE_STREAMS = {}
 
@@ -93,12 +94,23 @@ def _side_streams(device):
     return pair
 
 
-def _apply_block(Yp, Pv, target, target_planes):
-    """target <- target - Y (V^T target), fp32 and planes in one epilogue."""
+def _apply_block(Yp, Pv, target, target_planes, max_ctas=0):
+    """target <- target - Y (V^T target), fp32 and planes in one epilogue.  `max_ctas`: see
+    _background_ctas()."""
     from optimizers import _gemm
-    _, Wp = _gemm.matmul(Pv, target_planes, trans_a=True, want_float=False, want_planes=True)
-    _gemm.matmul(Yp, Wp, alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
+    _, Wp = _gemm.matmul(Pv, target_planes, trans_a=True, want_float=False, want_planes=True, max_ctas=max_ctas)
+    _gemm.matmul(Yp, Wp, alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes, max_ctas=max_ctas)
     return Wp
+
+
+def _background_ctas(device, batch):
+    """CTA cap of the products issued on the side streams.  The product kernel is persistent: it
+    takes every SM until it is done, and a panel launch (one CTA per matrix, the critical path)
+    issued meanwhile would wait for the whole product.  The cap leaves the panel kernel its SMs.
+    0: no room for background work."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    free = sms - batch - 4
+    return free if free >= sms // 4 else 0
 
 
 def householder_q(X, tensor_cores=True):
@@ -111,9 +123,13 @@ def householder_q(X, tensor_cores=True):
     The chain of 32-column panel launches is the critical path (a panel kernel occupies one SM
     per matrix for 30-150 us whatever the batch).  With LOOKAHEAD only the update of the NEXT
     outer block's 128 columns stays on it; the rest of each far update runs on a side stream beside
-    the next block's panels.  For small batches Q is accumulated forwards on a second side stream,
+    the next block's panels, and Q is accumulated forwards on a second side stream,
     Q <- Q (I - V T V^T) per finished block (1.5x the flops of the backward accumulation over
-    shrinking windows, but off the critical path), so that Q is ready when the last panel is."""
+    shrinking windows, but off the critical path), so that Q is ready when the last panel is.
+    The side-stream products run on a capped number of CTAs (_background_ctas) so that the panel
+    kernel always finds free SMs.  The choice of path depends on the order and on whether the batch
+    leaves SMs free at all (more than ~100 matrices do not), not otherwise on the batch: a matrix gets
+    the same bits whether it is factored alone, in a shard or in the full class."""
     B, n, _ = X.shape
     if (not X.is_cuda) or n > MAX_ORDER or n < 2:
         return torch.linalg.qr(X).Q
@@ -127,8 +143,9 @@ def householder_q(X, tensor_cores=True):
     T = torch.empty(B, npan, PANEL, PANEL, dtype=torch.float32, device=X.device)
     blocks = []                                           # (J0, wo, T_big, planes of V)
     split = _gemm.split
-    lookahead = tc and LOOKAHEAD and n > 2 * OUTER
-    forward_q = lookahead and B <= FORWARD_Q_MAX_BATCH
+    side_ctas = _background_ctas(X.device, B) if tc else 0
+    lookahead = tc and LOOKAHEAD and n > 2 * OUTER and side_ctas > 0
+    forward_q = lookahead and FORWARD_Q
     keep = []                                             # tensors used on side streams stay alive until the join
     with torch.cuda.device(X.device):
         main = torch.cuda.current_stream(X.device)
@@ -178,15 +195,16 @@ def householder_q(X, tensor_cores=True):
                 if t > nxt:
                     rest_stream.wait_event(y_ready)
                     with torch.cuda.stream(rest_stream):
-                        keep.append(_apply_block(Yp, Pv, X[:, J0:, J0 + wo + nxt:], Xp.window(J0, J0 + wo + nxt, m, t - nxt)))
+                        keep.append(_apply_block(Yp, Pv, X[:, J0:, J0 + wo + nxt:], Xp.window(J0, J0 + wo + nxt, m, t - nxt), side_ctas))
                         rest_done = torch.cuda.Event()
                         rest_done.record(rest_stream)
             if forward_q:                                 # Q[:, :, J0:] <- Q[:, :, J0:] - (Q[:, :, J0:] V) Y^T
                 q_stream.wait_event(y_ready)
                 with torch.cuda.stream(q_stream):
                     Qw = Qp.window(0, J0, n, m)
-                    _, Wp = _gemm.matmul(Qw, Pv, want_float=False, want_planes=True)
-                    _gemm.matmul(Wp, Yp, trans_b=True, alpha=-1.0, beta=1.0, C=Q[:, :, J0:], out=Q[:, :, J0:], out_planes=Qw)
+                    _, Wp = _gemm.matmul(Qw, Pv, want_float=False, want_planes=True, max_ctas=side_ctas)
+                    _gemm.matmul(Wp, Yp, trans_b=True, alpha=-1.0, beta=1.0, C=Q[:, :, J0:], out=Q[:, :, J0:], out_planes=Qw,
+                                 max_ctas=side_ctas)
                     keep.append(Wp)
         if lookahead:
             main.wait_stream(rest_stream)

@@ -48,7 +48,8 @@ class GemmDesc(ct.Structure):
                 ("aq_codes", ct.c_void_p), ("aq_absmax", ct.c_void_p), ("aq_diag", ct.c_void_p), ("aq_slots", ct.c_void_p),
                 ("aq_stride_codes", ct.c_longlong), ("aq_stride_absmax", ct.c_longlong), ("aq_stride_diag", ct.c_longlong),
                 ("bq_codes", ct.c_void_p), ("bq_absmax", ct.c_void_p), ("bq_diag", ct.c_void_p), ("bq_slots", ct.c_void_p),
-                ("bq_stride_codes", ct.c_longlong), ("bq_stride_absmax", ct.c_longlong), ("bq_stride_diag", ct.c_longlong)]
+                ("bq_stride_codes", ct.c_longlong), ("bq_stride_absmax", ct.c_longlong), ("bq_stride_diag", ct.c_longlong),
+                ("max_ctas", ct.c_int)]
 
 
 def library_path() -> Path:

@@ -49,3 +49,27 @@ def test_rank_deficient_input_stays_orthonormal(native_lib):
     X = G @ G.transpose(1, 2)                      # rank 40
     X[:, :, 5] = 0.0                               # an exactly zero column
     check(X)
+
+
+@pytest.mark.parametrize("n,batch", [(768, 3), (1200, 2), (400, 5)])
+def test_lookahead_orchestration_gives_the_same_q(native_lib, n, batch):
+    """The optional orchestration (far update split into the next block's columns and a remainder on
+    a side stream, Q accumulated forwards on a second one, side products on a capped grid) computes
+    the same factorisation in another order of operations: Q agrees to rounding, stays orthonormal,
+    and the device status stays clean."""
+    from optimizers import _qr
+    g = torch.Generator(device="cuda").manual_seed(n)
+    X = torch.randn(batch, n, n, device="cuda", generator=g)
+    base = _qr.householder_q(X.clone())
+    old = (_qr.LOOKAHEAD, _qr.FORWARD_Q)
+    try:
+        for forward in (False, True):
+            _qr.LOOKAHEAD, _qr.FORWARD_Q = True, forward
+            Q = _qr.householder_q(X.clone())
+            torch.cuda.synchronize()
+            assert native_lib.qt_device_error(1) == 0
+            assert float((Q - base).norm() / base.norm()) < 1e-5
+            eye = torch.eye(n, device="cuda")
+            assert float((Q.transpose(1, 2) @ Q - eye).abs().max()) < 1e-4
+    finally:
+        _qr.LOOKAHEAD, _qr.FORWARD_Q = old
