@@ -470,6 +470,15 @@ int qt_adamw_tail(const long long *p_ptrs, const long long *d_ptrs, const long l
                   int chunk_elems, const float *scalars, float beta1, float beta2, float one_minus_beta1,
                   float one_minus_beta2, float eps, void *stream);
 
+/*
+ * out[b][j] = sum_i A[b][i][j] * B[b][i][j] for `batch` pairs of row-major fp32 matrices (rows x cols,
+ * row pitch ld, matrix stride `stride`, both operands alike): the Rayleigh quotients diag(V^T L V) of
+ * the eigenbasis refresh (qtensor/utils.py:158) from L V and V.  The order of summation depends on
+ * rows and cols only, never on the batch.  Additive.
+ */
+int qt_column_dot(const float *A, const float *B, long long ld, long long stride, int rows, int cols, int batch,
+                  float *out, long long stride_out, void *stream);
+
 /* Sticky device-side error word (QT_OK or QT_ERR_TIMEOUT); synchronises the device.
  * clear != 0 resets it.  Additive; the reference has no device-side waits. */
 int qt_device_error(int clear);

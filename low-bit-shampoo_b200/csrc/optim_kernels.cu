@@ -70,7 +70,57 @@ int launch_adamw_tail(const long long *p_ptrs, const long long *d_ptrs, const lo
     return check_launch();
 }
 
+// Column-wise dot products of two batches of row-major matrices: out[b][j] = sum_i A[b][i][j] B[b][i][j]
+// - the Rayleigh quotients diag(V^T (L V)) of the eigenbasis refresh (qtensor/utils.py:158 forms the
+// whole product V^T L V and takes its diagonal).  One CTA per (32 columns, matrix): thread (ty, tx)
+// walks rows ty, ty+32, .. of column tx with four accumulators, then the 32 partial sums of a column
+// are added in a fixed tree.  The summation order depends on the matrix shape only, never on the
+// batch: a matrix gets the same bits alone, in a shard or in the full class (a library reduction
+// over the same data picks its launch configuration - and with it the order - from the batch size).
+__global__ void __launch_bounds__(1024)
+k_column_dot(const float *__restrict__ Abase, const float *__restrict__ Bbase, long long ld, long long stride,
+             int rows, int cols, float *__restrict__ out, long long stride_out) {
+    __shared__ float part[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int j = blockIdx.x * 32 + tx;
+    const float *A = Abase + (long long)blockIdx.y * stride, *B = Bbase + (long long)blockIdx.y * stride;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (j < cols) {
+        int k = 0;
+        for (int i = ty; i < rows; i += 32, ++k)
+            acc[k & 3] = fmaf(__ldg(A + (long long)i * ld + j), __ldg(B + (long long)i * ld + j), acc[k & 3]);
+    }
+    part[ty][tx] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    __syncthreads();
+    if (ty == 0 && j < cols) {
+        float s[32];
+#pragma unroll
+        for (int q = 0; q < 32; ++q) s[q] = part[q][tx];
+#pragma unroll
+        for (int w = 16; w > 0; w >>= 1)
+#pragma unroll
+            for (int q = 0; q < w; ++q) s[q] += s[q + w];
+        out[(long long)blockIdx.y * stride_out + j] = s[0];
+    }
+}
+
+int launch_column_dot(const float *A, const float *B, long long ld, long long stride, int rows, int cols, int batch,
+                      float *out, long long stride_out, cudaStream_t s) {
+    if (rows < 0 || cols < 0 || batch < 0 || batch > 65535 || ld < cols) return record(QT_ERR_ARG);
+    if (cols == 0 || batch == 0) return record(QT_OK);
+    if (!A || !B || !out) return record(QT_ERR_ARG);
+    dim3 grid((cols + 31) / 32, batch);
+    k_column_dot<<<grid, 1024, 0, s>>>(A, B, ld, stride, rows, cols, out, stride_out);
+    count_launch(1);
+    return check_launch();
+}
+
 }  // namespace qt
+
+extern "C" int qt_column_dot(const float *A, const float *B, long long ld, long long stride, int rows, int cols, int batch,
+                             float *out, long long stride_out, void *stream) {
+    return qt::launch_column_dot(A, B, ld, stride, rows, cols, batch, out, stride_out, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int qt_adamw_tail(const long long *p_ptrs, const long long *d_ptrs, const long long *m_ptrs, const long long *v_ptrs,
                              const long long *numels, const int *chunk_tensor, const int *chunk_index, int num_chunks,

@@ -338,8 +338,22 @@ def op_subspace_step(L, Vt):
     quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
     V = householder_q(mm(L, Vt, trans_b=True).f32, tensor_cores=_tc(L.f32))
     LV = mm(L, Mat(V, bound=_UNIT_BOUND)).f32
-    eigs = (LV * V).sum(dim=1)
-    return V, eigs
+    return V, column_dot(LV, V)
+
+
+def column_dot(A, B):
+    """out[b, j] = sum_i A[b, i, j] B[b, i, j] with an order of summation that depends on the matrix
+    shape only (qt_column_dot); plain torch off CUDA."""
+    if not (A.is_cuda and F.lib is not None and A.dtype == torch.float32 and B.dtype == torch.float32):
+        return (A * B).sum(dim=1)
+    A, B = A.contiguous(), B.contiguous()
+    b, r, c = A.shape
+    out = torch.empty(b, c, dtype=torch.float32, device=A.device)
+    with torch.cuda.device(A.device):
+        rc = F.lib.qt_column_dot(ct.c_void_p(A.data_ptr()), ct.c_void_p(B.data_ptr()), c, r * c, r, c, b,
+                                 ct.c_void_p(out.data_ptr()), c, F._stream(A))
+    F._check(rc, "column_dot")
+    return out
 
 
 def op_apply(P0, G, P1):

@@ -322,3 +322,21 @@ def test_cta_pair_product_equals_single_cta_product(native_lib, trans_a, trans_b
     assert bool((guard[:, M:, :] == 7.0).all()) and bool((guard[:, :, N:] == 7.0).all())
     ref = 0.75 * ((A.transpose(1, 2) if trans_a else A).double() @ (B.transpose(1, 2) if trans_b else B).double()) - 1.25 * C.double()
     assert rel(out[512][0], ref) < 1e-5, rel(out[512][0], ref)
+
+
+def test_column_dot_is_accurate_and_independent_of_the_batch(native_lib):
+    """Rayleigh quotients diag(V^T (L V)) through qt_column_dot: equal to a float64 evaluation to fp32
+    rounding, and a matrix gets the same bits in a batch of 62 as in a batch of 8 (torch's own
+    reduction over dim 1 does not: its launch configuration, and with it the order of summation,
+    follows the batch size - which made sharded and single-GPU runs drift apart)."""
+    from optimizers import _engine as E
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for n, big, small in ((1200, 62, 8), (768, 20, 1), (100, 7, 2), (50, 3, 1)):
+        A = torch.randn(big, n, n, device="cuda", generator=g)
+        B = torch.randn(big, n, n, device="cuda", generator=g)
+        full = E.column_dot(A, B)
+        assert device_ok(native_lib)
+        ref = (A.double() * B.double()).sum(dim=1)
+        assert float((full.double() - ref).abs().max() / ref.abs().max()) < 1e-6
+        part = E.column_dot(A[:small].contiguous(), B[:small].contiguous())
+        assert torch.equal(full[:small], part)
