@@ -756,7 +756,7 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="kernel sweep of the fused 4-bit statistics update and the inverse 4th root over orders 128..8192")
     ap.add_argument("--sweep-orders", default="128,512,1200,2048,4096,8192")
-    ap.add_argument("--profile-case", default=None, choices=["quant", "gemm", "step"],
+    ap.add_argument("--profile-case", default=None, choices=["quant", "gemm", "step", "panel"],
                     help="run only one small kernel case (for an ncu capture) and print its rates")
     args = ap.parse_args()
     if args.impl != "reference":
@@ -795,6 +795,24 @@ def main():
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
         print(json.dumps({"case": "one eager ShampooAdamW.step(), ViT-B/32, T1=T2=1", "ms": e0.elapsed_time(e1)}))
+        return
+    if args.profile_case == "panel":
+        # four launches of the QR panel kernel (8 matrices of order 1200: panels of 96 and of 1008 rows)
+        import torch
+        from qtensor.cextension import get_lib
+        lib = get_lib()
+        n, count = 1200, 8
+        A = torch.randn(count, n, n, device="cuda")
+        V = torch.zeros_like(A)
+        T = torch.zeros(count, 32, 32, device="cuda")
+        p = lambda t: ct.c_void_p(t.data_ptr())
+        st = ct.c_void_p(torch.cuda.current_stream().cuda_stream)
+        times = {}
+        for j0 in (1104, 192):
+            fn = lambda: lib.qt_householder_panel_fused(p(A), n * n, n, count, j0, 32, p(V), n * n, p(T), 1024, 0, None,
+                                                        min(n, (j0 // 128) * 128 + 128), st)
+            times[f"rows_{n - j0}_us"] = _time_cuda(torch, fn, 1, 2) * 1e3
+        print(json.dumps({"case": "k_householder_panel, 8 x 1200^2, 32-column panels", **times}))
         return
     if args.profile_case == "gemm":
         import torch
