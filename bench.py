@@ -622,8 +622,9 @@ def run_ours(args):
     # The loop is the one a training script would write around optimizer.step(): the gradients of
     # step i+1 are uploaded on a copy stream into the second of two device buffers while step i
     # computes (all K uploads lie inside the timed region; the first one is not overlapped with
-    # anything), p.grad is pointed at the buffer that just arrived, and a scalar is read back
-    # after every step, which also orders the reuse of the buffers.
+    # anything), p.grad is pointed at the buffer that just arrived, and every step's scalar is
+    # copied to pinned host memory and read by the host one step later (all K reads inside the
+    # timed region too); events order the reuse of the buffers.
     consumed = opt.consumed_params()
     idx = [k for k, p in enumerate(params) if p in consumed]
     host = [torch.empty(grads[k].shape, dtype=grads[k].dtype).pin_memory() for k in idx]
@@ -643,19 +644,36 @@ def run_ours(args):
 
     barrier()
     copy_stream.wait_stream(torch.cuda.current_stream())
+    main = torch.cuda.current_stream()
+    consumed = [torch.cuda.Event(), torch.cuda.Event()]           # step i has finished with gradient buffer i & 1
+    back_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+    back_done = [torch.cuda.Event(), torch.cuda.Event()]
+    backs = []
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
     upload(0)
     for i in range(args.steps):
         if i + 1 < args.steps:
-            upload((i + 1) & 1)                                   # its last reader (step i-1) finished before the read-back below
-        torch.cuda.current_stream().wait_event(arrived[i & 1])
+            if i >= 1:
+                copy_stream.wait_event(consumed[(i + 1) & 1])      # its last reader was step i-1
+            upload((i + 1) & 1)
+        main.wait_event(arrived[i & 1])
         for k, b in zip(idx, bufs[i & 1]):
             params[k].grad = b
         opt.step()
-        back = float(params[-1].detach().float().sum().cpu())
+        consumed[i & 1].record(main)
+        # the step's scalar goes to pinned host memory asynchronously and is read one step later,
+        # so the host enqueues step i+1 while step i runs (a logging loop, not a blocking read)
+        back_host[i & 1].copy_(params[-1].detach().float().sum(), non_blocking=True)
+        back_done[i & 1].record(main)
+        if i >= 1:
+            back_done[(i - 1) & 1].synchronize()
+            backs.append(float(back_host[(i - 1) & 1]))
+    back_done[(args.steps - 1) & 1].synchronize()
+    backs.append(float(back_host[(args.steps - 1) & 1]))
     e3.record()
     barrier()
+    assert len(backs) == args.steps
     for k in idx:
         params[k].grad = user_grads[k]
     e2e_ms = max_over_ranks(e2.elapsed_time(e3)) / args.steps
@@ -725,7 +743,8 @@ def run_ours(args):
             "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": h2d_total, "h2d_bytes_per_step_rank_max": h2d_max,
                     "d2h_bytes_per_step": 4 * world,
                     "loop": "gradients of step i+1 uploaded from pinned host memory on a copy stream while step i computes "
-                            "(two device buffers, p.grad re-pointed every step); every upload and a 4-byte read-back per step inside the timed region"},
+                            "(two device buffers, p.grad re-pointed every step); each step's 4-byte result copied to pinned host memory and read one step later; "
+                            "every upload and every read-back inside the timed region"},
             "gpu_launches": int(launches),
             "steady_state_step": {"value": steady_ms, "unit": "ms/step",
                                   "what": "same optimizer with no interval firing (apply + grafting + AdamW tail only)"},
