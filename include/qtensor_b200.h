@@ -191,6 +191,11 @@ int qt_householder_panel_fused(float *A, long long strideA, int order, int count
                                float *V, long long strideV, float *T, long long strideT,
                                int prev_width, const float *Tprev, int block_end, void *stream);
 
+/* Measurement / test hook: 0 (default) factors panels of more than 640 rows with the kernel that
+ * gives a warp two columns (16 warps, the whole panel in registers) and shorter ones with one
+ * column per warp (32 warps); 1 uses one column per warp at every height.  Additive. */
+void qt_panel_force_form(int form);
+
 /*
  * Triangular factor T (width x width, width <= 128) of a block of up to four consecutive panels,
  * H_1 .. H_width = I - Vo T Vo^T, from the panels' factors (Tp + m*strideTp: consecutive 32 x 32

@@ -161,4 +161,6 @@ int qt_householder_panel_fused(float *A, long long strideA, int order, int count
                                     static_cast<cudaStream_t>(stream), prev_width, Tprev, block_end);
 }
 
+void qt_panel_force_form(int form) { set_panel_pairs(form == 1 ? 0 : 1); }
+
 }  // extern "C"

@@ -63,6 +63,7 @@ int launch_state_exponents(const float *absmax, long long stride_absmax, int n_a
                            int n_diag, const int *slots, int count, int target, int *exp_out, cudaStream_t stream);
 int launch_selftest_division(unsigned long long seed, unsigned long long pairs, unsigned long long *mismatches_dev,
                              cudaStream_t stream);
+void set_panel_pairs(int on);
 int launch_householder_panel(float *A, long long strideA, int n, int count, int j0, int w,
                              float *V, long long strideV, float *T, long long strideT, cudaStream_t stream,
                              int prev_w = 0, const float *Tprev = nullptr, int block_end = 0);

@@ -21,7 +21,7 @@ LEGACY_SYMBOLS = tuple(
 )
 EXTRA_SYMBOLS = (
     "qt_version", "qt_launch_count", "qt_note_graph_replay", "qt_last_error", "qt_error_string", "qt_set_stream",
-    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_dequantize_planes", "qt_householder_panel", "qt_merge_t", "qt_selftest_division", "qt_split_bf16", "qt_split_bf16_rows", "qt_gemm_bf16x3", "qt_split_bf16_3", "qt_gemm_bf16x6", "qt_gemm_bf16x3_q4", "qt_gemm_bf16x6_q4", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error", "qt_adamw_tail", "qt_selftest_wait_timeout", "qt_gemm_ex", "qt_gemm_force_tile", "qt_column_dot", "qt_power_iter",
+    "qt_quantize_blockwise", "qt_dequantize_blockwise", "qt_dequantize_planes", "qt_householder_panel", "qt_merge_t", "qt_selftest_division", "qt_split_bf16", "qt_split_bf16_rows", "qt_gemm_bf16x3", "qt_split_bf16_3", "qt_gemm_bf16x6", "qt_gemm_bf16x3_q4", "qt_gemm_bf16x6_q4", "qt_matmul_f32", "qt_matmul_f32_scratch_bytes", "qt_matmul_f32_static", "qt_device_error", "qt_adamw_tail", "qt_selftest_wait_timeout", "qt_gemm_ex", "qt_gemm_force_tile", "qt_panel_force_form", "qt_column_dot", "qt_power_iter",
     "qt_inverse_root_newton", "qt_inverse_root_newton_workspace_bytes", "qt_split_f16", "qt_dequantize_planes_f16", "qt_householder_panel_fused", "qt_state_exponents",
 )
 
@@ -122,6 +122,8 @@ def _declare(lib):
     lib.qt_householder_panel_fused.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, i64, i32, vp, i32, vp]
     lib.qt_column_dot.restype = i32
     lib.qt_column_dot.argtypes = [vp, vp, i64, i64, i32, i32, i32, vp, i64, vp]
+    lib.qt_panel_force_form.restype = None
+    lib.qt_panel_force_form.argtypes = [i32]
     lib.qt_gemm_force_tile.restype = None
     lib.qt_gemm_force_tile.argtypes = [i32]
     lib.qt_power_iter.restype = i32

@@ -73,3 +73,22 @@ def test_lookahead_orchestration_gives_the_same_q(native_lib, n, batch):
             assert float((Q.transpose(1, 2) @ Q - eye).abs().max()) < 1e-4
     finally:
         _qr.LOOKAHEAD, _qr.FORWARD_Q = old
+
+
+@pytest.mark.parametrize("n", [768, 1200])
+def test_both_tall_panel_kernels_agree(native_lib, n):
+    """Panels of more than 640 rows are factored with two columns per warp by default and with one
+    column per warp on request: same conventions, Q equal to rounding."""
+    from optimizers import _qr
+    g = torch.Generator(device="cuda").manual_seed(3 * n)
+    X = torch.randn(2, n, n, device="cuda", generator=g)
+    Q0 = _qr.householder_q(X.clone())
+    try:
+        native_lib.qt_panel_force_form(1)
+        Q1 = _qr.householder_q(X.clone())
+    finally:
+        native_lib.qt_panel_force_form(0)
+    torch.cuda.synchronize()
+    assert native_lib.qt_device_error(1) == 0
+    assert float((Q0 - Q1).norm() / Q1.norm()) < 1e-5
+    check(X)
