@@ -338,7 +338,7 @@ class _ShampooBase(optim.Optimizer):
         # captured graphs, pointer tables and exchange plans refer to the state that was just replaced
         self._graph_state = None
         self._plans = {}
-        for name in ("_tail_cache", "_scalar_ring", "_tail_scalars", "_pending_exchange"):
+        for name in ("_tail_cache", "_scalar_ring", "_tail_scalars", "_pending_exchange", "_stable_direction_ptrs"):
             self.__dict__.pop(name, None)
         self._needs_eager = True                           # the next step rebuilds them eagerly
         for group in self.param_groups:
@@ -493,9 +493,13 @@ class _ShampooBase(optim.Optimizer):
             return
         plan, shipped, dev = ctx
         got = plan.views(dev, torch.float32)
+        stable = set()
         for k, p in shipped:
             if self.state[p]['owner'] != self._rank:
                 directions[k] = got[k].view(p.shape).to(p.grad.dtype)
+                if directions[k].data_ptr() == got[k].data_ptr():
+                    stable.add(got[k].data_ptr())             # lives in the persistent receive buffer
+        self._stable_direction_ptrs = stable
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -563,7 +567,14 @@ class _ShampooBase(optim.Optimizer):
         active = tuple(self.state[p]['preconditioner'].is_active() for p in params)
         key = (fires_stat, fires_root, all(active), any(active), step >= group['start_prec_step'])
         self._stage_scalars(group, step, gs["scalars"])
-        torch._foreach_copy_(gs["grads"], [p.grad for p in params])
+        # Gradients are staged into the buffers the graphs read.  In a sharded run the gradient of a
+        # parameter another rank owns is not read once that parameter is preconditioned (its direction
+        # arrives through the exchange), so it is not copied either.
+        shipped_now = step >= group['start_prec_step']
+        need = [k for k, p in enumerate(params)
+                if not (self._world > 1 and shipped_now and self.state[p].get('owner', -1) not in (-1, self._rank)
+                        and (fires_root or self.state[p]['preconditioner'].is_active()))]
+        torch._foreach_copy_([gs["grads"][k] for k in need], [params[k].grad for k in need])
         user_grads = [p.grad for p in params]
         for p, g in zip(params, gs["grads"]):
             p.grad = g
@@ -731,7 +742,15 @@ class ShampooAdamWBase(_ShampooBase):
         dev = params[0].device
         cache = self.__dict__.setdefault("_tail_cache", {})
         key = tuple(p.data_ptr() for p in params) + tuple(self.state[p]['exp_avg'].data_ptr() for p in params)
-        tab = cache.get(("static", key))
+        # directions that already sit at a persistent address (views of the exchange's receive buffer)
+        # are read where they are; the others are gathered into one persistent buffer
+        stable = self.__dict__.get("_stable_direction_ptrs") or ()
+        direct = tuple(d.data_ptr() if d.data_ptr() in stable else 0 for d in directions)
+        tab = cache.get(("static", key, direct))
+        if tab is None and any(direct) and torch.cuda.is_current_stream_capturing():
+            # no table for this pattern yet and none can be uploaded while a graph is captured: gather everything
+            direct = tuple(0 for _ in directions)
+            tab = cache.get(("static", key, direct))
         if tab is None:
             numels = [p.numel() for p in params]
             ct_, ci_ = [], []
@@ -742,17 +761,20 @@ class ShampooAdamWBase(_ShampooBase):
             i64 = lambda xs: torch.tensor(xs, dtype=torch.int64, device=dev)
             # directions are gathered into one persistent buffer (their own tensors move from step to
             # step), so every table is built once - nothing is uploaded while a graph is captured
-            flat = torch.empty(sum((n + 3) // 4 * 4 for n in numels), dtype=torch.float32, device=dev)
-            views, off = [], 0
-            for p_, n in zip(params, numels):
-                views.append(flat[off: off + n].view(p_.shape))
-                off += (n + 3) // 4 * 4
-            tab = cache[("static", key)] = dict(
+            copy_idx = [k for k, ptr in enumerate(direct) if not ptr]
+            flat = torch.empty(max(4, sum((numels[k] + 3) // 4 * 4 for k in copy_idx)), dtype=torch.float32, device=dev)
+            views, dptrs, off = [], list(direct), 0
+            for k in copy_idx:
+                views.append(flat[off: off + numels[k]].view(params[k].shape))
+                dptrs[k] = views[-1].data_ptr()
+                off += (numels[k] + 3) // 4 * 4
+            tab = cache[("static", key, direct)] = dict(
                 p=i64([p.data_ptr() for p in params]), m=i64([self.state[p]['exp_avg'].data_ptr() for p in params]),
                 v=i64([self.state[p]['exp_avg_sq'].data_ptr() for p in params]), n=i64(numels),
-                d=i64([v_.data_ptr() for v_ in views]), dviews=views, dflat=flat,
+                d=i64(dptrs), dviews=views, dflat=flat, copy_idx=copy_idx,
                 ct=torch.tensor(ct_, dtype=torch.int32, device=dev), ci=torch.tensor(ci_, dtype=torch.int32, device=dev))
-        torch._foreach_copy_(tab["dviews"], list(directions))
+        if tab["copy_idx"]:
+            torch._foreach_copy_(tab["dviews"], [directions[k] for k in tab["copy_idx"]])
         beta1, beta2 = group['betas']
         vp = lambda t: ct.c_void_p(t.data_ptr())
         with torch.cuda.device(dev):
