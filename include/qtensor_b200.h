@@ -378,11 +378,12 @@ int qt_split_f16(const float *X, long long ldx, long long strideX, int rows, int
                  float *amax, int compute_amax, const int *exp_in, int target_or_exp0, int *exp_out,
                  void *hi, void *lo, long long ldp, long long strideP, void *stream);
 
-/* Measurement / test hook for the tile configuration of two-plane products.  -1 (default) and
- * 128: single CTAs on 128 x 128 tiles; 256: single CTAs on 128 x 256 tiles; 512: CTA pairs
- * (tcgen05 cta_group::2: two CTAs of a cluster on one 256 x 128 tile, each staging its rows of A
- * and half of B) wherever they are possible (plain epilogue, more than 128 rows).  The results of
- * 128 and 512 are equal bit for bit.  Additive; no counterpart in the reference. */
+/* Measurement / test hook for the tile configuration of two-plane products.  -1 (default): 128 x 192
+ * tiles for plain products wider than 128 columns with K >= 256, else 128 x 128; 128, 192, 256: single
+ * CTAs with that tile width wherever the variant exists; 512: CTA pairs (tcgen05 cta_group::2: two CTAs
+ * of a cluster on one 256 x 128 tile, each staging its rows of A and half of B) wherever they are
+ * possible (plain epilogue, more than 128 rows).  All of them give the same bits.  Additive; no
+ * counterpart in the reference. */
 void qt_gemm_force_tile(int bn);
 
 /*

@@ -47,8 +47,7 @@ static constexpr unsigned WAIT_LIMIT = 1u << 18;
 //                      cores of the pair exchange the B halves between themselves.  25 % less operand
 //                      traffic from L2 and from shared memory per flop.
 template <int NP, int BN_, int EC, bool CONV = false, bool PAIR = false> struct TileCfg {
-    static constexpr int B_TILES = BN_ / 128;
-    static constexpr int B_PLANE_BYTES = PAIR ? PLANE_TILE_BYTES / 2 : B_TILES * PLANE_TILE_BYTES;
+    static constexpr int B_PLANE_BYTES = PAIR ? PLANE_TILE_BYTES / 2 : BN_ * BK * 2;   // BN_ rows of 64 k (or BN_ / 64 chunks of 64 x 64)
     static constexpr int STAGE_BYTES = NP * (PLANE_TILE_BYTES + B_PLANE_BYTES);
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
     // Epilogue warp e reads TMEM lanes 32 (e & 3) .. +31 and EC accumulator columns starting at
@@ -1369,10 +1368,11 @@ template <int NP, int BN_, int EC> static void fill_kernels(GemmKern (&t)[2][2][
     t[1][0][0] = k_gemm_bf16x3<true, false, NP, BN_, EC, false>;  t[1][0][1] = k_gemm_bf16x3<true, false, NP, BN_, EC, true>;
     t[1][1][0] = k_gemm_bf16x3<true, true, NP, BN_, EC, false>;   t[1][1][1] = k_gemm_bf16x3<true, true, NP, BN_, EC, true>;
 }
-static GemmKern g_kernels[5][2][2][2];
-static const int g_cfg_threads[5] = {TileCfg<2, 128, 64>::THREADS, TileCfg<2, 256, 128>::THREADS, TileCfg<3, 128, 128>::THREADS,
-                                     TileCfg<2, 128, 64, true>::THREADS, TileCfg<2, 128, 64, false, true>::THREADS};
-static const int g_cfg_bn[5] = {128, 256, 128, 128, 128};
+static GemmKern g_kernels[6][2][2][2];
+static const int g_cfg_threads[6] = {TileCfg<2, 128, 64>::THREADS, TileCfg<2, 256, 128>::THREADS, TileCfg<3, 128, 128>::THREADS,
+                                     TileCfg<2, 128, 64, true>::THREADS, TileCfg<2, 128, 64, false, true>::THREADS,
+                                     TileCfg<2, 192, 96>::THREADS};
+static const int g_cfg_bn[6] = {128, 256, 128, 128, 128, 192};
 
 static bool prepare_kernels() {
     static bool filled = false;
@@ -1389,12 +1389,18 @@ static bool prepare_kernels() {
         g_kernels[4][0][1][0] = k_gemm_bf16x3<false, true, 2, 128, 64, false, false, true>;
         g_kernels[4][1][0][0] = k_gemm_bf16x3<true, false, 2, 128, 64, false, false, true>;
         g_kernels[4][1][1][0] = k_gemm_bf16x3<true, true, 2, 128, 64, false, false, true>;
+        // configuration 5: 128 x 192 tiles, eight epilogue warps of 96 columns, plain epilogue only
+        for (int i = 0; i < 8; ++i) g_kernels[5][(i >> 2) & 1][(i >> 1) & 1][i & 1] = nullptr;
+        g_kernels[5][0][0][0] = k_gemm_bf16x3<false, false, 2, 192, 96>;
+        g_kernels[5][0][1][0] = k_gemm_bf16x3<false, true, 2, 192, 96>;
+        g_kernels[5][1][0][0] = k_gemm_bf16x3<true, false, 2, 192, 96>;
+        g_kernels[5][1][1][0] = k_gemm_bf16x3<true, true, 2, 192, 96>;
         filled = true;
     }
     static PerDeviceOnce attr_done;                      // function attributes are per device
     const int dev = current_device();
     if (attr_done.pending(dev)) {
-        for (int i = 0; i < 40; ++i) {
+        for (int i = 0; i < 48; ++i) {
             GemmKern k = g_kernels[i / 8][(i >> 2) & 1][(i >> 1) & 1][i & 1];
             if (k && cudaFuncSetAttribute(reinterpret_cast<const void *>(k), cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
                 return false;
@@ -1404,8 +1410,9 @@ static bool prepare_kernels() {
     return true;
 }
 
-// Test hook: tile configuration of two-plane products.  -1: chosen by problem size; 128: single CTAs,
-// 128 x 128 tiles; 256: single CTAs, 128 x 256 tiles; 512: CTA pairs wherever they are possible.
+// Test hook: tile configuration of two-plane products.  -1: chosen by problem size (128 x 192 for
+// products wider than 128 columns with at least 256 k, else 128 x 128); 128 / 192 / 256: single CTAs
+// with that tile width; 512: CTA pairs wherever they are possible.
 static int g_force_bn = -1;
 
 // a.Ahi/Alo (+ Amid/Bmid for three planes: order hi, mid, lo).  With `qs` the result (and the C
@@ -1461,6 +1468,15 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     // stays selectable (qt_gemm_force_tile) for measurements.
     int cfg = np == 3 ? 2 : 0;
     if (np == 2 && a.N > 128 && g_force_bn == 256) cfg = 1;
+    // 128 x 192 tiles (eight epilogue warps of 96 columns, two operand stages, two accumulators): 17 % less
+    // operand traffic per flop than 128 x 128 and, unlike 128 x 256, the 96 partial sums per thread
+    // (nearly) fit the register budget.  Measured against 128 x 128: 125 x 768^3 371 -> 332 us,
+    // 62 x 1200^3 868 -> 748, 36 x (768 x 3072 x 768) 489 -> 402, 8 x 4096^3 3653 -> 2882; with two
+    // k-blocks only (1200 x 1200 x 128) it loses (169 -> 180), so short products stay on 128 x 128.
+    // Products whose epilogue reads C and writes both fp32 and planes stay on 128 x 128 as well (the wide
+    // epilogue is out of registers there: 600 x 1200 x 600 with all three 1.01 -> 1.10 ms per four launches).
+    const bool heavy_epilogue = a.C && a.beta != 0.0f && a.D && a.Dhi;
+    if (np == 2 && a.N > 128 && !qs && (g_force_bn == 192 || (g_force_bn == -1 && a.K >= 256 && !heavy_epilogue))) cfg = 5;
     if (qa || qb) cfg = 3;
     // CTA pairs (256-row bands) only on request: measured on B200 they are no faster than single
     // CTAs on 128 x 128 tiles (125 x 768^3: 372 vs 364 us; 8 x 4096^3: 3980 vs 3480 us) - halving

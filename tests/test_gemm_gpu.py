@@ -294,9 +294,10 @@ def test_operand_dequantized_inside_the_product(native_lib, n, other, diagreal):
 @pytest.mark.parametrize("M,N,K,b", [(256, 128, 64, 1), (768, 768, 768, 3), (1200, 1200, 768, 2), (1104, 672, 200, 2),
                                      (200, 72, 50, 5), (1000, 1008, 336, 2), (129, 16, 1200, 1)])
 def test_cta_pair_product_equals_single_cta_product(native_lib, trans_a, trans_b, M, N, K, b):
-    """The cta_group::2 kernel (two CTAs on one 256 x 128 tile, each staging half of B) against the
-    single-CTA kernel on the same planes: same accumulation chains, so the results are equal bit
-    for bit - fp32 output, plane output, C operand, ragged rows / columns / k, all operand majors."""
+    """The 128 x 192 tile and the cta_group::2 kernel (two CTAs on one 256 x 128 tile, each staging half
+    of B) against the 128 x 128 single-CTA kernel on the same planes: same accumulation chains, so the
+    results are equal bit for bit - fp32 output, plane output, C operand, ragged rows / columns / k,
+    all operand majors."""
     from optimizers import _gemm
     g = torch.Generator(device="cuda").manual_seed(M + 3 * N + 7 * K)
     A = torch.randn((b, K, M) if trans_a else (b, M, K), device="cuda", generator=g)
@@ -305,7 +306,7 @@ def test_cta_pair_product_equals_single_cta_product(native_lib, trans_a, trans_b
     Ap, Bp = _gemm.split(A), _gemm.split(B)
     out = {}
     try:
-        for tile in (128, 512):
+        for tile in (128, 192, 512):
             native_lib.qt_gemm_force_tile(tile)
             D, P = _gemm.matmul(Ap, Bp, trans_a=trans_a, trans_b=trans_b, alpha=0.75, beta=-1.25, C=C, want_planes=True,
                                 out_bound=4.0 * K)
@@ -316,8 +317,9 @@ def test_cta_pair_product_equals_single_cta_product(native_lib, trans_a, trans_b
             out[tile] = (D, valid(P.hi), valid(P.lo), guard)
     finally:
         native_lib.qt_gemm_force_tile(-1)
-    for x, y in zip(out[128], out[512]):
-        assert torch.equal(x, y)
+    for other in (192, 512):
+        for x, y in zip(out[128], out[other]):
+            assert torch.equal(x, y)
     guard = out[512][3]
     assert bool((guard[:, M:, :] == 7.0).all()) and bool((guard[:, :, N:] == 7.0).all())
     ref = 0.75 * ((A.transpose(1, 2) if trans_a else A).double() @ (B.transpose(1, 2) if trans_b else B).double()) - 1.25 * C.double()
