@@ -795,8 +795,12 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                     float *drow = p.D + (long long)bo * p.strideD + (long long)row * p.ldd + n0;
                     const long long po = (long long)bo * p.strideP + (long long)row * p.ldp + n0;
                     const long long to = (long long)b * p.strideP + (long long)row * p.ldp + n0;   // T is stored by matrix number
-                    // C is fetched one 16-column group ahead of its use
-                    float cnext[16];
+                    // C is fetched two 16-column groups ahead of its use (the two-plane tiles; one group
+                    // ahead where 128 partial sums leave no registers): a product with a short K and a C
+                    // operand is bound by this stream, and eight warps with one 64-byte request each in
+                    // flight keep an SM at half of its share of the HBM bandwidth
+                    constexpr int CPF = (EC <= 64 && !CONV) ? 2 : 1;
+                    float cnext[CPF][16];
                     auto fetch_c = [&](int q, float (&dst)[16]) {
                         if (!has_c || q >= valid) return;
                         if (q + 16 <= valid && wide_d) { ldg256f(crow + q, dst); ldg256f(crow + q + 8, dst + 8); }
@@ -805,7 +809,8 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                             for (int t = 0; t < 16; ++t) dst[t] = (q + t < valid) ? __ldg(crow + q + t) : 0.0f;
                         }
                     };
-                    fetch_c(0, cnext);
+                    fetch_c(0, cnext[0]);
+                    if constexpr (CPF == 2) fetch_c(16, cnext[1]);
 #pragma unroll
                     for (int q = 0; q < EC; q += 16) {
                         if (q >= valid) continue;
@@ -813,8 +818,8 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                         float o[16];
                         if (has_c) {
 #pragma unroll
-                            for (int t = 0; t < 16; ++t) o[t] = cnext[t];
-                            if (q + 16 < EC) fetch_c(q + 16, cnext);
+                            for (int t = 0; t < 16; ++t) o[t] = cnext[(q >> 4) % CPF][t];
+                            if (q + 16 * CPF < EC) fetch_c(q + 16 * CPF, cnext[(q >> 4) % CPF]);
 #pragma unroll
                             for (int t = 0; t < 16; ++t) o[t] = fmaf(p.beta, o[t], alpha_eff * sum[q + t]);
                         } else {
