@@ -25,11 +25,11 @@ OUTER = 128                 # columns per outer block (four panels): trailing up
 USE_TENSOR_CORES = True     # rank-128 far updates on the tcgen05 kernel (rank-32 ones inside a block: fused into the panel kernel)
 
 
-def _reflect(Vk, Tk, target, target_planes, transpose_t, Pv=None):
+def _reflect(Vk, Tk, target, target_planes, transpose_t, Pv=None, Pt=None):
     """target <- (I - Vk T' Vk^T) target with T' = T^T (transpose_t) or T, fp32 in place.
     With `target_planes` (the operand planes of `target`) everything runs on the tensor cores:
     Y = Vk T' and W = Vk^T target are produced directly as operand planes, then
-    target <- target - Y W with the planes of `target` kept in step.  `Pv`: planes of Vk."""
+    target <- target - Y W with the planes of `target` kept in step.  `Pv`, `Pt`: planes of Vk, Tk."""
     from optimizers import _gemm
     if target_planes is None:
         W = torch.bmm(Vk.transpose(1, 2), target)
@@ -38,7 +38,9 @@ def _reflect(Vk, Tk, target, target_planes, transpose_t, Pv=None):
         return
     if Pv is None:
         Pv = _gemm.split(Vk, bound=2.0)
-    _, Yp = _gemm.matmul(Pv, _gemm.split(Tk), trans_b=transpose_t, want_float=False, want_planes=True)
+    if Pt is None:
+        Pt = _gemm.split(Tk)
+    _, Yp = _gemm.matmul(Pv, Pt, trans_b=transpose_t, want_float=False, want_planes=True)
     _, Wp = _gemm.matmul(Pv, target_planes, trans_a=True, want_float=False, want_planes=True)
     _gemm.matmul(Yp, Wp, alpha=-1.0, beta=1.0, C=target, out=target, out_planes=target_planes)
 
@@ -175,15 +177,16 @@ def householder_q(X, tensor_cores=True):
             Vo = V[:, J0:, J0:J0 + wo]
             Pv = split(Vo, bound=2.0) if tc else None     # Householder vectors: entries <= 1; shared by the merge, the far update and the accumulation of Q
             Tb = _merge_t(Vo, T[:, J0 // PANEL:], widths, Pv)
-            blocks.append((J0, wo, Tb, Pv))
+            Pt = split(Tb) if tc else None                # planes of T: shared by the far update (as T^T) and the accumulation of Q
+            blocks.append((J0, wo, Tb, Pv, Pt))
             m, t = n - J0, n - J0 - wo
             if not lookahead:
                 if t > 0:
-                    _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True, Pv)
+                    _reflect(Vo, Tb, X[:, J0:, J0 + wo:], Xp.window(J0, J0 + wo, m, t) if tc else None, True, Pv, Pt)
                 continue
             if t == 0 and not forward_q:
                 continue
-            _, Yp = _gemm.matmul(Pv, split(Tb), trans_b=True, want_float=False, want_planes=True)     # Y = V T^T
+            _, Yp = _gemm.matmul(Pv, Pt, trans_b=True, want_float=False, want_planes=True)     # Y = V T^T
             keep += [Pv, Yp, Tb]
             y_ready = torch.cuda.Event()
             y_ready.record(main)
@@ -213,7 +216,7 @@ def householder_q(X, tensor_cores=True):
                 return Q
         Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
         Qp = split(Q, bound=2.0) if tc else None         # Q stays orthonormal: entries <= 1
-        for J0, wo, Tb, Pv in reversed(blocks):
+        for J0, wo, Tb, Pv, Pt in reversed(blocks):
             m = n - J0
-            _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False, Pv)
+            _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False, Pv, Pt)
     return Q
