@@ -8,6 +8,7 @@ accumulation  Q <- (I - V T V^T) Q  are batched products.  Sign conventions are 
 so Q agrees with torch.linalg.qr's up to rounding on full-rank input.
 """
 import ctypes as ct
+import warnings
 
 import torch
 
@@ -84,6 +85,7 @@ LOOKAHEAD = False           # far update split into the next block's columns (cr
 FORWARD_Q = True            # Q accumulated block by block beside the factorisation (with LOOKAHEAD), else backwards afterwards
 
 _SIDE_STREAMS = {}
+_WARNED_LARGE = False
 
 
 def _side_streams(device):
@@ -133,7 +135,14 @@ def householder_q(X, tensor_cores=True):
     leaves SMs free at all (more than ~100 matrices do not), not otherwise on the batch: a matrix gets
     the same bits whether it is factored alone, in a shard or in the full class."""
     B, n, _ = X.shape
-    if (not X.is_cuda) or n > MAX_ORDER or n < 2:
+    if X.is_cuda and n > MAX_ORDER:
+        global _WARNED_LARGE
+        if not _WARNED_LARGE:
+            _WARNED_LARGE = True
+            warnings.warn(f"householder_q: order {n} exceeds the panel kernel's {MAX_ORDER} rows (a panel must fit one SM's "
+                          "shared memory); using torch.linalg.qr for this order - per-matrix library QR, much slower")
+        return torch.linalg.qr(X).Q
+    if (not X.is_cuda) or n < 2:
         return torch.linalg.qr(X).Q
     F._require_lib(X)
     X = X.contiguous()

@@ -92,3 +92,14 @@ def test_both_tall_panel_kernels_agree(native_lib, n):
     assert native_lib.qt_device_error(1) == 0
     assert float((Q0 - Q1).norm() / Q1.norm()) < 1e-5
     check(X)
+
+
+def test_orders_beyond_the_panel_kernel_fall_back_with_a_warning(native_lib):
+    """A panel of more than 1216 rows does not fit one SM's shared memory: such orders go to
+    torch.linalg.qr, and say so once."""
+    from optimizers import _qr
+    _qr._WARNED_LARGE = False
+    X = torch.randn(1, _qr.MAX_ORDER + 16, _qr.MAX_ORDER + 16, device="cuda")
+    with pytest.warns(UserWarning, match="torch.linalg.qr"):
+        Q = _qr.householder_q(X.clone())
+    assert float((Q - torch.linalg.qr(X).Q).abs().max()) == 0.0
