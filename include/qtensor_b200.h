@@ -18,7 +18,7 @@
  *   - launches are asynchronous on the calling thread's current stream
  *     (qt_set_stream; the legacy default stream until it is called).
  *
- * Byte format (the judged one is the reference's CPU quantizer,
+ * Byte format (that of the reference's CPU quantizer,
  * qtensor/functional.py:526-746): element 2j of the flat row-major index stream is the
  * HIGH nibble of byte j; an all-zero block stores code index 0 and dequantizes to +0.0;
  * normalisation is an IEEE fp32 division; ties between two codes go to the lower one.
