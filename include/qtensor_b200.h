@@ -327,6 +327,8 @@ typedef struct qt_gemm_desc {
     int max_ctas;   /* > 0: at most this many CTAs (the kernel is persistent and otherwise takes every SM until
                      * it is done, so a latency-critical kernel launched beside it on another stream would wait for
                      * the whole product); 0: one CTA per SM */
+    int c_follows_d; /* != 0: the C operand of matrix b is entry d_slot[b] of its array, like the outputs
+                      * (C == D then updates selected entries of an array in place) */
 } qt_gemm_desc;
 int qt_gemm_ex(const qt_gemm_desc *desc, void *stream);
 

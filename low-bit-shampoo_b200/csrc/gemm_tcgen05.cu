@@ -91,6 +91,7 @@ struct GemmParams {
     const int *out_exp; int *out_exp_w; int out_exp0, out_rel;            // exponent of the plane output: given per entry, or
                                                                           // (out_rel) operand exponents + out_exp0; written to out_exp_w
     int kc;                                                               // k-blocks per accumulation chain (two-plane kernels)
+    int c_follows_d;                                                      // C of matrix b is entry d_slot[b] of its array (in-place updates of selected entries)
     // Operands taken straight from 4-bit state (CONV kernels; block size 64, square order qn):
     // codes == nullptr: the operand comes from its planes through TMA as usual.
     QOperand aq, bq;
@@ -791,7 +792,7 @@ k_gemm_bf16x3(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                     if (p.out_exp_w && tm == 0 && tn == 0 && seg == 0 && quad == 0 && lane == 0) p.out_exp_w[bo] = e_out;
                 }
                 if (row_ok && valid > 0) {
-                    const float *crow = p.C + (long long)b * p.strideC + (long long)row * p.ldc + n0;
+                    const float *crow = p.C + (long long)(p.c_follows_d ? bo : b) * p.strideC + (long long)row * p.ldc + n0;
                     float *drow = p.D + (long long)bo * p.strideD + (long long)row * p.ldd + n0;
                     const long long po = (long long)bo * p.strideP + (long long)row * p.ldp + n0;
                     const long long to = (long long)b * p.strideP + (long long)row * p.ldp + n0;   // T is stored by matrix number
@@ -1350,6 +1351,7 @@ struct GemmExtras {
     QOperand aq = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0}, bq = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
     const float *oq_code = nullptr;
     int max_ctas = 0;                                       // > 0: cap of the persistent grid (SMs left to kernels on other streams)
+    int c_follows_d = 0;                                    // C indexed through d_slot like the outputs
 };
 
 static inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -1515,7 +1517,7 @@ int launch_gemm_planes(const GemmArgs &a, const void *Amid, const void *Bmid, cu
     p.t_c0 = x.t_c0; p.t_c1 = x.t_c1; p.maxdev = x.maxdev;
     p.a_slot = x.a_slot; p.b_slot = x.b_slot; p.d_slot = x.d_slot; p.active = x.active;
     p.f16 = x.f16; p.a_exp = x.a_exp; p.b_exp = x.b_exp; p.ab_exp0 = x.ab_exp0;
-    p.out_exp = x.out_exp; p.out_exp_w = x.out_exp_w; p.out_exp0 = x.out_exp0; p.out_rel = x.out_rel; p.kc = x.kc;
+    p.out_exp = x.out_exp; p.out_exp_w = x.out_exp_w; p.out_exp0 = x.out_exp0; p.out_rel = x.out_rel; p.kc = x.kc; p.c_follows_d = x.c_follows_d;
     p.aq = x.aq; p.bq = x.bq; p.oq_code = x.oq_code;
     p.tiles_m = pair ? (a.M + 2 * BM - 1) / (2 * BM) : tiles_m; p.tiles_n = (a.N + bn - 1) / bn;
     p.q_in = nullptr; p.q_absmax_in = p.q_diag_in = nullptr; p.q_out = nullptr; p.q_absmax_out = p.q_diag_out = nullptr;
@@ -1816,7 +1818,7 @@ int qt_gemm_ex(const qt_gemm_desc *d, void *stream) {
     x.maxdev = d->maxdev; x.a_slot = d->a_slot; x.b_slot = d->b_slot; x.d_slot = d->d_slot; x.active = d->active;
     x.a_entries = d->a_entries; x.b_entries = d->b_entries;
     x.f16 = d->f16; x.a_exp = d->a_exp; x.b_exp = d->b_exp; x.ab_exp0 = d->ab_exp0;
-    x.out_exp = d->out_exp; x.out_exp_w = d->out_exp_w; x.out_exp0 = d->out_exp0; x.out_rel = d->out_rel; x.kc = d->kc; x.max_ctas = d->max_ctas;
+    x.out_exp = d->out_exp; x.out_exp_w = d->out_exp_w; x.out_exp0 = d->out_exp0; x.out_rel = d->out_rel; x.kc = d->kc; x.max_ctas = d->max_ctas; x.c_follows_d = d->c_follows_d;
     if (d->aq_codes) x.aq = QOperand{d->aq_codes, d->aq_absmax, d->aq_diag, d->aq_slots, d->aq_stride_codes, d->aq_stride_absmax,
                                      d->aq_stride_diag, d->M, (d->M + 63) / 64};
     if (d->bq_codes) x.bq = QOperand{d->bq_codes, d->bq_absmax, d->bq_diag, d->bq_slots, d->bq_stride_codes, d->bq_stride_absmax,

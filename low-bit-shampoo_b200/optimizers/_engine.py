@@ -333,6 +333,16 @@ def op_ema_gram(L, G, axis, w1, w2):
     return mm(Gm, Gm, trans_a=True, alpha=w2, beta=w1, C=L).f32
 
 
+def op_ema_gram_selected(L, sel, G, axis, w1, w2):
+    """op_ema_gram on the matrices L[sel[k]] with G[k], updated in place: the product reads its C
+    operand and writes its result through the slot list, so the selected matrices are neither
+    gathered into a temporary nor scattered back (sel: int32 device tensor)."""
+    P = Mat(G).planes
+    _gemm.gemm_ex(P, P, trans_a=(axis == 1), trans_b=(axis == 0), alpha=w2, beta=w1, C=L, D=L,
+                  d_slot=sel, c_follows_d=True, batch=G.shape[0])
+    return L
+
+
 def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
     quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
@@ -424,6 +434,8 @@ def _ema_update(L, grads_axes, w1, w2):
         Gs = torch.stack([grads_axes[k][0].float() for k in ks])
         if len(ks) == L.shape[0]:
             L = op_ema_gram(L, Gs, axis, w1, w2)
+        elif _tc(L) and L.is_contiguous():
+            L = op_ema_gram_selected(L, _index_tensor(ks, L.device, torch.int32), Gs, axis, w1, w2)
         else:
             sel = _index_tensor(ks, L.device)
             L[sel] = op_ema_gram(L[sel], Gs, axis, w1, w2)

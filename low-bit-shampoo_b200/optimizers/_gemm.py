@@ -297,7 +297,7 @@ def matmul_q4(A, B, code, out, trans_a=False, trans_b=False, alpha=1.0, beta=0.0
 
 def gemm_ex(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, D=None, P=None, T=None, t_c0=0.0, t_c1=0.0,
             maxdev=None, a_slot=None, b_slot=None, d_slot=None, active=None, batch=None,
-            out_exp=None, out_exp0=0, out_rel=0, out_exp_w=None, q=None, max_ctas=0):
+            out_exp=None, out_exp0=0, out_rel=0, out_exp_w=None, q=None, max_ctas=0, c_follows_d=False):
     """General product (qt_gemm_ex): A, B are Planes (possibly holding more entries than `batch` when slot
     arrays select among them); results go to the fp32 tensor D and / or the Planes P, optionally
     T = t_c0 * I + t_c1 * result (three bf16 planes, indexed by matrix number), or - with `q` - into
@@ -335,6 +335,7 @@ def gemm_ex(A, B, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, C=None, D=N
     d.t_c0, d.t_c1 = float(t_c0), float(t_c1)
     d.maxdev, d.a_slot, d.b_slot, d.d_slot, d.active = ip(maxdev), ip(a_slot), ip(b_slot), ip(d_slot), ip(active)
     d.max_ctas = int(max_ctas)
+    d.c_follows_d = 1 if c_follows_d else 0
     if A.f16 or B.f16:
         assert A.f16 and B.f16
         d.f16, d.kc = 1, CHAIN_K

@@ -49,7 +49,7 @@ class GemmDesc(ct.Structure):
                 ("aq_stride_codes", ct.c_longlong), ("aq_stride_absmax", ct.c_longlong), ("aq_stride_diag", ct.c_longlong),
                 ("bq_codes", ct.c_void_p), ("bq_absmax", ct.c_void_p), ("bq_diag", ct.c_void_p), ("bq_slots", ct.c_void_p),
                 ("bq_stride_codes", ct.c_longlong), ("bq_stride_absmax", ct.c_longlong), ("bq_stride_diag", ct.c_longlong),
-                ("max_ctas", ct.c_int)]
+                ("max_ctas", ct.c_int), ("c_follows_d", ct.c_int)]
 
 
 def library_path() -> Path:
