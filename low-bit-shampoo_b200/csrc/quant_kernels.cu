@@ -442,10 +442,20 @@ k_state_amax(const float *__restrict__ absmax_base, long long stride_absmax, int
              const int *__restrict__ slots, float *__restrict__ amax, int *__restrict__ exp_out = nullptr, int target = 0) {
     const int m = blockIdx.x;
     const long long src = slots ? (long long)slots[m] : (long long)m;
-    float v = 0.0f;
-    for (int i = threadIdx.x; i < n_absmax; i += blockDim.x) v = fmaxf(v, fabsf(absmax_base[src * stride_absmax + i]));
+    // four independent loads in flight per thread: a matrix has 9 K - 23 K block scales and this CTA is
+    // alone with them, so the loop is bound by load latency, not bandwidth
+    float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f, v3 = 0.0f;
+    const float *am = absmax_base + src * stride_absmax;
+    const int step = blockDim.x;
+    int i = threadIdx.x;
+    for (; i + 3 * step < n_absmax; i += 4 * step) {
+        const float a = __ldg(am + i), b = __ldg(am + i + step), c = __ldg(am + i + 2 * step), d = __ldg(am + i + 3 * step);
+        v0 = fmaxf(v0, fabsf(a)); v1 = fmaxf(v1, fabsf(b)); v2 = fmaxf(v2, fabsf(c)); v3 = fmaxf(v3, fabsf(d));
+    }
+    for (; i < n_absmax; i += step) v0 = fmaxf(v0, fabsf(__ldg(am + i)));
+    float v = fmaxf(fmaxf(v0, v1), fmaxf(v2, v3));
     if (diag_base)
-        for (int i = threadIdx.x; i < n_diag; i += blockDim.x) v = fmaxf(v, fabsf(diag_base[src * stride_diag + i]));
+        for (int k = threadIdx.x; k < n_diag; k += blockDim.x) v = fmaxf(v, fabsf(__ldg(diag_base + src * stride_diag + k)));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
     __shared__ float red[8];

@@ -90,9 +90,13 @@ class BlockPartitioner:
         return [tensor[idx] for idx in self.block_slices()]
 
     def merge_partitions(self, partitions):
-        out = torch.empty(self._shape, dtype=partitions[0].dtype, device=partitions[0].device)
         slices = self.block_slices()
         assert len(slices) == len(partitions)
+        if len(partitions) == 1:                              # not split: the block is the tensor
+            return partitions[0].reshape(self._shape)
+        if len(self._splits) == 1:                            # split along one dimension: one concatenation
+            return torch.cat(list(partitions), dim=self._splits[0][0])
+        out = torch.empty(self._shape, dtype=partitions[0].dtype, device=partitions[0].device)
         for idx, part in zip(slices, partitions):
             out[idx].copy_(part)
         return out
