@@ -89,14 +89,21 @@ class BlockPartitioner:
         assert tensor.shape == self._shape
         return [tensor[idx] for idx in self.block_slices()]
 
-    def merge_partitions(self, partitions):
+    def merge_partitions(self, partitions, out=None):
+        """The tensor whose blocks are `partitions`; written into `out` (same shape, contiguous) if given."""
         slices = self.block_slices()
         assert len(slices) == len(partitions)
         if len(partitions) == 1:                              # not split: the block is the tensor
-            return partitions[0].reshape(self._shape)
+            if out is None:
+                return partitions[0].reshape(self._shape)
+            out.copy_(partitions[0].reshape(self._shape))
+            return out
         if len(self._splits) == 1:                            # split along one dimension: one concatenation
-            return torch.cat(list(partitions), dim=self._splits[0][0])
-        out = torch.empty(self._shape, dtype=partitions[0].dtype, device=partitions[0].device)
+            if out is None:
+                return torch.cat(list(partitions), dim=self._splits[0][0])
+            return torch.cat(list(partitions), dim=self._splits[0][0], out=out)
+        if out is None:
+            out = torch.empty(self._shape, dtype=partitions[0].dtype, device=partitions[0].device)
         for idx, part in zip(slices, partitions):
             out[idx].copy_(part)
         return out
@@ -207,8 +214,11 @@ class Preconditioner:
             items.append((c0, s0, c1, s1, g))
         return items
 
-    def merge(self, blocks):
-        return torch.reshape(self._partitioner.merge_partitions(blocks), self._original_shape)
+    def merge(self, blocks, out=None):
+        """`out`: a contiguous tensor of the parameter's shape that receives the result (or None)."""
+        if out is not None:
+            out = out.view(self._partitioner._shape)
+        return torch.reshape(self._partitioner.merge_partitions(blocks, out), self._original_shape)
 
     # -- per-parameter entry points (reference API) --------------------------------------
     def _weights(self):
@@ -342,7 +352,7 @@ class _ShampooBase(optim.Optimizer):
         # captured graphs, pointer tables and exchange plans refer to the state that was just replaced
         self._graph_state = None
         self._plans = {}
-        for name in ("_tail_cache", "_scalar_ring", "_tail_scalars", "_pending_exchange", "_stable_direction_ptrs"):
+        for name in ("_tail_cache", "_scalar_ring", "_tail_scalars", "_pending_exchange", "_stable_direction_ptrs", "_last_tail_tab"):
             self.__dict__.pop(name, None)
         self._needs_eager = True                           # the next step rebuilds them eagerly
         for group in self.param_groups:
@@ -406,6 +416,10 @@ class _ShampooBase(optim.Optimizer):
                 self._init_moments(p, state)
             state['preconditioner'] = pre
 
+    def _tail_direction_views(self, params):
+        """Persistent buffers the update directions should be produced in, by parameter index (none here)."""
+        return {}
+
     def _precondition(self, group, params, split_exchange=False):
         """Runs the statistics / inverse-root / apply phases for `params` (all with grads) and
         returns the list of update directions (grafted to the gradient norm where active).
@@ -447,8 +461,10 @@ class _ShampooBase(optim.Optimizer):
                     owner.append((k, pre, len(items), len(items) + len(its)))
                     items += its
             blocks = E.preconditioned_blocks(items) if items else []
+            # the fused tail reads directions from one persistent buffer: merge straight into it
+            tail_views = self._tail_direction_views(params)
             for k, pre, a, b in owner:
-                directions[k] = pre.merge(blocks[a:b])
+                directions[k] = pre.merge(blocks[a:b], out=tail_views.get(k))
             # grafting: rescale the direction to the gradient's norm (shampoo2.py:453).  For
             # parameters without preconditioners the direction IS the gradient, scaled in place.
             ks = [k for k, _, pre in apply_list if not isinstance(pre, RemotePreconditioner)]
@@ -740,6 +756,17 @@ class ShampooAdamWBase(_ShampooBase):
                 return False
         return True
 
+    def _tail_direction_views(self, params):
+        """{parameter index: view of the tail's persistent direction buffer} from the table the last
+        fused tail used, if it was built for these parameters; empty otherwise (first step, other tail)."""
+        last = self.__dict__.get("_last_tail_tab")
+        if last is None or not FUSED_TAIL:
+            return {}
+        key, tab = last
+        if len(key) != 2 * len(params) or any(p.data_ptr() != q for p, q in zip(params, key)):
+            return {}
+        return {k: v for v, k in zip(tab["dviews"], tab["copy_idx"])}
+
     def _fused_tail(self, group, params, directions, scalars):
         """Decay, both moments and the update for every parameter in one launch (qt_adamw_tail).
         `scalars`: device tensor of the three step-dependent factors."""
@@ -777,8 +804,10 @@ class ShampooAdamWBase(_ShampooBase):
                 v=i64([self.state[p]['exp_avg_sq'].data_ptr() for p in params]), n=i64(numels),
                 d=i64(dptrs), dviews=views, dflat=flat, copy_idx=copy_idx,
                 ct=torch.tensor(ct_, dtype=torch.int32, device=dev), ci=torch.tensor(ci_, dtype=torch.int32, device=dev))
-        if tab["copy_idx"]:
-            torch._foreach_copy_(tab["dviews"], [directions[k] for k in tab["copy_idx"]])
+        self._last_tail_tab = (key, tab)
+        todo = [(v, directions[k]) for v, k in zip(tab["dviews"], tab["copy_idx"]) if directions[k].data_ptr() != v.data_ptr()]
+        if todo:                                              # directions that were not produced in place
+            torch._foreach_copy_([v for v, _ in todo], [d for _, d in todo])
         beta1, beta2 = group['betas']
         vp = lambda t: ct.c_void_p(t.data_ptr())
         with torch.cuda.device(dev):
