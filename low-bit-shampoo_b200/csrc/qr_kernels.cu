@@ -634,12 +634,15 @@ k_merge_t(const float *__restrict__ Gbase, long long ldg, long long strideG,
     float (*Ts)[kMergeMax + 1] = reinterpret_cast<float (*)[kMergeMax + 1]>(merge_sm);
     float (*M1)[kPanel + 1] = reinterpret_cast<float (*)[kPanel + 1]>(merge_sm + kMergeMax * (kMergeMax + 1));
     float (*Tk)[kPanel + 1] = reinterpret_cast<float (*)[kPanel + 1]>(merge_sm + kMergeMax * (kMergeMax + 1) + 96 * (kPanel + 1));
+    // the Gram matrix is staged once: the recurrence below reads each entry in a dependent chain
+    float (*Gs)[kMergeMax + 1] = reinterpret_cast<float (*)[kMergeMax + 1]>(merge_sm + kMergeMax * (kMergeMax + 1) + 96 * (kPanel + 1) +
+                                                                            kPanel * (kPanel + 1));
     const float *G = Gbase + (long long)blockIdx.x * strideG;
     const float *Tp = Tp_base + (long long)blockIdx.x * strideTp;
     float *T = Tbase + (long long)blockIdx.x * strideT;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // warp ty works on rows ty, ty+32, ..; lane = column
     for (int i = ty; i < wo; i += 32)
-        for (int j = tx; j < wo; j += 32) Ts[i][j] = 0.0f;
+        for (int j = tx; j < wo; j += 32) { Ts[i][j] = 0.0f; Gs[i][j] = __ldg(G + (long long)i * ldg + j); }
     __syncthreads();
     for (int c = 0, k = 0; c < wo; c += kPanel, ++k) {
         const int w = min(kPanel, wo - c);
@@ -648,10 +651,16 @@ k_merge_t(const float *__restrict__ Gbase, long long ldg, long long strideG,
         if (ty < w && tx < w) Ts[c + ty][c + tx] = Tk[ty][tx];
         if (c > 0) {
             for (int i = ty; i < c; i += 32) {                   // M1 = T[:c, :c] G[:c, c:c+w]; T is upper triangular
-                float acc = 0.0f;
-                if (tx < w)
-                    for (int l = i; l < c; ++l) acc = fmaf(Ts[i][l], __ldg(G + (long long)l * ldg + c + tx), acc);
-                M1[i][tx] = acc;
+                float acc = 0.0f, acc1 = 0.0f;
+                if (tx < w) {
+                    int l = i;
+                    for (; l + 1 < c; l += 2) {
+                        acc = fmaf(Ts[i][l], Gs[l][c + tx], acc);
+                        acc1 = fmaf(Ts[i][l + 1], Gs[l + 1][c + tx], acc1);
+                    }
+                    if (l < c) acc = fmaf(Ts[i][l], Gs[l][c + tx], acc);
+                }
+                M1[i][tx] = acc + acc1;
             }
             __syncthreads();
             for (int i = ty; i < c; i += 32) {                   // T[:c, c:c+w] = -M1 T_k; T_k is upper triangular
@@ -671,7 +680,7 @@ int launch_merge_t(const float *G, long long ldg, long long strideG, const float
     if (wo <= 0 || wo > kMergeMax || count < 0 || ldg < wo) return record(QT_ERR_ARG);
     if (!G || !Tp || !T) return record(QT_ERR_ARG);
     if (count == 0) return record(QT_OK);
-    constexpr size_t smem = sizeof(float) * (kMergeMax * (kMergeMax + 1) + 96 * (kPanel + 1) + kPanel * (kPanel + 1));
+    constexpr size_t smem = sizeof(float) * (2 * kMergeMax * (kMergeMax + 1) + 96 * (kPanel + 1) + kPanel * (kPanel + 1));
     static PerDeviceOnce attr_set;
     const int dev = current_device();
     if (attr_set.pending(dev)) {
