@@ -72,6 +72,15 @@ def test_block_partitioner_roundtrip():
     assert bp.num_splits() == 2
     # a dimension that is an exact multiple makes no empty block (reference: (d-1)//block_size)
     assert [tuple(p.shape) for p in BlockPartitioner(torch.zeros(8, 3), 4).partition(torch.zeros(8, 3))] == [(4, 3), (4, 3)]
+    # merge: every split pattern (none, rows only, columns only, both), with and without a destination
+    for shape in ((3, 4), (10, 3), (3, 10), (7, 10)):
+        x = torch.randn(*shape)
+        q = BlockPartitioner(x, 4)
+        blocks = [b.clone() for b in q.partition(x)]
+        assert torch.equal(q.merge_partitions(blocks), x)
+        dst = torch.full(shape, 7.0)
+        got = q.merge_partitions(blocks, out=dst)
+        assert got.data_ptr() == dst.data_ptr() and torch.equal(dst, x)
 
 
 def test_ridged_inverse_root_equals_reference_where_it_is_finite():
