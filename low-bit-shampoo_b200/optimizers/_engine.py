@@ -346,8 +346,8 @@ def op_ema_gram_selected(L, sel, G, axis, w1, w2):
 def op_subspace_step(L, Vt):
     """Orthonormal basis of L V (one subspace-iteration step, utils.py:157) and the Rayleigh
     quotients diag(V^T L V) (utils.py:158).  L, Vt are Mat; returns fp32 tensors."""
-    V = householder_q(mm(L, Vt, trans_b=True).f32, tensor_cores=_tc(L.f32))
-    LV = mm(L, Mat(V, bound=_UNIT_BOUND)).f32
+    V, Vp = householder_q(mm(L, Vt, trans_b=True).f32, tensor_cores=_tc(L.f32), with_planes=True)
+    LV = mm(L, Mat(V, planes=Vp, bound=_UNIT_BOUND)).f32            # the QR hands over the planes it kept of Q
     return V, column_dot(LV, V)
 
 

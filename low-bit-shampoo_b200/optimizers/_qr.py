@@ -117,9 +117,11 @@ def _background_ctas(device, batch):
     return free if free >= sms // 4 else 0
 
 
-def householder_q(X, tensor_cores=True):
+def householder_q(X, tensor_cores=True, with_planes=False):
     """Q of the QR factorisation of each X[b] (X: (B, n, n) fp32 CUDA, overwritten).
-    `tensor_cores=False` keeps every product in fp32 library products.  The planes of X carry one
+    `tensor_cores=False` keeps every product in fp32 library products.  `with_planes`: returns
+    (Q, operand planes of Q or None) - the accumulation keeps the planes of Q in step with its fp32
+    form anyway, so a caller that multiplies by Q next need not split it again.  The planes of X carry one
     exponent per matrix, fixed when X is first split: Householder reflections preserve column
     norms, so no entry of the trailing matrix outgrows sqrt(n) times the largest entry of X, which
     the split's headroom (largest entry below 2^9 of fp16's 2^16) covers up to n = 16384.
@@ -141,9 +143,11 @@ def householder_q(X, tensor_cores=True):
             _WARNED_LARGE = True
             warnings.warn(f"householder_q: order {n} exceeds the panel kernel's {MAX_ORDER} rows (a panel must fit one SM's "
                           "shared memory); using torch.linalg.qr for this order - per-matrix library QR, much slower")
-        return torch.linalg.qr(X).Q
+        Q = torch.linalg.qr(X).Q
+        return (Q, None) if with_planes else Q
     if (not X.is_cuda) or n < 2:
-        return torch.linalg.qr(X).Q
+        Q = torch.linalg.qr(X).Q
+        return (Q, None) if with_planes else Q
     F._require_lib(X)
     X = X.contiguous()
     lib = F.lib
@@ -222,10 +226,10 @@ def householder_q(X, tensor_cores=True):
             main.wait_stream(rest_stream)
             if forward_q:
                 main.wait_stream(q_stream)
-                return Q
+                return (Q, Qp) if with_planes else Q
         Q = torch.eye(n, dtype=torch.float32, device=X.device).expand(B, n, n).contiguous()
         Qp = split(Q, bound=2.0) if tc else None         # Q stays orthonormal: entries <= 1
         for J0, wo, Tb, Pv, Pt in reversed(blocks):
             m = n - J0
             _reflect(V[:, J0:, J0:J0 + wo], Tb, Q[:, J0:, J0:], Qp.window(J0, J0, m, m) if tc else None, False, Pv, Pt)
-    return Q
+    return (Q, Qp) if with_planes else Q
