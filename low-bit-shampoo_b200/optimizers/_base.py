@@ -523,15 +523,8 @@ class _ShampooBase(optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
-        # launches are free on graph replay: cut dominant order classes into more concurrent units
-        # (from the first, eager step on, so that every cached index list exists before capture)
-        split_before = E.SPLIT_CLASSES
-        E.SPLIT_CLASSES = split_before or self._use_graph
-        try:
-            self._step_groups()
-            self._needs_eager = False
-        finally:
-            E.SPLIT_CLASSES = split_before
+        self._step_groups()
+        self._needs_eager = False
 
     def _step_groups(self):
         for group in self.param_groups:
